@@ -1,0 +1,688 @@
+// context.cu -- the C ABI of include/cudarl.h: one context per GPU owning the shard's device
+// buffers, one stream, and (optionally) an NCCL communicator for replica averaging.
+// Host logic only; every hot operation is a kernel of kernels.cu.  There is no CPU fallback:
+// a call either runs on the device or returns an error code.
+#include "../../include/cudarl.h"
+#include "kernels.cuh"
+#include <nccl.h>
+#include <dlfcn.h>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+#include <new>
+
+using namespace cudarl;
+
+namespace {
+
+thread_local std::string g_err;
+
+// ---- host Philox4x32-10 for the one-time grid construction ---------------------------------------
+struct HW { uint32_t w[4]; };
+HW philox(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1) {
+    uint32_t c[4] = {c0, c1, c2, c3};
+    for (int r = 0; r < 10; ++r) {
+        uint64_t a = 0xD2511F53ull * c[0], b = 0xCD9E8D57ull * c[2];
+        uint32_t t0 = (uint32_t)(b >> 32) ^ c[1] ^ k0, t2 = (uint32_t)(a >> 32) ^ c[3] ^ k1;
+        c[1] = (uint32_t)b; c[3] = (uint32_t)a; c[0] = t0; c[2] = t2;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    return HW{{c[0], c[1], c[2], c[3]}};
+}
+constexpr uint32_t TG_GRID = 0x47524944u, TG_WALL = 0x57414C4Cu, TG_GOAL = 0x474F414Cu;
+inline uint32_t hi32(uint32_t a, uint32_t b) { return (uint32_t)(((uint64_t)a * b) >> 32); }
+
+// ---- NCCL through dlopen: the library loads (and single-GPU use works) without NCCL present ------
+struct NcclApi {
+    void* h = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    bool load(std::string& err) {
+        if (h) return true;
+        h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) { err = std::string("dlopen libnccl.so.2: ") + dlerror(); return false; }
+        GetUniqueId = (decltype(GetUniqueId))dlsym(h, "ncclGetUniqueId");
+        CommInitRank = (decltype(CommInitRank))dlsym(h, "ncclCommInitRank");
+        CommDestroy = (decltype(CommDestroy))dlsym(h, "ncclCommDestroy");
+        AllReduce = (decltype(AllReduce))dlsym(h, "ncclAllReduce");
+        GetErrorString = (decltype(GetErrorString))dlsym(h, "ncclGetErrorString");
+        if (!GetUniqueId || !CommInitRank || !CommDestroy || !AllReduce) { err = "NCCL symbols missing"; h = nullptr; return false; }
+        return true;
+    }
+};
+NcclApi g_nccl;
+
+__global__ void k_ctl_eps(Ctl* c, unsigned mode, unsigned len, unsigned long long base_k) {
+    c->eps_idx = 0; c->eps_mode = mode; c->eps_len = len; c->eps_base_k = base_k;
+}
+__global__ void k_ctl_eval_clear(Ctl* c) { c->eval_reached = 0; c->eval_steps = 0; }
+
+}  // namespace
+
+struct cudarl_ctx {
+    cudarl_config cfg{};
+    Params p{};
+    cudaStream_t st = nullptr;
+    std::string err;
+    std::vector<uint8_t> cells;           // host copy of the cell classes
+    // device buffers
+    void *dQ = nullptr, *dci = nullptr, *dx = nullptr, *dy = nullptr, *dt = nullptr, *dreward = nullptr, *ddone = nullptr;
+    void *dent = nullptr, *dblockcnt = nullptr, *dmailbox = nullptr, *dctl = nullptr, *deps = nullptr;
+    void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
+    void *ddense = nullptr;               // S float4: table in the caller's layout / allreduce buffer
+    void* dub[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; size_t ub_cap = 0;   // update_batch staging
+    void* dact = nullptr;                 // actions staging for the host form of step_actions
+    size_t ent_cap = 0, eps_cap = 0;
+    float* h_eps = nullptr; size_t h_eps_cap = 0; cudaEvent_t ev_eps = nullptr; bool eps_inflight = false;
+    float eps_fixed_cached = -1.0f; bool eps_fixed_valid = false;
+    // host mirror of schedule state
+    int64_t h_step = 0;
+    double eps_running = 1.0;
+    int64_t eval_calls = 0;
+    bool occ_valid = false, trace = false;
+    // communicator
+    ncclComm_t comm = nullptr; int rank = 0, nranks = 1;
+    // timing
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    bool ktiming = false; std::vector<cudaEvent_t> kev; size_t kev_used = 0;
+    double main_ms = 0, fix_ms = 0; int64_t klaunches = 0;
+};
+
+namespace {
+
+int fail(cudarl_ctx* c, int code, const std::string& m) { if (c) c->err = m; g_err = m; return code; }
+#define CK(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(c, 1000 + (int)e_, std::string(#call) + ": " + cudaGetErrorString(e_)); } while (0)
+#define NK(call) do { ncclResult_t r_ = (call); if (r_ != ncclSuccess) return fail(c, 2000 + (int)r_, std::string(#call) + ": " + (g_nccl.GetErrorString ? g_nccl.GetErrorString(r_) : "nccl error")); } while (0)
+
+size_t pow2ceil(size_t v) { size_t r = 1; while (r < v) r <<= 1; return r; }
+
+// Build the cell classes (0 free, 1 obstacle, 2 goal) from the config.
+int build_cells(cudarl_ctx* c, std::vector<uint8_t>& cells, uint32_t& start_cell, uint32_t& fallback) {
+    const cudarl_config& f = c->cfg;
+    const int W = f.width, H = f.height; const uint32_t S = (uint32_t)W * (uint32_t)H;
+    const uint32_t k0 = (uint32_t)f.seed, k1 = (uint32_t)(f.seed >> 32);
+    cells.assign(S, 0);
+    if (f.obstacle_kind == CUDARL_OBST_BERNOULLI) {
+        double t = (double)f.obstacle_p * 4294967296.0;
+        uint32_t thr = t <= 0.0 ? 0u : (t >= 4294967295.0 ? 0xFFFFFFFFu : (uint32_t)t);
+        for (uint32_t q = 0; q * 4u < S; ++q) {
+            HW r = philox(q, 0, 0, 0, k0, k1 ^ TG_GRID);
+            for (uint32_t j = 0; j < 4 && q * 4u + j < S; ++j) cells[q * 4u + j] = r.w[j] < thr ? 1 : 0;
+        }
+    } else if (f.obstacle_kind == CUDARL_OBST_WALLS) {
+        const int64_t want = (int64_t)std::floor((double)f.obstacle_p * (double)S);
+        int64_t have = 0;
+        for (uint32_t k = 0; have < want && k < 0x7fffffffu; ++k) {
+            HW r = philox(k, 0, 0, 0, k0, k1 ^ TG_WALL);
+            uint32_t o = hi32(r.w[0], S);
+            int ox = (int)(o % (uint32_t)W), oy = (int)(o / (uint32_t)W);
+            const bool horizontal = r.w[1] & 1u; const int len = 1 + (int)(r.w[2] & 31u);
+            for (int j = 0; j < len; ++j) {
+                int px = ox + (horizontal ? j : 0), py = oy + (horizontal ? 0 : j);
+                if (px >= W || py >= H) break;
+                uint8_t& cell = cells[(size_t)py * W + px];
+                if (!cell) { cell = 1; ++have; }
+            }
+        }
+    } else if (f.obstacle_kind != CUDARL_OBST_NONE) return fail(c, -1, "bad obstacle_kind");
+
+    int64_t fixed = -1;
+    if (f.start_mode == CUDARL_START_CENTRE) fixed = (int64_t)(H / 2) * W + W / 2;
+    else if (f.start_mode == CUDARL_START_FIXED) {
+        if (f.start_x < 0 || f.start_x >= W || f.start_y < 0 || f.start_y >= H) return fail(c, -1, "start cell out of range");
+        fixed = (int64_t)f.start_y * W + f.start_x;
+    } else if (f.start_mode != CUDARL_START_RANDOM) return fail(c, -1, "bad start_mode");
+    if (fixed >= 0) cells[fixed] = 0;
+    start_cell = fixed >= 0 ? (uint32_t)fixed : 0u;
+
+    if (f.goal_mode == CUDARL_GOAL_TOP_RIGHT) cells[W - 1] = 2;
+    else if (f.goal_mode == CUDARL_GOAL_LIST || f.goal_mode == CUDARL_GOAL_SEEDED) {
+        if (f.num_goals < 1 || f.num_goals > CUDARL_MAX_GOALS) return fail(c, -1, "num_goals out of range");
+        for (int g = 0; g < f.num_goals; ++g) {
+            if (f.goal_mode == CUDARL_GOAL_LIST) {
+                int gx = f.goal_xy[2 * g], gy = f.goal_xy[2 * g + 1];
+                if (gx < 0 || gx >= W || gy < 0 || gy >= H) return fail(c, -1, "goal cell out of range");
+                cells[(size_t)gy * W + gx] = 2;
+            } else {
+                uint32_t attempt = 0; bool ok = false;
+                for (; attempt < (1u << 20); ++attempt) {
+                    uint32_t cand = hi32(philox((uint32_t)g, attempt, 0, 0, k0, k1 ^ TG_GOAL).w[0], S);
+                    if (cells[cand] == 0 && (int64_t)cand != fixed) { cells[cand] = 2; ok = true; break; }
+                }
+                if (!ok) return fail(c, -1, "could not place a seeded goal");
+            }
+        }
+    } else return fail(c, -1, "bad goal_mode");
+
+    fallback = 0xFFFFFFFFu;
+    for (uint32_t s = 0; s < S; ++s) if (cells[s] == 0) { fallback = s; break; }
+    if (f.start_mode == CUDARL_START_RANDOM && fallback == 0xFFFFFFFFu) return fail(c, -1, "no free cell");
+    if (fallback == 0xFFFFFFFFu) fallback = start_cell;
+    return 0;
+}
+
+int upload_cells(cudarl_ctx* c) {
+    const size_t S = c->p.S, pad = (S + 15) / 16 * 16;
+    std::vector<uint8_t> b(pad, 0);
+    for (size_t s = 0; s < S; ++s) b[s] = c->cells[s] == 1 ? CI_OBST : (c->cells[s] == 2 ? CI_GOAL : 0);
+    CK(cudaMemcpyAsync(c->dci, b.data(), pad, cudaMemcpyHostToDevice, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    c->occ_valid = false;
+    return 0;
+}
+
+// (Re)allocate the collision buffers for `cap` entries.
+int ensure_entry_capacity(cudarl_ctx* c, size_t cap) {
+    if (cap <= c->ent_cap) return 0;
+    CK(cudaStreamSynchronize(c->st));
+    cudaFree(c->dent); cudaFree(c->dmailbox); cudaFree(c->dsckey); cudaFree(c->dscval);
+    c->dent = c->dmailbox = c->dsckey = c->dscval = nullptr; c->ent_cap = 0;
+    size_t slots = pow2ceil(cap) / 2; if (slots < 1024) slots = 1024;
+    unsigned lg = 0; while ((1ull << lg) < slots) ++lg;
+    size_t sc = 2 * pow2ceil(cap); if (sc < 4096) sc = 4096;
+    CK(cudaMalloc(&c->dent, cap * sizeof(uint4)));
+    CK(cudaMalloc(&c->dmailbox, slots * sizeof(unsigned)));
+    CK(cudaMemsetAsync(c->dmailbox, 0, slots * sizeof(unsigned), c->st));
+    CK(cudaMalloc(&c->dsckey, sc * sizeof(unsigned long long)));
+    CK(cudaMalloc(&c->dscval, sc * sizeof(float)));
+    c->p.ent = (uint4*)c->dent; c->p.mailbox = (unsigned*)c->dmailbox; c->p.mb_shift = 32u - lg;
+    c->p.sc_key = (unsigned long long*)c->dsckey; c->p.sc_val = (float*)c->dscval; c->p.sc_cap = (unsigned)sc;
+    c->ent_cap = cap; c->p.ent_cap = (unsigned)cap;
+    return 0;
+}
+
+int ensure_occupancy(cudarl_ctx* c) {
+    if (c->occ_valid) return 0;
+    launch_rebuild_occupancy(c->p, c->st);
+    CK(cudaGetLastError());
+    c->occ_valid = true;
+    return 0;
+}
+
+int ensure_step_buffers(cudarl_ctx* c) {
+    if (c->dreward) return 0;
+    size_t N = c->p.N ? c->p.N : 1;
+    CK(cudaMalloc(&c->dreward, N * sizeof(float)));
+    CK(cudaMalloc(&c->ddone, N));
+    CK(cudaMalloc(&c->dact, N * sizeof(int)));
+    CK(cudaMemsetAsync(c->dreward, 0, N * sizeof(float), c->st));
+    CK(cudaMemsetAsync(c->ddone, 0, N, c->st));
+    c->p.reward = (float*)c->dreward; c->p.done = (unsigned char*)c->ddone;
+    return 0;
+}
+
+int ensure_dense(cudarl_ctx* c) {
+    if (c->ddense) return 0;
+    CK(cudaMalloc(&c->ddense, (size_t)c->p.S * sizeof(float4)));
+    return 0;
+}
+
+// Stage `n` epsilons (host array) into the device table.
+int upload_eps(cudarl_ctx* c, const float* eps, size_t n) {
+    if (c->eps_inflight) { CK(cudaEventSynchronize(c->ev_eps)); c->eps_inflight = false; }
+    if (n > c->h_eps_cap) {
+        if (c->h_eps) cudaFreeHost(c->h_eps);
+        c->h_eps = nullptr; c->h_eps_cap = 0;
+        size_t cap = pow2ceil(n < 256 ? 256 : n);
+        CK(cudaMallocHost((void**)&c->h_eps, cap * sizeof(float)));
+        c->h_eps_cap = cap;
+    }
+    if (n > c->eps_cap) {
+        CK(cudaStreamSynchronize(c->st));
+        cudaFree(c->deps); c->deps = nullptr; c->eps_cap = 0;
+        size_t cap = pow2ceil(n < 256 ? 256 : n);
+        CK(cudaMalloc(&c->deps, cap * sizeof(float)));
+        c->eps_cap = cap; c->p.eps_tab = (const float*)c->deps;
+    }
+    std::memcpy(c->h_eps, eps, n * sizeof(float));
+    CK(cudaMemcpyAsync(c->deps, c->h_eps, n * sizeof(float), cudaMemcpyHostToDevice, c->st));
+    CK(cudaEventRecord(c->ev_eps, c->st));
+    c->eps_inflight = true; c->eps_fixed_valid = false;
+    return 0;
+}
+
+int drain_kernel_events(cudarl_ctx* c) {
+    if (!c->kev_used) return 0;
+    CK(cudaStreamSynchronize(c->st));
+    for (size_t k = 0; k + 2 < c->kev_used + 1; k += 3) {
+        float a = 0, b = 0;
+        CK(cudaEventElapsedTime(&a, c->kev[k], c->kev[k + 1]));
+        CK(cudaEventElapsedTime(&b, c->kev[k + 1], c->kev[k + 2]));
+        c->main_ms += a; c->fix_ms += b; c->klaunches += 1;
+    }
+    c->kev_used = 0;
+    return 0;
+}
+
+int average_now(cudarl_ctx* c) {
+    if (!c->comm || c->nranks <= 1) return 0;
+    int rc = ensure_dense(c); if (rc) return rc;
+    launch_q_gather(c->p, (float4*)c->ddense, c->st);
+    NK(g_nccl.AllReduce(c->ddense, c->ddense, (size_t)c->p.S * 4, ncclFloat, ncclSum, c->comm, c->st));
+    launch_q_scatter(c->p, (const float4*)c->ddense, 1.0f / (float)c->nranks, c->st);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+int run_steps(cudarl_ctx* c, int64_t n) {
+    for (int64_t k = 0; k < n; ++k) {
+        cudaEvent_t a = nullptr, b = nullptr, d = nullptr;
+        if (c->ktiming) {
+            if (c->kev_used + 3 > c->kev.size()) { int rc = drain_kernel_events(c); if (rc) return rc; }
+            a = c->kev[c->kev_used]; b = c->kev[c->kev_used + 1]; d = c->kev[c->kev_used + 2]; c->kev_used += 3;
+        }
+        launch_train_step(c->p, c->trace, c->st, a, b, d);
+        c->h_step += 1;
+        if (c->cfg.sync_every > 0 && c->comm && (c->h_step % c->cfg.sync_every) == 0) { int rc = average_now(c); if (rc) return rc; }
+    }
+    CK(cudaGetLastError());
+    return 0;
+}
+
+void free_all(cudarl_ctx* c) {
+    if (c->st) cudaStreamSynchronize(c->st);
+    if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+    void* bufs[] = {c->dQ, c->dci, c->dx, c->dy, c->dt, c->dreward, c->ddone, c->dent, c->dblockcnt, c->dmailbox, c->dctl, c->deps,
+                    c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->ddense, c->dact,
+                    c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6]};
+    for (void* b : bufs) if (b) cudaFree(b);
+    if (c->h_eps) cudaFreeHost(c->h_eps);
+    for (auto e : c->kev) cudaEventDestroy(e);
+    if (c->ev_eps) cudaEventDestroy(c->ev_eps);
+    if (c->ev0) cudaEventDestroy(c->ev0);
+    if (c->ev1) cudaEventDestroy(c->ev1);
+    if (c->st) cudaStreamDestroy(c->st);
+}
+
+}  // namespace
+
+// =================================================================================================
+extern "C" {
+
+const char* cudarl_version(void) { return "0.1.0"; }
+const char* cudarl_last_global_error(void) { return g_err.c_str(); }
+const char* cudarl_last_error(const cudarl_ctx* c) { return c ? c->err.c_str() : g_err.c_str(); }
+
+void cudarl_default_config(cudarl_config* f) {
+    std::memset(f, 0, sizeof(*f));
+    f->struct_size = (uint32_t)sizeof(*f);
+    f->width = 10; f->height = 10; f->num_envs = 1;
+    f->goal_mode = CUDARL_GOAL_TOP_RIGHT; f->start_mode = CUDARL_START_CENTRE;
+    f->lr = 0.1f; f->gamma = 0.99f;
+    f->eps_kind = CUDARL_EPS_MULT_PER_STEP; f->eps0 = 1.0; f->eps_decay = 0.995; f->eps_end = 0.0;
+    f->q_init_kind = CUDARL_QINIT_ZERO; f->q_init_scale = 0.01f;
+}
+
+int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
+    if (!f || !out) return fail(nullptr, -1, "null argument");
+    *out = nullptr;
+    if (f->struct_size != sizeof(cudarl_config)) return fail(nullptr, -1, "cudarl_config.struct_size mismatch");
+    if (f->width < 1 || f->height < 1) return fail(nullptr, -1, "grid must be at least 1x1");
+    if ((uint64_t)f->width * (uint64_t)f->height >= (1ull << 28)) return fail(nullptr, -1, "grid larger than 2^28 cells");
+    if (f->num_envs < 0 || f->num_envs >= (1ll << 31)) return fail(nullptr, -1, "num_envs out of range");
+    if (f->env_offset < 0 || f->env_offset + f->num_envs >= (1ll << 32)) return fail(nullptr, -1, "env_offset out of range");
+    if (f->max_steps < 0) return fail(nullptr, -1, "max_steps negative");
+    if (f->eps_kind < 0 || f->eps_kind > 3) return fail(nullptr, -1, "bad eps_kind");
+    cudarl_ctx* c = new (std::nothrow) cudarl_ctx();
+    if (!c) return fail(nullptr, -1, "out of host memory");
+    c->cfg = *f;
+    int rc = 0;
+    do {
+        cudaError_t e = cudaSetDevice(f->device);
+        if (e != cudaSuccess) { rc = fail(c, 1000 + (int)e, std::string("cudaSetDevice: ") + cudaGetErrorString(e)); break; }
+        Params& p = c->p;
+        p.W = f->width; p.H = f->height; p.S = (unsigned)(f->width * f->height); p.N = (unsigned)f->num_envs;
+        p.env_offset = (unsigned)f->env_offset; p.k0 = (uint32_t)f->seed; p.k1 = (uint32_t)(f->seed >> 32);
+        p.max_steps = f->max_steps; p.start_mode = f->start_mode; p.lr = f->lr; p.gamma = f->gamma; p.legacy_clamp = f->legacy_clamp;
+        p.nblocks_main = (p.N + BLOCK - 1) / BLOCK;
+        uint32_t sc = 0, fb = 0;
+        rc = build_cells(c, c->cells, sc, fb); if (rc) break;
+        p.start_cell = sc; p.fallback_start = fb;
+        auto body = [&]() -> int {
+            CK(cudaStreamCreateWithFlags(&c->st, cudaStreamNonBlocking));
+            CK(cudaEventCreateWithFlags(&c->ev_eps, cudaEventDisableTiming));
+            CK(cudaEventCreate(&c->ev0)); CK(cudaEventCreate(&c->ev1));
+            const size_t S = p.S, N = p.N ? p.N : 1, pad = (S + 15) / 16 * 16;
+            CK(cudaMalloc(&c->dQ, S * 2 * sizeof(float4)));
+            CK(cudaMalloc(&c->dci, pad));
+            CK(cudaMalloc(&c->dx, N * 4)); CK(cudaMalloc(&c->dy, N * 4)); CK(cudaMalloc(&c->dt, N * 4));
+            CK(cudaMalloc(&c->dblockcnt, (p.nblocks_main ? p.nblocks_main : 1) * sizeof(unsigned)));
+            CK(cudaMalloc(&c->dctl, sizeof(Ctl)));
+            CK(cudaMemsetAsync(c->dctl, 0, sizeof(Ctl), c->st));
+            CK(cudaMemsetAsync(c->dblockcnt, 0, (p.nblocks_main ? p.nblocks_main : 1) * sizeof(unsigned), c->st));
+            p.Q = (float4*)c->dQ; p.ci = (unsigned char*)c->dci; p.x = (int*)c->dx; p.y = (int*)c->dy; p.t = (int*)c->dt;
+            p.blockcnt = (unsigned*)c->dblockcnt; p.ctl = (Ctl*)c->dctl;
+            int r2 = ensure_entry_capacity(c, N); if (r2) return r2;
+            r2 = upload_cells(c); if (r2) return r2;
+            launch_q_init(p, f->q_init_kind, f->q_init_scale, c->st);
+            float e0 = (float)f->eps0; r2 = upload_eps(c, &e0, 1); if (r2) return r2;
+            k_ctl_eps<<<1, 1, 0, c->st>>>(p.ctl, 0u, 1u, 0ull);
+            launch_reset_all(p, c->st);
+            CK(cudaGetLastError());
+            CK(cudaStreamSynchronize(c->st));
+            return 0;
+        };
+        rc = body();
+    } while (0);
+    if (rc) { g_err = c->err; free_all(c); delete c; return rc; }
+    c->eps_running = (double)f->eps0;
+    *out = c;
+    return 0;
+}
+
+void cudarl_destroy(cudarl_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->cfg.device);
+    free_all(c);
+    delete c;
+}
+
+int cudarl_get_config(const cudarl_ctx* c, cudarl_config* out) { if (!c || !out) return -1; *out = c->cfg; return 0; }
+
+int cudarl_synchronize(cudarl_ctx* c) { if (!c) return -1; CK(cudaStreamSynchronize(c->st)); return 0; }
+
+int cudarl_reset_all(cudarl_ctx* c) {
+    if (!c) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    launch_reset_all(c->p, c->st);
+    CK(cudaGetLastError());
+    c->occ_valid = false;
+    return 0;
+}
+
+int cudarl_step_actions_device(cudarl_ctx* c, const int32_t* d_actions, float* d_rewards, uint8_t* d_dones) {
+    if (!c || !d_actions) return fail(c, -1, "null argument");
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = ensure_step_buffers(c); if (rc) return rc;
+    launch_step_actions(c->p, d_actions, d_rewards, d_dones, c->st);
+    CK(cudaGetLastError());
+    c->occ_valid = false;
+    return 0;
+}
+
+int cudarl_step_actions(cudarl_ctx* c, const int32_t* actions, float* rewards, uint8_t* dones) {
+    if (!c || !actions) return fail(c, -1, "null argument");
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = ensure_step_buffers(c); if (rc) return rc;
+    const size_t N = c->p.N;
+    CK(cudaMemcpyAsync(c->dact, actions, N * sizeof(int), cudaMemcpyHostToDevice, c->st));
+    launch_step_actions(c->p, (const int*)c->dact, nullptr, nullptr, c->st);
+    CK(cudaGetLastError());
+    if (rewards) CK(cudaMemcpyAsync(rewards, c->dreward, N * sizeof(float), cudaMemcpyDeviceToHost, c->st));
+    if (dones) CK(cudaMemcpyAsync(dones, c->ddone, N, cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    c->occ_valid = false;
+    return 0;
+}
+
+int cudarl_get_reward_done(cudarl_ctx* c, float* rewards, uint8_t* dones) {
+    if (!c) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = ensure_step_buffers(c); if (rc) return rc;
+    if (rewards) CK(cudaMemcpyAsync(rewards, c->dreward, (size_t)c->p.N * sizeof(float), cudaMemcpyDeviceToHost, c->st));
+    if (dones) CK(cudaMemcpyAsync(dones, c->ddone, (size_t)c->p.N, cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    return 0;
+}
+
+int cudarl_train_steps(cudarl_ctx* c, int64_t n) {
+    if (!c || n < 0) return fail(c, -1, "bad argument");
+    if (n == 0 || c->p.N == 0) return 0;
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = ensure_occupancy(c); if (rc) return rc;
+    const cudarl_config& f = c->cfg;
+    if (f.eps_kind == CUDARL_EPS_FIXED) {
+        if (!c->eps_fixed_valid) {
+            float e = (float)f.eps0; rc = upload_eps(c, &e, 1); if (rc) return rc;
+            k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 0u, 1u, 0ull);
+            c->eps_fixed_valid = true;
+        }
+    } else if (f.eps_kind == CUDARL_EPS_MULT_PER_STEP || f.eps_kind == CUDARL_EPS_LINEAR) {
+        std::vector<float> tab((size_t)n);
+        for (int64_t k = 0; k < n; ++k) {
+            if (f.eps_kind == CUDARL_EPS_MULT_PER_STEP) { tab[k] = (float)c->eps_running; c->eps_running *= (double)f.eps_decay; }
+            else {
+                int64_t g = c->h_step + k;
+                tab[k] = (f.eps_steps <= 0 || g >= f.eps_steps) ? (float)f.eps_end
+                       : (float)((double)f.eps0 + ((double)f.eps_end - (double)f.eps0) * (double)g / (double)f.eps_steps);
+            }
+        }
+        rc = upload_eps(c, tab.data(), (size_t)n); if (rc) return rc;
+        k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 1u, (unsigned)n, 0ull);
+    } else {  // per episode: index = episodes finished / environments, resolved on the device every step
+        Ctl h; CK(cudaMemcpyAsync(&h, c->dctl, sizeof(Ctl), cudaMemcpyDeviceToHost, c->st));
+        CK(cudaStreamSynchronize(c->st));
+        unsigned long long k0 = h.episodes / (unsigned long long)c->p.N;
+        std::vector<float> tab((size_t)n + 1);
+        double e = (double)f.eps0;
+        for (unsigned long long j = 0; j < k0; ++j) e *= (double)f.eps_decay;
+        for (int64_t k = 0; k <= n; ++k) { tab[k] = (float)e; e *= (double)f.eps_decay; }
+        rc = upload_eps(c, tab.data(), (size_t)n + 1); if (rc) return rc;
+        k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 2u, (unsigned)(n + 1), k0);
+    }
+    return run_steps(c, n);
+}
+
+int cudarl_train_steps_eps(cudarl_ctx* c, int64_t n, const float* eps_host) {
+    if (!c || n < 0 || (n > 0 && !eps_host)) return fail(c, -1, "bad argument");
+    if (n == 0 || c->p.N == 0) return 0;
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = ensure_occupancy(c); if (rc) return rc;
+    rc = upload_eps(c, eps_host, (size_t)n); if (rc) return rc;
+    k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 1u, (unsigned)n, 0ull);
+    return run_steps(c, n);
+}
+
+int cudarl_set_trace(cudarl_ctx* c, int on) {
+    if (!c) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    if (on && !c->dtra) {
+        size_t N = c->p.N ? c->p.N : 1;
+        CK(cudaMalloc(&c->dtra, N * 4)); CK(cudaMalloc(&c->dtrr, N * 4)); CK(cudaMalloc(&c->dtrd, N));
+        c->p.tr_a = (int*)c->dtra; c->p.tr_r = (float*)c->dtrr; c->p.tr_d = (unsigned char*)c->dtrd;
+    }
+    c->trace = on != 0;
+    return 0;
+}
+int cudarl_get_trace(cudarl_ctx* c, int32_t* a, float* r, uint8_t* d) {
+    if (!c || !c->dtra) return fail(c, -2, "trace is off");
+    CK(cudaSetDevice(c->cfg.device));
+    const size_t N = c->p.N;
+    if (a) CK(cudaMemcpyAsync(a, c->dtra, N * 4, cudaMemcpyDeviceToHost, c->st));
+    if (r) CK(cudaMemcpyAsync(r, c->dtrr, N * 4, cudaMemcpyDeviceToHost, c->st));
+    if (d) CK(cudaMemcpyAsync(d, c->dtrd, N, cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    return 0;
+}
+
+int cudarl_eval_rollout(cudarl_ctx* c, int32_t max_steps, cudarl_eval_stats* out) {
+    if (!c || !out || max_steps < 0) return fail(c, -1, "bad argument");
+    CK(cudaSetDevice(c->cfg.device));
+    k_ctl_eval_clear<<<1, 1, 0, c->st>>>(c->p.ctl);
+    launch_eval(c->p, max_steps, (unsigned long long)c->eval_calls, c->st);
+    CK(cudaGetLastError());
+    Ctl h; CK(cudaMemcpyAsync(&h, c->dctl, sizeof(Ctl), cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    c->eval_calls += 1;
+    out->envs = c->p.N; out->reached = (int64_t)h.eval_reached; out->total_steps = (int64_t)h.eval_steps;
+    out->reward_sum = (double)out->reached * 1.0 - 0.01 * (double)(out->total_steps - out->reached);
+    return 0;
+}
+
+int cudarl_update_batch(cudarl_ctx* c, int64_t n, const int32_t* sx, const int32_t* sy, const int32_t* a,
+                        const float* r, const int32_t* nx, const int32_t* ny, const uint8_t* dn) {
+    if (!c || n < 0) return fail(c, -1, "bad argument");
+    if (n == 0) return 0;
+    if (!sx || !sy || !a || !r || !nx || !ny || !dn) return fail(c, -1, "null argument");
+    if (n >= (1ll << 31)) return fail(c, -1, "batch too large");
+    const int W = c->p.W, H = c->p.H;
+    for (int64_t i = 0; i < n; ++i)   // src/q_learning.cu:192-194,212-214 reject these; the reference kernel would read out of bounds
+        if (sx[i] < 0 || sx[i] >= W || sy[i] < 0 || sy[i] >= H || a[i] < 0 || a[i] >= CUDARL_ACTIONS ||
+            nx[i] < 0 || nx[i] >= W || ny[i] < 0 || ny[i] >= H) return fail(c, -3, "Invalid state or action");
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = ensure_entry_capacity(c, (size_t)n); if (rc) return rc;
+    if ((size_t)n > c->ub_cap) {
+        CK(cudaStreamSynchronize(c->st));
+        for (auto& b : c->dub) { if (b) cudaFree(b); b = nullptr; }
+        c->ub_cap = 0;
+        size_t cap = pow2ceil((size_t)n);
+        for (int k = 0; k < 7; ++k) CK(cudaMalloc(&c->dub[k], cap * 4));
+        c->ub_cap = cap;
+    }
+    const void* src[7] = {sx, sy, a, r, nx, ny, dn};
+    for (int k = 0; k < 7; ++k) CK(cudaMemcpyAsync(c->dub[k], src[k], (size_t)n * (k == 6 ? 1 : 4), cudaMemcpyHostToDevice, c->st));
+    launch_update_batch(c->p, (unsigned)n, (const int*)c->dub[0], (const int*)c->dub[1], (const int*)c->dub[2], (const float*)c->dub[3],
+                        (const int*)c->dub[4], (const int*)c->dub[5], (const unsigned char*)c->dub[6], c->st);
+    CK(cudaGetLastError());
+    CK(cudaStreamSynchronize(c->st));
+    return 0;
+}
+
+int cudarl_get_state(cudarl_ctx* c, int32_t* x, int32_t* y, int32_t* t) {
+    if (!c) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    const size_t b = (size_t)c->p.N * 4;
+    if (x) CK(cudaMemcpyAsync(x, c->dx, b, cudaMemcpyDeviceToHost, c->st));
+    if (y) CK(cudaMemcpyAsync(y, c->dy, b, cudaMemcpyDeviceToHost, c->st));
+    if (t) CK(cudaMemcpyAsync(t, c->dt, b, cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    return 0;
+}
+
+int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const int32_t* t) {
+    if (!c) return -1;
+    const size_t N = c->p.N;
+    if (x) for (size_t i = 0; i < N; ++i) if (x[i] < 0 || x[i] >= c->p.W) return fail(c, -3, "Invalid state");
+    if (y) for (size_t i = 0; i < N; ++i) if (y[i] < 0 || y[i] >= c->p.H) return fail(c, -3, "Invalid state");
+    CK(cudaSetDevice(c->cfg.device));
+    if (x) CK(cudaMemcpyAsync(c->dx, x, N * 4, cudaMemcpyHostToDevice, c->st));
+    if (y) CK(cudaMemcpyAsync(c->dy, y, N * 4, cudaMemcpyHostToDevice, c->st));
+    if (t) CK(cudaMemcpyAsync(c->dt, t, N * 4, cudaMemcpyHostToDevice, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    c->occ_valid = false;
+    return 0;
+}
+
+int cudarl_get_q(cudarl_ctx* c, float* q) {
+    if (!c || !q) return fail(c, -1, "null argument");
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = ensure_dense(c); if (rc) return rc;
+    launch_q_gather(c->p, (float4*)c->ddense, c->st);
+    CK(cudaGetLastError());
+    CK(cudaMemcpyAsync(q, c->ddense, (size_t)c->p.S * sizeof(float4), cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    return 0;
+}
+int cudarl_set_q(cudarl_ctx* c, const float* q) {
+    if (!c || !q) return fail(c, -1, "null argument");
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = ensure_dense(c); if (rc) return rc;
+    CK(cudaMemcpyAsync(c->ddense, q, (size_t)c->p.S * sizeof(float4), cudaMemcpyHostToDevice, c->st));
+    launch_q_scatter(c->p, (const float4*)c->ddense, 1.0f, c->st);
+    CK(cudaGetLastError());
+    CK(cudaStreamSynchronize(c->st));
+    return 0;
+}
+
+int cudarl_get_cells(cudarl_ctx* c, uint8_t* cells) {
+    if (!c || !cells) return fail(c, -1, "null argument");
+    std::memcpy(cells, c->cells.data(), c->cells.size());
+    return 0;
+}
+
+static int set_cell(cudarl_ctx* c, int32_t x, int32_t y, unsigned cls, bool single_goal) {
+    if (!c) return -1;
+    if (x < 0 || x >= c->p.W || y < 0 || y >= c->p.H) return fail(c, -3, "Invalid state");
+    CK(cudaSetDevice(c->cfg.device));
+    const unsigned cell = (unsigned)y * (unsigned)c->p.W + (unsigned)x;
+    if (single_goal) {
+        for (auto& v : c->cells) if (v == 2) v = 0;
+        launch_cell_set(c->p, 0, 0, 1, c->st);
+    }
+    c->cells[cell] = (uint8_t)cls;
+    launch_cell_set(c->p, cell, cls == 1 ? CI_OBST : (cls == 2 ? CI_GOAL : 0u), 0, c->st);
+    CK(cudaGetLastError());
+    uint32_t fb = 0xFFFFFFFFu;
+    for (uint32_t s = 0; s < c->p.S; ++s) if (c->cells[s] == 0) { fb = s; break; }
+    c->p.fallback_start = fb == 0xFFFFFFFFu ? c->p.start_cell : fb;
+    CK(cudaStreamSynchronize(c->st));
+    return 0;
+}
+int cudarl_add_obstacle(cudarl_ctx* c, int32_t x, int32_t y) { return set_cell(c, x, y, 1, false); }
+int cudarl_set_goal(cudarl_ctx* c, int32_t x, int32_t y) { return set_cell(c, x, y, 2, true); }
+
+int cudarl_get_stats(cudarl_ctx* c, cudarl_stats* out) {
+    if (!c || !out) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    Ctl h; CK(cudaMemcpyAsync(&h, c->dctl, sizeof(Ctl), cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    std::memset(out, 0, sizeof(*out));
+    out->steps = (int64_t)h.step; out->env_steps = (int64_t)h.step * (int64_t)c->p.N;
+    out->episodes = (int64_t)h.episodes; out->goals = (int64_t)h.goals; out->timeouts = (int64_t)h.timeouts;
+    out->conflicts = (int64_t)h.conflicts; out->long_chains = (int64_t)h.long_chains;
+    out->reward_sum = (double)out->goals * 1.0 - 0.01 * (double)(out->env_steps - out->goals);
+    out->epsilon = h.eps_used; out->device_error = (int32_t)h.error;
+    return 0;
+}
+
+int cudarl_comm_unique_id(void* id128) {
+    cudarl_ctx* c = nullptr;
+    if (!id128) return fail(c, -1, "null argument");
+    std::string e; if (!g_nccl.load(e)) return fail(c, -4, e);
+    static_assert(sizeof(ncclUniqueId) == CUDARL_COMM_ID_BYTES, "ncclUniqueId size");
+    ncclUniqueId id; NK(g_nccl.GetUniqueId(&id));
+    std::memcpy(id128, &id, sizeof(id));
+    return 0;
+}
+int cudarl_comm_init(cudarl_ctx* c, const void* id128, int32_t rank, int32_t nranks) {
+    if (!c || !id128 || nranks < 1 || rank < 0 || rank >= nranks) return fail(c, -1, "bad argument");
+    std::string e; if (!g_nccl.load(e)) return fail(c, -4, e);
+    CK(cudaSetDevice(c->cfg.device));
+    ncclUniqueId id; std::memcpy(&id, id128, sizeof(id));
+    NK(g_nccl.CommInitRank(&c->comm, nranks, id, rank));
+    c->rank = rank; c->nranks = nranks;
+    return ensure_dense(c);
+}
+int cudarl_average_replicas(cudarl_ctx* c) {
+    if (!c) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    return average_now(c);
+}
+
+int cudarl_timer_start(cudarl_ctx* c) { if (!c) return -1; CK(cudaSetDevice(c->cfg.device)); CK(cudaEventRecord(c->ev0, c->st)); return 0; }
+int cudarl_timer_stop_ms(cudarl_ctx* c, float* ms) {
+    if (!c || !ms) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    CK(cudaEventRecord(c->ev1, c->st));
+    CK(cudaEventSynchronize(c->ev1));
+    CK(cudaEventElapsedTime(ms, c->ev0, c->ev1));
+    return 0;
+}
+int cudarl_kernel_timing(cudarl_ctx* c, int on) {
+    if (!c) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    if (on && c->kev.empty()) {
+        c->kev.resize(3 * 512);
+        for (auto& e : c->kev) CK(cudaEventCreate(&e));
+    }
+    if (!on) { int rc = drain_kernel_events(c); if (rc) return rc; }
+    else { c->main_ms = c->fix_ms = 0; c->klaunches = 0; c->kev_used = 0; }
+    c->ktiming = on != 0;
+    return 0;
+}
+int cudarl_kernel_time_ms(cudarl_ctx* c, float* main_ms, float* fix_ms, int64_t* launches) {
+    if (!c) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    int rc = drain_kernel_events(c); if (rc) return rc;
+    if (main_ms) *main_ms = (float)c->main_ms;
+    if (fix_ms) *fix_ms = (float)c->fix_ms;
+    if (launches) *launches = c->klaunches;
+    return 0;
+}
+
+}  // extern "C"

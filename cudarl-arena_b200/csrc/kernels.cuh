@@ -1,0 +1,85 @@
+// kernels.cuh -- device-side data layout and launch entry points shared by kernels.cu (the
+// sm_100a kernels) and context.cu (the C ABI).  Nothing here is visible outside the library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cudarl {
+
+// ---- per-cell info byte (one byte per grid cell, 16-byte padded array) -----------------------
+// One load of the byte of a target cell answers "obstacle?", "goal?", "which half of the Q row is
+// current?" and "is another environment standing there?" in a single L2 access.
+enum : unsigned {
+    CI_OBST   = 1u,   // static: cell blocks movement            (src/kernels.cu:29-36 of the reference)
+    CI_GOAL   = 2u,   // static: cell ends the episode, reward 1  (src/environment.cu:43-46)
+    CI_PAR    = 4u,   // which 16-byte half of the 32-byte Q row holds Q_t for this cell
+    CI_OCC    = 8u,   // >= 1 environment stands on the cell during the current step
+    CI_MULTI  = 16u,  // >= 2 environments stand on the cell during the current step
+    CI_OCCN   = 32u,  // the same two facts for the NEXT step, announced while the current one runs
+    CI_MULTIN = 64u,
+};
+
+// ---- control block in device memory ------------------------------------------------------------
+struct Ctl {
+    unsigned long long step;        // global batched step index g (keys the policy stream)
+    unsigned long long episodes, goals, timeouts, conflicts, long_chains;
+    unsigned long long eval_reached, eval_steps;
+    unsigned int eps_idx;           // index of the current step's epsilon in the table
+    unsigned int eps_mode;          // 0 fixed index, 1 advance by one per step, 2 per-episode index
+    unsigned int eps_len;           // table length (clamp)
+    unsigned long long eps_base_k;  // per-episode mode: table[0] belongs to episodes/N == eps_base_k
+    unsigned int scratch_cursor;    // bump allocator of the long-chain scratch, reset every step
+    unsigned int blocks_done;       // last-block detection of the fix kernel
+    unsigned int error;             // sticky internal error bits
+    float eps_used;                 // epsilon of the most recent step (for the stats call)
+};
+
+enum : unsigned { ERR_SCRATCH_OVERFLOW = 1u, ERR_BAD_STATE = 2u, ERR_BAD_TRANSITION = 4u, ERR_CHAIN_CYCLE = 8u };
+
+// ---- everything a kernel needs, passed by value ------------------------------------------------
+struct Params {
+    int W, H;
+    unsigned S;            // cells
+    unsigned N;            // local environments
+    unsigned env_offset;   // global index of local env 0
+    unsigned k0, k1;       // Philox key base = seed (k1 is xor-ed with the stream tag)
+    int max_steps;
+    int start_mode;
+    unsigned start_cell;   // CENTRE / FIXED start
+    unsigned fallback_start;
+    float lr, gamma;
+    int legacy_clamp;
+    float4* Q;             // 2*S float4: row s = {half0, half1}, 32-byte aligned
+    unsigned char* ci;     // S bytes (padded to 16)
+    int *x, *y, *t;        // structure-of-arrays environment state
+    float* reward; unsigned char* done;       // only for caller-driven stepping
+    uint4* ent;            // collision entries, one slot per environment / transition
+    unsigned ent_cap;      // slots in ent
+    unsigned* blockcnt;    // entries produced by each 256-thread block of the main kernel
+    unsigned* mailbox;     // hashed chain heads (0 = empty), power-of-two size
+    unsigned mb_shift;     // 32 - log2(mailbox slots)
+    Ctl* ctl;
+    const float* eps_tab;
+    int* tr_a; float* tr_r; unsigned char* tr_d;   // optional trace of the last step
+    unsigned long long* sc_key; float* sc_val; unsigned sc_cap;   // long-chain scratch (global)
+    unsigned nblocks_main;
+};
+
+constexpr int BLOCK = 256;
+
+// launch wrappers (kernels.cu); all asynchronous on `st`
+void launch_rebuild_occupancy(const Params& p, cudaStream_t st);
+void launch_reset_all(const Params& p, cudaStream_t st);
+void launch_train_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c);
+void launch_step_actions(const Params& p, const int* d_actions, float* d_rewards, unsigned char* d_dones, cudaStream_t st);
+void launch_eval(const Params& p, int max_steps, unsigned long long nonce, cudaStream_t st);
+void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* sy, const int* a, const float* r,
+                         const int* nx, const int* ny, const unsigned char* dn, cudaStream_t st);
+void launch_q_gather(const Params& p, float4* dense, cudaStream_t st);
+void launch_q_scatter(const Params& p, const float4* dense, float scale, cudaStream_t st);
+void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st);
+void launch_cells_get(const Params& p, unsigned char* d_cells, cudaStream_t st);
+void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st);
+int  kernel_attr_report(char* buf, int n);
+
+}  // namespace cudarl
