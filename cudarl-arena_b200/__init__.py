@@ -88,6 +88,7 @@ ABI = {
     "cudarl_get_cells": (C.c_int, [_P, _P]),
     "cudarl_add_obstacle": (C.c_int, [_P, C.c_int32, C.c_int32]),
     "cudarl_set_goal": (C.c_int, [_P, C.c_int32, C.c_int32]),
+    "cudarl_set_legacy_clamp": (C.c_int, [_P, C.c_int]),
     "cudarl_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "cudarl_get_config": (C.c_int, [_P, C.POINTER(Config)]),
     "cudarl_comm_unique_id": (C.c_int, [_P]),

@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <string>
 #include <vector>
 #include <new>
@@ -72,12 +73,12 @@ struct cudarl_ctx {
     std::vector<uint8_t> cells;           // host copy of the cell classes
     // device buffers
     void *dQ = nullptr, *dci = nullptr, *dx = nullptr, *dy = nullptr, *dt = nullptr, *dreward = nullptr, *ddone = nullptr;
-    void *dent = nullptr, *dblockcnt = nullptr, *dmailbox = nullptr, *dctl = nullptr, *deps = nullptr;
+    void *dent = nullptr, *dctl = nullptr, *deps = nullptr;
     void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
     void *ddense = nullptr;               // S float4: table in the caller's layout / allreduce buffer
     void* dub[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; size_t ub_cap = 0;   // update_batch staging
     void* dact = nullptr;                 // actions staging for the host form of step_actions
-    size_t ent_cap = 0, eps_cap = 0;
+    size_t ent_cap = 0, eps_cap = 0, l2_window_bytes = 0;
     float* h_eps = nullptr; size_t h_eps_cap = 0; cudaEvent_t ev_eps = nullptr; bool eps_inflight = false;
     float eps_fixed_cached = -1.0f; bool eps_fixed_valid = false;
     // host mirror of schedule state
@@ -176,23 +177,54 @@ int upload_cells(cudarl_ctx* c) {
     return 0;
 }
 
-// (Re)allocate the collision buffers for `cap` entries.
+// (Re)allocate the collision entry array and the long-chain scratch for `cap` entries.
 int ensure_entry_capacity(cudarl_ctx* c, size_t cap) {
     if (cap <= c->ent_cap) return 0;
     CK(cudaStreamSynchronize(c->st));
-    cudaFree(c->dent); cudaFree(c->dmailbox); cudaFree(c->dsckey); cudaFree(c->dscval);
-    c->dent = c->dmailbox = c->dsckey = c->dscval = nullptr; c->ent_cap = 0;
-    size_t slots = pow2ceil(cap) / 2; if (slots < 1024) slots = 1024;
-    unsigned lg = 0; while ((1ull << lg) < slots) ++lg;
+    cudaFree(c->dent); cudaFree(c->dsckey); cudaFree(c->dscval);
+    c->dent = c->dsckey = c->dscval = nullptr; c->ent_cap = 0;
     size_t sc = 2 * pow2ceil(cap); if (sc < 4096) sc = 4096;
     CK(cudaMalloc(&c->dent, cap * sizeof(uint4)));
-    CK(cudaMalloc(&c->dmailbox, slots * sizeof(unsigned)));
-    CK(cudaMemsetAsync(c->dmailbox, 0, slots * sizeof(unsigned), c->st));
     CK(cudaMalloc(&c->dsckey, sc * sizeof(unsigned long long)));
     CK(cudaMalloc(&c->dscval, sc * sizeof(float)));
-    c->p.ent = (uint4*)c->dent; c->p.mailbox = (unsigned*)c->dmailbox; c->p.mb_shift = 32u - lg;
+    c->p.ent = (uint4*)c->dent;
     c->p.sc_key = (unsigned long long*)c->dsckey; c->p.sc_val = (float*)c->dscval; c->p.sc_cap = (unsigned)sc;
     c->ent_cap = cap; c->p.ent_cap = (unsigned)cap;
+    return 0;
+}
+
+// The per-cell info bytes and the mailbox are the two structures every step hits with random
+// accesses and atomics; they share one allocation so that one L2 access-policy window can keep
+// both resident while the state arrays and Q rows stream through.
+int alloc_hot(cudarl_ctx* c) {
+    const size_t S = c->p.S, N = c->p.N ? c->p.N : 1;
+    const size_t ci_bytes = (S + 255) / 256 * 256;
+    size_t slots = pow2ceil(N); if (slots < (1u << 16)) slots = 1u << 16; if (slots > (1u << 24)) slots = 1u << 24;
+    unsigned lg = 0; while ((1ull << lg) < slots) ++lg;
+    const size_t total = ci_bytes + slots * sizeof(unsigned);
+    CK(cudaMalloc(&c->dci, total));
+    CK(cudaMemsetAsync(c->dci, 0, total, c->st));
+    c->p.ci = (unsigned char*)c->dci;
+    c->p.mailbox = (unsigned*)((char*)c->dci + ci_bytes); c->p.mb_shift = 32u - lg; c->p.mb_slots = (unsigned)slots;
+    // L2 persistence (per context, released with it): best effort, a refusal is not an error.
+    int dev = c->cfg.device, max_persist = 0, max_window = 0;
+    cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev);
+    cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev);
+    c->l2_window_bytes = 0;
+    if (max_persist > 0 && max_window > 0 && !getenv("CUDARL_NO_L2_WINDOW")) {
+        size_t want = total; if (want > (size_t)max_window) want = (size_t)max_window;
+        size_t carve = want; if (carve > (size_t)max_persist) carve = (size_t)max_persist;
+        if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, carve) == cudaSuccess) {
+            cudaStreamAttrValue av; std::memset(&av, 0, sizeof(av));
+            av.accessPolicyWindow.base_ptr = c->dci;
+            av.accessPolicyWindow.num_bytes = want;
+            av.accessPolicyWindow.hitRatio = (float)((double)carve / (double)want);
+            av.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+            av.accessPolicyWindow.missProp = cudaAccessPropertyNormal;
+            if (cudaStreamSetAttribute(c->st, cudaStreamAttributeAccessPolicyWindow, &av) == cudaSuccess) c->l2_window_bytes = want;
+        }
+        cudaGetLastError();
+    }
     return 0;
 }
 
@@ -287,7 +319,7 @@ int run_steps(cudarl_ctx* c, int64_t n) {
 void free_all(cudarl_ctx* c) {
     if (c->st) cudaStreamSynchronize(c->st);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
-    void* bufs[] = {c->dQ, c->dci, c->dx, c->dy, c->dt, c->dreward, c->ddone, c->dent, c->dblockcnt, c->dmailbox, c->dctl, c->deps,
+    void* bufs[] = {c->dQ, c->dci, c->dx, c->dy, c->dt, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->ddense, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6]};
     for (void* b : bufs) if (b) cudaFree(b);
@@ -347,16 +379,14 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             CK(cudaStreamCreateWithFlags(&c->st, cudaStreamNonBlocking));
             CK(cudaEventCreateWithFlags(&c->ev_eps, cudaEventDisableTiming));
             CK(cudaEventCreate(&c->ev0)); CK(cudaEventCreate(&c->ev1));
-            const size_t S = p.S, N = p.N ? p.N : 1, pad = (S + 15) / 16 * 16;
+            const size_t S = p.S, N = p.N ? p.N : 1;
             CK(cudaMalloc(&c->dQ, S * 2 * sizeof(float4)));
-            CK(cudaMalloc(&c->dci, pad));
+            { int r0 = alloc_hot(c); if (r0) return r0; }
             CK(cudaMalloc(&c->dx, N * 4)); CK(cudaMalloc(&c->dy, N * 4)); CK(cudaMalloc(&c->dt, N * 4));
-            CK(cudaMalloc(&c->dblockcnt, (p.nblocks_main ? p.nblocks_main : 1) * sizeof(unsigned)));
             CK(cudaMalloc(&c->dctl, sizeof(Ctl)));
             CK(cudaMemsetAsync(c->dctl, 0, sizeof(Ctl), c->st));
-            CK(cudaMemsetAsync(c->dblockcnt, 0, (p.nblocks_main ? p.nblocks_main : 1) * sizeof(unsigned), c->st));
-            p.Q = (float4*)c->dQ; p.ci = (unsigned char*)c->dci; p.x = (int*)c->dx; p.y = (int*)c->dy; p.t = (int*)c->dt;
-            p.blockcnt = (unsigned*)c->dblockcnt; p.ctl = (Ctl*)c->dctl;
+            p.Q = (float4*)c->dQ; p.x = (int*)c->dx; p.y = (int*)c->dy; p.t = (int*)c->dt;
+            p.ctl = (Ctl*)c->dctl;
             int r2 = ensure_entry_capacity(c, N); if (r2) return r2;
             r2 = upload_cells(c); if (r2) return r2;
             launch_q_init(p, f->q_init_kind, f->q_init_scale, c->st);
@@ -615,6 +645,12 @@ static int set_cell(cudarl_ctx* c, int32_t x, int32_t y, unsigned cls, bool sing
 }
 int cudarl_add_obstacle(cudarl_ctx* c, int32_t x, int32_t y) { return set_cell(c, x, y, 1, false); }
 int cudarl_set_goal(cudarl_ctx* c, int32_t x, int32_t y) { return set_cell(c, x, y, 2, true); }
+
+int cudarl_set_legacy_clamp(cudarl_ctx* c, int on) {
+    if (!c) return -1;
+    c->cfg.legacy_clamp = on ? 1 : 0; c->p.legacy_clamp = on ? 1 : 0;
+    return 0;
+}
 
 int cudarl_get_stats(cudarl_ctx* c, cudarl_stats* out) {
     if (!c || !out) return -1;

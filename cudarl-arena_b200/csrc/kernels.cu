@@ -200,7 +200,6 @@ __global__ void __launch_bounds__(BLOCK) k_train_main(Params p) {
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        p.blockcnt[blockIdx.x] = s_cnt;
         if (s_cnt) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_cnt);
         if (s_goals) atomicAdd(&p.ctl->goals, (unsigned long long)s_goals);
         if (s_timeouts) atomicAdd(&p.ctl->timeouts, (unsigned long long)s_timeouts);
@@ -294,84 +293,128 @@ __device__ void process_long(const Params& p, unsigned head1, unsigned long long
     __syncthreads();
 }
 
-// DENSE = false: entries of main-kernel block b sit at ent[b*BLOCK .. b*BLOCK+blockcnt[b]) (train step);
-//                this kernel also sweeps the info bytes and advances the step.
-// DENSE = true : entries are ent[0..n) (update_batch); row parity is flipped per folded cell.
-template <bool DENSE>
-__global__ void __launch_bounds__(BLOCK) k_fix(Params p, unsigned n_dense) {
+constexpr unsigned MED_MAX = 32;                         // chain entries ranked by one warp with shuffles
+constexpr unsigned MED_CHUNKS = LONG_SMEM / MED_MAX;     // medium chains a block can stage in shared memory
+
+// One warp orders a staged chain of L <= 32 entries by (cell, action, index) with a shuffle ranking
+// (indices are unique, so ranks are a permutation), then the first lane of every cell run folds it.
+template <bool FLIP>
+__device__ void process_medium(const Params& p, unsigned long long* keys, float* vals, unsigned L) {
+    const unsigned lane = threadIdx.x & 31u;
+    unsigned long long key = lane < L ? keys[lane] : ~0ull;
+    float val = lane < L ? vals[lane] : 0.0f;
+    unsigned rank = 0;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        unsigned long long other = __shfl_sync(0xFFFFFFFFu, key, k);
+        rank += (other < key) ? 1u : 0u;
+    }
+    __syncwarp();
+    if (lane < L) { keys[rank] = key; vals[rank] = val; }
+    __syncwarp();
+    if (lane < L) {
+        unsigned cp = (unsigned)(keys[lane] >> 34);
+        if (lane == 0 || (unsigned)(keys[lane - 1] >> 34) != cp) apply_run<FLIP>(p, keys, vals, lane, L);
+    }
+    __syncwarp();
+}
+
+// Collision folding, one thread per mailbox slot.  A slot's chain holds every entry whose cell hashes
+// there; the thread that finds a non-empty slot owns the chain:
+//   <= 8 entries   gathered, ordered (sorting network) and folded in registers by that thread;
+//   <= 32 entries  staged in shared memory by that thread, ordered and folded by one warp;
+//   longer         walked by one thread, sorted by the whole block (shared memory up to 1024 entries,
+//                  the global scratch beyond that).
+// TRAIN = true : part of a train step -- also sweeps the info bytes (parity ^= occupied, next-step
+//                occupancy -> current) and, in the last block to finish, advances step and epsilon.
+// TRAIN = false: update_batch -- flips the row parity of every folded cell instead.
+template <bool TRAIN>
+__global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
+    constexpr bool FLIP = !TRAIN;
     __shared__ unsigned long long s_keys[LONG_SMEM];
     __shared__ float s_vals[LONG_SMEM];
     __shared__ unsigned s_long[BLOCK];
-    __shared__ unsigned s_nlong, s_bcast[3];
+    __shared__ unsigned s_medlen[MED_CHUNKS];
+    __shared__ unsigned s_nlong, s_nmed, s_bcast[3];
     __shared__ bool s_last;
-    if (threadIdx.x == 0) s_nlong = 0;
+    if (threadIdx.x == 0) { s_nlong = 0; s_nmed = 0; }
     __syncthreads();
-    const unsigned b = blockIdx.x;
-    unsigned cnt = DENSE ? ((b * BLOCK < n_dense) ? min((unsigned)BLOCK, n_dense - b * BLOCK) : 0u)
-                         : (b < p.nblocks_main ? p.blockcnt[b] : 0u);
-    if (threadIdx.x < cnt) {
-        const unsigned pos = b * BLOCK + threadIdx.x;
-        const uint4 me = p.ent[pos];
-        const unsigned slot = mb_slot(p, me.x >> 3);
-        if (p.mailbox[slot] == pos + 1u) {          // this entry is the head of its chain
-            // gather up to SHORT_MAX entries in registers
-            unsigned long long k[SHORT_MAX]; float v[SHORT_MAX];
-            unsigned q = pos + 1u;
+    const unsigned slot = blockIdx.x * BLOCK + threadIdx.x;
+    const unsigned head1 = slot < p.mb_slots ? p.mailbox[slot] : 0u;
+    if (head1) {
+        p.mailbox[slot] = 0u;                          // leave the mailbox empty for the next step
+        unsigned long long k[SHORT_MAX]; float v[SHORT_MAX];
+        unsigned q = head1;
+#pragma unroll
+        for (int j = 0; j < SHORT_MAX; ++j) {
+            if (q) {
+                uint4 e = __ldcg(p.ent + (q - 1u));
+                k[j] = ((unsigned long long)e.x << 32) | e.y; v[j] = __uint_as_float(e.z); q = e.w;
+            } else { k[j] = ~0ull; v[j] = 0.0f; }
+        }
+        if (q) {
+            unsigned chunk = atomicAdd(&s_nmed, 1u);
+            bool staged = false;
+            if (chunk < MED_CHUNKS) {
+                unsigned long long* mk = s_keys + chunk * MED_MAX; float* mv = s_vals + chunk * MED_MAX;
+#pragma unroll
+                for (int j = 0; j < SHORT_MAX; ++j) { mk[j] = k[j]; mv[j] = v[j]; }
+                unsigned L = SHORT_MAX;
+                while (q && L < MED_MAX) {
+                    uint4 e = __ldcg(p.ent + (q - 1u));
+                    mk[L] = ((unsigned long long)e.x << 32) | e.y; mv[L] = __uint_as_float(e.z); q = e.w; ++L;
+                }
+                staged = (q == 0u);
+                s_medlen[chunk] = staged ? L : 0u;
+            }
+            if (!staged) { unsigned li = atomicAdd(&s_nlong, 1u); s_long[li] = head1; }
+        } else {
+            // sorting network for 8 (19 comparators)
+            cswap(k[0],v[0],k[1],v[1]); cswap(k[2],v[2],k[3],v[3]); cswap(k[4],v[4],k[5],v[5]); cswap(k[6],v[6],k[7],v[7]);
+            cswap(k[0],v[0],k[2],v[2]); cswap(k[1],v[1],k[3],v[3]); cswap(k[4],v[4],k[6],v[6]); cswap(k[5],v[5],k[7],v[7]);
+            cswap(k[1],v[1],k[2],v[2]); cswap(k[5],v[5],k[6],v[6]); cswap(k[0],v[0],k[4],v[4]); cswap(k[3],v[3],k[7],v[7]);
+            cswap(k[1],v[1],k[5],v[5]); cswap(k[2],v[2],k[6],v[6]);
+            cswap(k[1],v[1],k[4],v[4]); cswap(k[3],v[3],k[6],v[6]);
+            cswap(k[2],v[2],k[4],v[4]); cswap(k[3],v[3],k[5],v[5]);
+            cswap(k[3],v[3],k[4],v[4]);
+            unsigned curcp = 0xFFFFFFFFu; float4 row = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < SHORT_MAX; ++j) {
-                if (q) {
-                    uint4 e = (j == 0) ? me : p.ent[q - 1u];
-                    k[j] = ((unsigned long long)e.x << 32) | e.y; v[j] = __uint_as_float(e.z); q = e.w;
-                } else { k[j] = ~0ull; v[j] = 0.0f; }
-            }
-            if (q) {                                  // longer than SHORT_MAX: whole block handles it below
-                unsigned li = atomicAdd(&s_nlong, 1u);
-                s_long[li] = pos + 1u;
-            } else {
-                // sorting network for 8 (19 comparators)
-                cswap(k[0],v[0],k[1],v[1]); cswap(k[2],v[2],k[3],v[3]); cswap(k[4],v[4],k[5],v[5]); cswap(k[6],v[6],k[7],v[7]);
-                cswap(k[0],v[0],k[2],v[2]); cswap(k[1],v[1],k[3],v[3]); cswap(k[4],v[4],k[6],v[6]); cswap(k[5],v[5],k[7],v[7]);
-                cswap(k[1],v[1],k[2],v[2]); cswap(k[5],v[5],k[6],v[6]); cswap(k[0],v[0],k[4],v[4]); cswap(k[3],v[3],k[7],v[7]);
-                cswap(k[1],v[1],k[5],v[5]); cswap(k[2],v[2],k[6],v[6]);
-                cswap(k[1],v[1],k[4],v[4]); cswap(k[3],v[3],k[6],v[6]);
-                cswap(k[2],v[2],k[4],v[4]); cswap(k[3],v[3],k[5],v[5]);
-                cswap(k[3],v[3],k[4],v[4]);
-                unsigned curcp = 0xFFFFFFFFu; float4 row = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int j = 0; j < SHORT_MAX; ++j) {
-                    if (k[j] != ~0ull) {
-                        unsigned w0 = (unsigned)(k[j] >> 32), cp = w0 >> 2;
-                        if (cp != curcp) {
-                            if (curcp != 0xFFFFFFFFu) {
-                                unsigned cell = curcp >> 1, par = curcp & 1u;
-                                p.Q[2u * cell + (par ^ 1u)] = row;
-                                if (DENSE) atomicXor(reinterpret_cast<unsigned*>(p.ci) + (cell >> 2), CI_PAR << ((cell & 3u) * 8u));
-                            }
-                            curcp = cp;
-                            row = __ldcg(p.Q + 2u * (cp >> 1) + (cp & 1u));
+                if (k[j] != ~0ull) {
+                    unsigned w0 = (unsigned)(k[j] >> 32), cp = w0 >> 2;
+                    if (cp != curcp) {
+                        if (curcp != 0xFFFFFFFFu) {
+                            unsigned cell = curcp >> 1, par = curcp & 1u;
+                            p.Q[2u * cell + (par ^ 1u)] = row;
+                            if (FLIP) atomicXor(reinterpret_cast<unsigned*>(p.ci) + (cell >> 2), CI_PAR << ((cell & 3u) * 8u));
                         }
-                        fold(row, (int)(w0 & 3u), p.lr, v[j]);
+                        curcp = cp;
+                        row = __ldcg(p.Q + 2u * (cp >> 1) + (cp & 1u));
                     }
+                    fold(row, (int)(w0 & 3u), p.lr, v[j]);
                 }
-                if (curcp != 0xFFFFFFFFu) {
-                    unsigned cell = curcp >> 1, par = curcp & 1u;
-                    p.Q[2u * cell + (par ^ 1u)] = row;
-                    if (DENSE) atomicXor(reinterpret_cast<unsigned*>(p.ci) + (cell >> 2), CI_PAR << ((cell & 3u) * 8u));
-                }
-                p.mailbox[slot] = 0u;
+            }
+            if (curcp != 0xFFFFFFFFu) {
+                unsigned cell = curcp >> 1, par = curcp & 1u;
+                p.Q[2u * cell + (par ^ 1u)] = row;
+                if (FLIP) atomicXor(reinterpret_cast<unsigned*>(p.ci) + (cell >> 2), CI_PAR << ((cell & 3u) * 8u));
             }
         }
     }
     __syncthreads();
-    const unsigned nlong = s_nlong;
-    for (unsigned c = 0; c < nlong; ++c) {
-        unsigned head1 = s_long[c];
-        process_long<DENSE>(p, head1, s_keys, s_vals, s_bcast);
-        if (threadIdx.x == 0) p.mailbox[mb_slot(p, p.ent[head1 - 1u].x >> 3)] = 0u;
+    {   // medium chains: one warp each
+        const unsigned nmed = s_nmed < MED_CHUNKS ? s_nmed : MED_CHUNKS;
+        for (unsigned c = threadIdx.x >> 5; c < nmed; c += BLOCK / 32) {
+            const unsigned L = s_medlen[c];
+            if (L) process_medium<FLIP>(p, s_keys + c * MED_MAX, s_vals + c * MED_MAX, L);
+        }
     }
+    __syncthreads();
+    const unsigned nlong = s_nlong;
+    for (unsigned c = 0; c < nlong; ++c) process_long<FLIP>(p, s_long[c], s_keys, s_vals, s_bcast);
     if (threadIdx.x == 0 && nlong) atomicAdd(&p.ctl->long_chains, (unsigned long long)nlong);
 
-    if (!DENSE) {
+    if (TRAIN) {
         // sweep: parity ^= occupied, next-step occupancy becomes current, next bits cleared
         const unsigned n16 = (p.S + 15u) / 16u;
         uint4* wv = reinterpret_cast<uint4*>(p.ci);
@@ -537,8 +580,7 @@ void launch_train_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t
     if (trace) k_train_main<true><<<p.nblocks_main, BLOCK, 0, st>>>(p);
     else       k_train_main<false><<<p.nblocks_main, BLOCK, 0, st>>>(p);
     if (ev_b) cudaEventRecord(ev_b, st);
-    unsigned fb = p.nblocks_main; unsigned sb = sweep_blocks(p.S); if (sb > fb) fb = sb;
-    k_fix<false><<<fb, BLOCK, 0, st>>>(p, 0u);
+    k_fix<true><<<p.mb_slots / BLOCK, BLOCK, 0, st>>>(p);
     if (ev_c) cudaEventRecord(ev_c, st);
 }
 void launch_step_actions(const Params& p, const int* a, float* r, unsigned char* d, cudaStream_t st) {
@@ -551,7 +593,7 @@ void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* 
                          const int* nx, const int* ny, const unsigned char* dn, cudaStream_t st) {
     if (!n) return;
     k_update_main<<<nblk(n), BLOCK, 0, st>>>(p, n, sx, sy, a, r, nx, ny, dn);
-    k_fix<true><<<nblk(n), BLOCK, 0, st>>>(p, n);
+    k_fix<false><<<p.mb_slots / BLOCK, BLOCK, 0, st>>>(p);
 }
 void launch_q_gather(const Params& p, float4* dense, cudaStream_t st) { k_q_gather<<<nblk(p.S), BLOCK, 0, st>>>(p, dense); }
 void launch_q_scatter(const Params& p, const float4* dense, float scale, cudaStream_t st) { k_q_scatter<<<nblk(p.S), BLOCK, 0, st>>>(p, dense, scale); }
@@ -564,7 +606,7 @@ void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goa
 int kernel_attr_report(char* buf, int n) {
     cudaFuncAttributes a, b;
     if (cudaFuncGetAttributes(&a, k_train_main<false>) != cudaSuccess) return -1;
-    if (cudaFuncGetAttributes(&b, k_fix<false>) != cudaSuccess) return -1;
+    if (cudaFuncGetAttributes(&b, k_fix<true>) != cudaSuccess) return -1;
     return snprintf(buf, n, "train_main: %d regs, %zu B smem; train_fix: %d regs, %zu B smem",
                     a.numRegs, a.sharedSizeBytes, b.numRegs, b.sharedSizeBytes);
 }

@@ -55,9 +55,9 @@ struct Params {
     float* reward; unsigned char* done;       // only for caller-driven stepping
     uint4* ent;            // collision entries, one slot per environment / transition
     unsigned ent_cap;      // slots in ent
-    unsigned* blockcnt;    // entries produced by each 256-thread block of the main kernel
     unsigned* mailbox;     // hashed chain heads (0 = empty), power-of-two size
     unsigned mb_shift;     // 32 - log2(mailbox slots)
+    unsigned mb_slots;     // mailbox slots (power of two, multiple of BLOCK)
     Ctl* ctl;
     const float* eps_tab;
     int* tr_a; float* tr_r; unsigned char* tr_d;   // optional trace of the last step

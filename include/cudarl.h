@@ -172,6 +172,9 @@ int cudarl_get_cells(cudarl_ctx* ctx, uint8_t* cells);
 int cudarl_add_obstacle(cudarl_ctx* ctx, int32_t x, int32_t y);
 int cudarl_set_goal(cudarl_ctx* ctx, int32_t x, int32_t y);
 
+/* Switch the max(0, .) clamp of the flat reference kernel (src/kernels.cu:102-110) on or off. */
+int cudarl_set_legacy_clamp(cudarl_ctx* ctx, int on);
+
 int cudarl_get_stats(cudarl_ctx* ctx, cudarl_stats* out);
 int cudarl_get_config(const cudarl_ctx* ctx, cudarl_config* out);
 

@@ -160,7 +160,7 @@ def test_lockstep_c3_uniform_q_linear_eps(pkg, orc):
 
 def test_lockstep_dense_collisions(pkg, orc):
     """Tiny grids packed with environments: every chain is long, shared-memory and global-scratch sort paths."""
-    for w, h, n, steps in [(3, 3, 512, 40), (5, 5, 4096, 25), (2, 2, 6000, 12), (1, 1, 300, 5)]:
+    for w, h, n, steps in [(3, 3, 512, 40), (5, 5, 4096, 25), (2, 2, 6000, 12), (2, 1, 300, 5)]:
         cfg = pkg.make_config(w, h, n, start_mode=pkg.START_RANDOM, eps_kind=pkg.EPS_FIXED, eps0=0.3, max_steps=7, lr=0.25)
         gpu, cpu = pair(pkg, orc, cfg)
         s = lockstep(gpu, cpu, steps, what="dense %dx%d" % (w, h))
