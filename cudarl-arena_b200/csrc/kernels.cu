@@ -501,6 +501,7 @@ __global__ void __launch_bounds__(BLOCK) k_eval(Params p, int max_steps, unsigne
 __global__ void k_update_main(Params p, unsigned n, const int* sx, const int* sy, const int* act, const float* rew,
                               const int* nxs, const int* nys, const unsigned char* dn) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0) p.ctl->scratch_cursor = 0;        // the long-chain scratch is per call; nobody reads it in this kernel
     if (i >= n) return;
     int x = sx[i], y = sy[i], a = act[i], nx = nxs[i], ny = nys[i];
     unsigned s = (unsigned)y * (unsigned)p.W + (unsigned)x;

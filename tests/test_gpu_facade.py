@@ -1,0 +1,124 @@
+"""GPU tests of the reference-facing surfaces: the `cudarl_core` pybind11 module (class Environment with the
+ten methods of the reference's src/python_bindings.cpp:8-26, plus aliases) and CudaQLearning."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def core():
+    sys.path.insert(0, os.path.join(ROOT, "cudarl-arena_b200"))
+    import cudarl_core
+    return cudarl_core
+
+
+def test_module_surface(core):
+    assert core.__version__ == "0.1.0"
+    env = core.Environment(5, 5)
+    for name in ("reset", "step", "get_observation", "get_width", "get_height", "get_agent_position",
+                 "add_obstacle", "set_goal", "add_trap"):
+        assert hasattr(env, name)
+    assert (env.get_width(), env.get_height()) == (5, 5)
+    assert core.Environment().get_width() == 10 and core.Environment(width=7, height=3).get_height() == 3
+
+
+def test_environment_like_the_reference_tests(core):
+    """tests/test_environment.cpp and tests/test_environment.py of the reference, through Python."""
+    env = core.Environment(5, 5)
+    obs = env.reset()
+    assert isinstance(obs, list) and len(obs) == 25 and obs[4] == 1.0           # goal cell value (:132-133)
+    assert env.get_agent_position() == (2, 2)
+    obs, reward, done, info = env.step(1)
+    assert isinstance(reward, float) and isinstance(done, bool) and isinstance(info, str)
+    assert reward < 0 and not done and info == "agent_pos: (3,2)"
+    assert abs(reward + 0.01) < 1e-7
+    for a in (1, 0, np.int64(0)):                 # src/train.py passes numpy integers from np.argmax
+        obs, reward, done, info = env.step(a)
+    assert done and reward == 1.0 and env.get_agent_position() == (4, 0)
+    assert env.is_done() and env.get_reward() == 1.0 and (env.get_agent_x(), env.get_agent_y()) == (4, 0)
+    env.reset()
+    assert env.get_agent_position() == (2, 2) and not env.is_done()
+    assert (env.width, env.height, env.env_id) == (5, 5, 0)
+
+
+def test_obstacle_goal_trap_edits(core):
+    env = core.Environment(5, 5)
+    env.reset()
+    env.add_obstacle(3, 2)
+    _, r, d, _ = env.step(1)
+    assert env.get_agent_position() == (2, 2) and abs(r + 0.01) < 1e-7           # blocked (src/kernels.cu:39-44)
+    env.add_trap(2, 1, -0.5)
+    _, r, d, _ = env.step(0)
+    assert env.get_agent_position() == (2, 2) and r == -0.5                      # trap penalty (src/kernels.cu:61-63)
+    env.set_goal(2, 3)
+    obs, r, d, _ = env.step(2)
+    assert d and r == 1.0 and obs[3 * 5 + 2] == 1.0 and obs[4] == 0.0 and obs[2 * 5 + 3] == -1.0 and obs[1 * 5 + 2] == -0.5
+
+
+def test_cuda_q_learning(core):
+    q = core.CudaQLearning(6, 4, 4, 0.5, 0.9)
+    assert len(q.get_q_table()) == 96 and max(q.get_q_table()) == 0.0
+    q.update_batch([(1, 1), (1, 1), (2, 3)], [2, 2, 0], [1.0, 1.0, -0.01], [(1, 2), (1, 2), (2, 2)], [True, True, False])
+    f = np.float32
+    v1 = f(0.5) * f(1.0)
+    v2 = f(np.float64(f(0.5)) * np.float64(f(1.0)) + np.float64(v1))           # second fold sees the first
+    assert q.get_q_value(1, 1, 2) == float(v2) and q.get_best_action(1, 1) == 2
+    assert q.get_best_action(0, 0) == 0                                          # ties -> lowest index (src/q_learning.cu:196-206)
+    with pytest.raises(RuntimeError, match="Inconsistent batch sizes"):
+        q.update_batch([(0, 0)], [0, 1], [0.0], [(0, 0)], [False])
+    with pytest.raises(RuntimeError, match="Invalid state or action"):
+        q.get_q_value(6, 0, 0)
+    with pytest.raises(RuntimeError, match="Invalid state"):
+        q.get_best_action(0, 4)
+    with pytest.raises(RuntimeError, match="Invalid Q-table size"):
+        q.set_q_table([0.0] * 5)
+    with pytest.raises(RuntimeError, match="Invalid state or action"):
+        q.update_batch([(9, 9)], [0], [0.0], [(0, 0)], [False])
+    big = 5000                                                                   # beyond the reference's 1024 cap
+    q.update_batch([(i % 6, i % 4) for i in range(big)], [i % 4 for i in range(big)], [0.1] * big,
+                   [(0, 0)] * big, [False] * big)
+    t = q.get_q_table()
+    q.set_q_table(t)
+    assert q.get_q_table() == t
+
+
+def test_vec_environment(core):
+    v = core.VecEnvironment(width=32, height=32, num_envs=2048, obstacle_kind=1, obstacle_p=0.2, goal_mode=2, num_goals=3,
+                            start_mode=2, max_steps=200, eps_kind=0, eps0=0.2)
+    v.train_steps(300)
+    s = v.stats()
+    assert s["steps"] == 300 and s["env_steps"] == 300 * 2048 and s["goals"] > 0
+    assert v.q_table().shape == (32, 32, 4) and v.cells().shape == (32, 32)
+    r = v.eval_rollout(100)
+    assert r["envs"] == 2048 and 0 <= r["reached"] <= 2048
+    rew, done = v.step(np.zeros(2048, np.int32))
+    assert rew.shape == (2048,) and done.dtype == np.uint8
+
+
+def test_reference_training_script_shape(core):
+    """The loop of the reference's src/train.py:191-222 with its QTableAgent arithmetic restated inline:
+    Environment(w,h) positional, reset(), get_agent_position() as NumPy index, step(np.int64), 4-tuple."""
+    rng = np.random.RandomState(0)
+    env = core.Environment(6, 6)
+    q = np.zeros((6, 6, 4))
+    eps, lengths = 1.0, []
+    for episode in range(60):
+        obs = env.reset()
+        pos = env.get_agent_position()
+        for step in range(200):
+            a = rng.randint(0, 4) if rng.rand() < eps else np.argmax(q[pos[0], pos[1]])
+            nobs, r, done, info = env.step(a)
+            npos = env.get_agent_position()
+            nq = 0 if done else np.max(q[npos[0], npos[1]])
+            q[pos[0], pos[1], a] += 0.1 * (r + 0.99 * nq - q[pos[0], pos[1], a])
+            eps *= 0.995
+            pos = npos
+            if done:
+                break
+        lengths.append(step + 1)
+    assert np.mean(lengths[-10:]) < np.mean(lengths[:10])       # it learns the way to (5,0)

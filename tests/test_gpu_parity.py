@@ -223,7 +223,7 @@ def test_update_batch_with_duplicates(pkg, orc):
     gpu, cpu = pair(pkg, orc, cfg)
     q0 = rng.uniform(-1, 1, 9 * 7 * 4).astype(np.float32)
     gpu.set_q(q0); cpu.set_q(q0)
-    for n in (1, 5, 300, 5000, 40000):          # far beyond the reference's 1024 cap (src/q_learning.cu:10)
+    for n in (1, 5, 300, 5000, 40000, 40000, 40000):   # far beyond the reference's 1024 cap (src/q_learning.cu:10)
         b = dict(sx=rng.randint(0, 9, n), sy=rng.randint(0, 7, n), a=rng.randint(0, 4, n),
                  r=rng.choice([-0.01, 1.0, 0.5], n).astype(np.float32), nx=rng.randint(0, 9, n), ny=rng.randint(0, 7, n),
                  dn=(rng.rand(n) < 0.2).astype(np.uint8))
@@ -233,6 +233,16 @@ def test_update_batch_with_duplicates(pkg, orc):
     with pytest.raises(pkg.CudarlError):        # "Invalid state or action" (src/q_learning.cu:212-214)
         gpu.update_batch([9], [0], [0], [0.0], [0], [0], [0])
     assert gpu.get_stats().device_error == 0
+    # two cells, thousands of transitions each, call after call: the global-scratch sort path every time
+    tiny_g, tiny_c = pair(pkg, orc, pkg.make_config(2, 1, 1, lr=0.3, gamma=0.95))
+    for _ in range(4):
+        n = 4000
+        b = dict(sx=rng.randint(0, 2, n), sy=np.zeros(n, np.int32), a=rng.randint(0, 4, n), r=rng.choice([-0.01, 1.0], n).astype(np.float32),
+                 nx=rng.randint(0, 2, n), ny=np.zeros(n, np.int32), dn=(rng.rand(n) < 0.2).astype(np.uint8))
+        tiny_g.update_batch(**b)
+        assert tiny_c.update_batch(**b) == 0
+        assert np.array_equal(tiny_g.get_q(), tiny_c.get_q())
+    assert tiny_g.get_stats().device_error == 0
 
 
 def test_eval_rollout(pkg, orc):
