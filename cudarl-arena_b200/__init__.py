@@ -19,6 +19,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libcudarl.so")
 MAX_GOALS = 64
+STATIC_MAX_BATCH = 65536
 COMM_ID_BYTES = 128
 
 OBST_NONE, OBST_BERNOULLI, OBST_WALLS = 0, 1, 2
@@ -80,6 +81,8 @@ ABI = {
     "cudarl_get_trace": (C.c_int, [_P, _P, _P, _P]),
     "cudarl_eval_rollout": (C.c_int, [_P, C.c_int32, C.POINTER(EvalStats)]),
     "cudarl_update_batch": (C.c_int, [_P, C.c_int64, _P, _P, _P, _P, _P, _P, _P]),
+    "cudarl_update_batch_static": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int64, _P, _P, _P, _P, _P, _P, _P,
+                                            C.c_float, C.c_float, C.c_int32, _P]),
     "cudarl_get_state": (C.c_int, [_P, _P, _P, _P]),
     "cudarl_set_state": (C.c_int, [_P, _P, _P, _P]),
     "cudarl_get_reward_done": (C.c_int, [_P, _P, _P]),

@@ -1,6 +1,6 @@
 """Build recipe for the native pieces: explicit nvcc / g++ command lines, outputs in-tree.
 
-  libcudarl.so          cudarl-arena_b200/csrc/{kernels.cu,context.cu,facade.cpp}  (sm_100a only)
+  libcudarl.so          cudarl-arena_b200/csrc/{kernels.cu,context.cu,update_static.cu,facade.cpp}  (sm_100a only)
   cudarl_core*.so       pybind11 module with the reference's `cudarl_core` surface
   oracle/liboracle.so   the CPU oracle (test infrastructure)
   oracle/_ref/libref.so the reference's own kernels, compiled from the reference checkout when it
@@ -52,7 +52,7 @@ def _run(cmd, log=None):
 
 
 def build_lib(force=False):
-    srcs = [os.path.join(CSRC, f) for f in ("kernels.cu", "context.cu", "facade.cpp")]
+    srcs = [os.path.join(CSRC, f) for f in ("kernels.cu", "context.cu", "update_static.cu", "facade.cpp")]
     deps = srcs + [os.path.join(CSRC, "kernels.cuh"), os.path.join(CSRC, "facade.h"), os.path.join(ROOT, "include", "cudarl.h")]
     deps = [d for d in deps if os.path.exists(d)]
     srcs = [s for s in srcs if os.path.exists(s)]
@@ -99,13 +99,13 @@ def build_ref(force=False):
     if not os.path.isdir(REFERENCE_SRC) or not os.path.exists(harness):
         return REF_LIB if os.path.exists(REF_LIB) else None
     srcs = [harness, os.path.join(REFERENCE_SRC, "kernels.cu"), os.path.join(REFERENCE_SRC, "environment.cu"),
-            os.path.join(REFERENCE_SRC, "gpu", "kernels.cu")]
+            os.path.join(REFERENCE_SRC, "gpu", "kernels.cu")]   # the last three are #included by the harness
     if not force and _newer(REF_LIB, srcs):
         return REF_LIB
     os.makedirs(REF_DIR, exist_ok=True)
     # the reference's own flags (CMakeLists.txt:67-72) except the architecture list
     cmd = [_nvcc(), "-O2", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC", "-shared"] + ARCH + \
-          ["-I" + REFERENCE_SRC, "-I" + os.path.join(REFERENCE_SRC, "gpu"), "-o", REF_LIB] + srcs
+          ["-I" + REFERENCE_SRC, "-o", REF_LIB, harness]
     _run(cmd)
     return REF_LIB
 

@@ -153,6 +153,22 @@ int cudarl_update_batch(cudarl_ctx* ctx, int64_t n,
                         const float* rewards, const int32_t* next_x, const int32_t* next_y,
                         const uint8_t* dones);
 
+/* No counterpart in the reference.  The same batched TD update for callers that cannot allocate
+ * device memory at call time (a real-time loop that must not block in the allocator, a plug-in whose
+ * host framework owns the device heap, a process at its memory cap): nothing in this call allocates
+ * or frees.  All arrays are DEVICE pointers owned by the caller -- d_q is the table in the layout
+ * (y*width + x)*4 + a (16-byte aligned), updated in place; the transition arrays hold n elements.
+ * The kernels' working memory is one fixed static device array inside the library, which limits n to
+ * CUDARL_STATIC_MAX_BATCH (larger n returns -5 and launches nothing).  Every call on a GPU shares
+ * that array: calls that could overlap on the GPU must be serialised by the caller.  The first call
+ * on each device looks up the array's device address; make that call outside stream capture.
+ * Asynchronous on `stream` (a cudaStream_t, NULL = default stream); out-of-range transitions are skipped. */
+#define CUDARL_STATIC_MAX_BATCH 65536
+int cudarl_update_batch_static(float* d_q, int32_t width, int32_t height, int64_t n,
+                               const int32_t* d_state_x, const int32_t* d_state_y, const int32_t* d_actions,
+                               const float* d_rewards, const int32_t* d_next_x, const int32_t* d_next_y,
+                               const uint8_t* d_dones, float lr, float gamma, int32_t legacy_clamp, void* stream);
+
 /* Environment::getAgentX/getAgentY (src/environment.h:27-28) for all environments, plus the
  * per-episode step counters.  Any pointer may be NULL. */
 int cudarl_get_state(cudarl_ctx* ctx, int32_t* x, int32_t* y, int32_t* t);
