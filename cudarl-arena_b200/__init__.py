@@ -54,7 +54,7 @@ class Config(C.Structure):
 
 class Stats(C.Structure):
     _fields_ = [("steps", C.c_int64), ("env_steps", C.c_int64), ("episodes", C.c_int64), ("goals", C.c_int64),
-                ("timeouts", C.c_int64), ("conflicts", C.c_int64), ("long_chains", C.c_int64),
+                ("timeouts", C.c_int64), ("conflicts", C.c_int64), ("long_chains", C.c_int64), ("chained", C.c_int64),
                 ("reward_sum", C.c_double), ("epsilon", C.c_float), ("device_error", C.c_int32)]
 
 

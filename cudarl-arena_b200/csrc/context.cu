@@ -72,7 +72,12 @@ struct cudarl_ctx {
     std::string err;
     std::vector<uint8_t> cells;           // host copy of the cell classes
     // device buffers
-    void *dQ = nullptr, *dci = nullptr, *dx = nullptr, *dy = nullptr, *dt = nullptr, *dreward = nullptr, *ddone = nullptr;
+    void *dQ = nullptr, *dci = nullptr, *dreward = nullptr, *ddone = nullptr;
+    void *dstate[2][4] = {{nullptr, nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr, nullptr}};   // x, y, t, id: two copies (sort / export target)
+    void *dsortcnt = nullptr, *dsortblk = nullptr, *dactive = nullptr;
+    int cur = 0;                          // which copy of the state is live
+    bool slots_identity = true;           // id[k] == k
+    int64_t sort_every = 16, since_sort = 0;
     void *dent = nullptr, *dctl = nullptr, *deps = nullptr;
     void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
     void *ddense = nullptr;               // S float4: table in the caller's layout / allreduce buffer
@@ -83,6 +88,8 @@ struct cudarl_ctx {
     float eps_fixed_cached = -1.0f; bool eps_fixed_valid = false;
     // host mirror of schedule state
     int64_t h_step = 0;
+    int eps_mode = 0;                     // 0 one fixed value, 1 table indexed by step of the call, 2 per-episode (device index)
+    float eps_used = 0.0f;
     double eps_running = 1.0;
     int64_t eval_calls = 0;
     bool occ_valid = false, trace = false;
@@ -167,13 +174,40 @@ int build_cells(cudarl_ctx* c, std::vector<uint8_t>& cells, uint32_t& start_cell
     return 0;
 }
 
+void bind_state(cudarl_ctx* c) {
+    Params& p = c->p; const int a = c->cur, b = 1 - c->cur;
+    p.x = (int*)c->dstate[a][0]; p.y = (int*)c->dstate[a][1]; p.t = (int*)c->dstate[a][2]; p.id = (unsigned*)c->dstate[a][3];
+    p.x2 = (int*)c->dstate[b][0]; p.y2 = (int*)c->dstate[b][1]; p.t2 = (int*)c->dstate[b][2]; p.id2 = (unsigned*)c->dstate[b][3];
+}
+
 int upload_cells(cudarl_ctx* c) {
-    const size_t S = c->p.S, pad = (S + 15) / 16 * 16;
-    std::vector<uint8_t> b(pad, 0);
-    for (size_t s = 0; s < S; ++s) b[s] = c->cells[s] == 1 ? CI_OBST : (c->cells[s] == 2 ? CI_GOAL : 0);
-    CK(cudaMemcpyAsync(c->dci, b.data(), pad, cudaMemcpyHostToDevice, c->st));
+    const size_t S = c->p.S, pad = (S + 7) / 8 * 8;
+    std::vector<uint16_t> b(pad, 0);
+    for (size_t s = 0; s < S; ++s) b[s] = c->cells[s] == 1 ? CW_OBST : (c->cells[s] == 2 ? CW_GOAL : 0);
+    CK(cudaMemcpyAsync(c->dci, b.data(), pad * 2, cudaMemcpyHostToDevice, c->st));
     CK(cudaStreamSynchronize(c->st));
     c->occ_valid = false;
+    return 0;
+}
+
+// Re-order the slots by cell (counting sort into the other copy of the state, then swap).
+int sort_slots(cudarl_ctx* c) {
+    if (c->p.N < 2048) return 0;                   // nothing to gain for a handful of environments
+    launch_sort_by_cell(c->p, c->st);
+    CK(cudaGetLastError());
+    c->cur = 1 - c->cur; bind_state(c);
+    c->slots_identity = false; c->since_sort = 0;
+    return 0;
+}
+
+// Bring the state back to environment order (slot k = environment k), e.g. before the caller overwrites it.
+int normalize_slots(cudarl_ctx* c) {
+    if (c->slots_identity) return 0;
+    launch_export_state(c->p, c->st);
+    c->cur = 1 - c->cur; bind_state(c);
+    launch_identity_ids(c->p, c->st);
+    CK(cudaGetLastError());
+    c->slots_identity = true;
     return 0;
 }
 
@@ -198,14 +232,16 @@ int ensure_entry_capacity(cudarl_ctx* c, size_t cap) {
 // both resident while the state arrays and Q rows stream through.
 int alloc_hot(cudarl_ctx* c) {
     const size_t S = c->p.S, N = c->p.N ? c->p.N : 1;
-    const size_t ci_bytes = (S + 255) / 256 * 256;
+    const size_t ci_bytes = (2 * S + 255) / 256 * 256;      // one 16-bit word per cell
     size_t slots = pow2ceil(N); if (slots < (1u << 16)) slots = 1u << 16; if (slots > (1u << 24)) slots = 1u << 24;
     unsigned lg = 0; while ((1ull << lg) < slots) ++lg;
     const size_t total = ci_bytes + slots * sizeof(unsigned);
     CK(cudaMalloc(&c->dci, total));
     CK(cudaMemsetAsync(c->dci, 0, total, c->st));
-    c->p.ci = (unsigned char*)c->dci;
-    c->p.mailbox = (unsigned*)((char*)c->dci + ci_bytes); c->p.mb_shift = 32u - lg; c->p.mb_slots = (unsigned)slots;
+    c->p.cw = (unsigned short*)c->dci;
+    c->p.mailbox = (unsigned*)((char*)c->dci + ci_bytes); c->p.mb_slots = (unsigned)slots; (void)lg;
+    CK(cudaMalloc(&c->dactive, slots * sizeof(unsigned)));
+    c->p.active = (unsigned*)c->dactive;
     // L2 persistence (per context, released with it): best effort, a refusal is not an error.
     int dev = c->cfg.device, max_persist = 0, max_window = 0;
     cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev);
@@ -230,6 +266,8 @@ int alloc_hot(cudarl_ctx* c) {
 
 int ensure_occupancy(cudarl_ctx* c) {
     if (c->occ_valid) return 0;
+    { int rs = sort_slots(c); if (rs) return rs; }
+    c->p.step = (unsigned long long)c->h_step;
     launch_rebuild_occupancy(c->p, c->st);
     CK(cudaGetLastError());
     c->occ_valid = true;
@@ -308,8 +346,13 @@ int run_steps(cudarl_ctx* c, int64_t n) {
             if (c->kev_used + 3 > c->kev.size()) { int rc = drain_kernel_events(c); if (rc) return rc; }
             a = c->kev[c->kev_used]; b = c->kev[c->kev_used + 1]; d = c->kev[c->kev_used + 2]; c->kev_used += 3;
         }
+        if (c->sort_every > 0 && c->since_sort >= c->sort_every) { int rs = sort_slots(c); if (rs) return rs; }
+        c->p.step = (unsigned long long)c->h_step;
+        c->p.eps_idx = c->eps_mode == 1 ? (unsigned)k : 0u;
+        c->p.eps_from_ctl = c->eps_mode == 2 ? 1 : 0;
+        if (c->eps_mode != 2 && c->h_eps) c->eps_used = c->h_eps[c->p.eps_idx];
         launch_train_step(c->p, c->trace, c->st, a, b, d);
-        c->h_step += 1;
+        c->h_step += 1; c->since_sort += 1;
         if (c->cfg.sync_every > 0 && c->comm && (c->h_step % c->cfg.sync_every) == 0) { int rc = average_now(c); if (rc) return rc; }
     }
     CK(cudaGetLastError());
@@ -319,7 +362,8 @@ int run_steps(cudarl_ctx* c, int64_t n) {
 void free_all(cudarl_ctx* c) {
     if (c->st) cudaStreamSynchronize(c->st);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
-    void* bufs[] = {c->dQ, c->dci, c->dx, c->dy, c->dt, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
+    void* bufs[] = {c->dQ, c->dci, c->dstate[0][0], c->dstate[0][1], c->dstate[0][2], c->dstate[0][3], c->dstate[1][0], c->dstate[1][1],
+                    c->dstate[1][2], c->dstate[1][3], c->dsortcnt, c->dsortblk, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->ddense, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6]};
     for (void* b : bufs) if (b) cudaFree(b);
@@ -382,21 +426,29 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             const size_t S = p.S, N = p.N ? p.N : 1;
             CK(cudaMalloc(&c->dQ, S * 2 * sizeof(float4)));
             { int r0 = alloc_hot(c); if (r0) return r0; }
-            CK(cudaMalloc(&c->dx, N * 4)); CK(cudaMalloc(&c->dy, N * 4)); CK(cudaMalloc(&c->dt, N * 4));
+            for (int cp = 0; cp < 2; ++cp) for (int k = 0; k < 4; ++k) CK(cudaMalloc(&c->dstate[cp][k], N * 4));
+            p.sort_shift = 0; while (((S - 1) >> p.sort_shift) + 1 > 8 * N && ((S - 1) >> p.sort_shift) + 1 > (1u << 16)) ++p.sort_shift;
+            p.nkeys = (unsigned)(((S - 1) >> p.sort_shift) + 1);
+            CK(cudaMalloc(&c->dsortcnt, ((size_t)p.nkeys + 1) * sizeof(unsigned)));
+            CK(cudaMalloc(&c->dsortblk, ((size_t)p.nkeys / 4096 + 2) * sizeof(unsigned)));
             CK(cudaMalloc(&c->dctl, sizeof(Ctl)));
             CK(cudaMemsetAsync(c->dctl, 0, sizeof(Ctl), c->st));
-            p.Q = (float4*)c->dQ; p.x = (int*)c->dx; p.y = (int*)c->dy; p.t = (int*)c->dt;
+            p.Q = (float4*)c->dQ; bind_state(c); p.sort_cnt = (unsigned*)c->dsortcnt; p.sort_blk = (unsigned*)c->dsortblk;
             p.ctl = (Ctl*)c->dctl;
             int r2 = ensure_entry_capacity(c, N); if (r2) return r2;
             r2 = upload_cells(c); if (r2) return r2;
             launch_q_init(p, f->q_init_kind, f->q_init_scale, c->st);
             float e0 = (float)f->eps0; r2 = upload_eps(c, &e0, 1); if (r2) return r2;
             k_ctl_eps<<<1, 1, 0, c->st>>>(p.ctl, 0u, 1u, 0ull);
+            launch_identity_ids(p, c->st);
             launch_reset_all(p, c->st);
             CK(cudaGetLastError());
             CK(cudaStreamSynchronize(c->st));
             return 0;
         };
+        c->sort_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 16);
+        if (const char* ev = getenv("CUDARL_SORT_EVERY")) c->sort_every = atoll(ev);
+        if (const char* ev = getenv("CUDARL_DBG")) c->p.dbg = atoi(ev);
         rc = body();
     } while (0);
     if (rc) { g_err = c->err; free_all(c); delete c; return rc; }
@@ -419,6 +471,7 @@ int cudarl_synchronize(cudarl_ctx* c) { if (!c) return -1; CK(cudaStreamSynchron
 int cudarl_reset_all(cudarl_ctx* c) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));
+    c->p.step = (unsigned long long)c->h_step;
     launch_reset_all(c->p, c->st);
     CK(cudaGetLastError());
     c->occ_valid = false;
@@ -472,6 +525,7 @@ int cudarl_train_steps(cudarl_ctx* c, int64_t n) {
             k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 0u, 1u, 0ull);
             c->eps_fixed_valid = true;
         }
+        c->eps_mode = 0;
     } else if (f.eps_kind == CUDARL_EPS_MULT_PER_STEP || f.eps_kind == CUDARL_EPS_LINEAR) {
         std::vector<float> tab((size_t)n);
         for (int64_t k = 0; k < n; ++k) {
@@ -484,6 +538,7 @@ int cudarl_train_steps(cudarl_ctx* c, int64_t n) {
         }
         rc = upload_eps(c, tab.data(), (size_t)n); if (rc) return rc;
         k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 1u, (unsigned)n, 0ull);
+        c->eps_mode = 1;
     } else {  // per episode: index = episodes finished / environments, resolved on the device every step
         Ctl h; CK(cudaMemcpyAsync(&h, c->dctl, sizeof(Ctl), cudaMemcpyDeviceToHost, c->st));
         CK(cudaStreamSynchronize(c->st));
@@ -494,6 +549,7 @@ int cudarl_train_steps(cudarl_ctx* c, int64_t n) {
         for (int64_t k = 0; k <= n; ++k) { tab[k] = (float)e; e *= (double)f.eps_decay; }
         rc = upload_eps(c, tab.data(), (size_t)n + 1); if (rc) return rc;
         k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 2u, (unsigned)(n + 1), k0);
+        c->eps_mode = 2;
     }
     return run_steps(c, n);
 }
@@ -505,6 +561,7 @@ int cudarl_train_steps_eps(cudarl_ctx* c, int64_t n, const float* eps_host) {
     int rc = ensure_occupancy(c); if (rc) return rc;
     rc = upload_eps(c, eps_host, (size_t)n); if (rc) return rc;
     k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 1u, (unsigned)n, 0ull);
+    c->eps_mode = 1;
     return run_steps(c, n);
 }
 
@@ -566,6 +623,7 @@ int cudarl_update_batch(cudarl_ctx* c, int64_t n, const int32_t* sx, const int32
     }
     const void* src[7] = {sx, sy, a, r, nx, ny, dn};
     for (int k = 0; k < 7; ++k) CK(cudaMemcpyAsync(c->dub[k], src[k], (size_t)n * (k == 6 ? 1 : 4), cudaMemcpyHostToDevice, c->st));
+    c->p.step = (unsigned long long)c->h_step;
     launch_update_batch(c->p, (unsigned)n, (const int*)c->dub[0], (const int*)c->dub[1], (const int*)c->dub[2], (const float*)c->dub[3],
                         (const int*)c->dub[4], (const int*)c->dub[5], (const unsigned char*)c->dub[6], c->st);
     CK(cudaGetLastError());
@@ -577,9 +635,12 @@ int cudarl_get_state(cudarl_ctx* c, int32_t* x, int32_t* y, int32_t* t) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));
     const size_t b = (size_t)c->p.N * 4;
-    if (x) CK(cudaMemcpyAsync(x, c->dx, b, cudaMemcpyDeviceToHost, c->st));
-    if (y) CK(cudaMemcpyAsync(y, c->dy, b, cudaMemcpyDeviceToHost, c->st));
-    if (t) CK(cudaMemcpyAsync(t, c->dt, b, cudaMemcpyDeviceToHost, c->st));
+    // state lives in slot order; the export kernel writes it in environment order into the spare copy
+    const void *sx = c->p.x, *sy = c->p.y, *st = c->p.t;
+    if (!c->slots_identity) { launch_export_state(c->p, c->st); CK(cudaGetLastError()); sx = c->p.x2; sy = c->p.y2; st = c->p.t2; }
+    if (x) CK(cudaMemcpyAsync(x, sx, b, cudaMemcpyDeviceToHost, c->st));
+    if (y) CK(cudaMemcpyAsync(y, sy, b, cudaMemcpyDeviceToHost, c->st));
+    if (t) CK(cudaMemcpyAsync(t, st, b, cudaMemcpyDeviceToHost, c->st));
     CK(cudaStreamSynchronize(c->st));
     return 0;
 }
@@ -590,9 +651,10 @@ int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const in
     if (x) for (size_t i = 0; i < N; ++i) if (x[i] < 0 || x[i] >= c->p.W) return fail(c, -3, "Invalid state");
     if (y) for (size_t i = 0; i < N; ++i) if (y[i] < 0 || y[i] >= c->p.H) return fail(c, -3, "Invalid state");
     CK(cudaSetDevice(c->cfg.device));
-    if (x) CK(cudaMemcpyAsync(c->dx, x, N * 4, cudaMemcpyHostToDevice, c->st));
-    if (y) CK(cudaMemcpyAsync(c->dy, y, N * 4, cudaMemcpyHostToDevice, c->st));
-    if (t) CK(cudaMemcpyAsync(c->dt, t, N * 4, cudaMemcpyHostToDevice, c->st));
+    { int rn = normalize_slots(c); if (rn) return rn; }
+    if (x) CK(cudaMemcpyAsync(c->p.x, x, N * 4, cudaMemcpyHostToDevice, c->st));
+    if (y) CK(cudaMemcpyAsync(c->p.y, y, N * 4, cudaMemcpyHostToDevice, c->st));
+    if (t) CK(cudaMemcpyAsync(c->p.t, t, N * 4, cudaMemcpyHostToDevice, c->st));
     CK(cudaStreamSynchronize(c->st));
     c->occ_valid = false;
     return 0;
@@ -635,7 +697,7 @@ static int set_cell(cudarl_ctx* c, int32_t x, int32_t y, unsigned cls, bool sing
         launch_cell_set(c->p, 0, 0, 1, c->st);
     }
     c->cells[cell] = (uint8_t)cls;
-    launch_cell_set(c->p, cell, cls == 1 ? CI_OBST : (cls == 2 ? CI_GOAL : 0u), 0, c->st);
+    launch_cell_set(c->p, cell, cls == 1 ? CW_OBST : (cls == 2 ? CW_GOAL : 0u), 0, c->st);
     CK(cudaGetLastError());
     uint32_t fb = 0xFFFFFFFFu;
     for (uint32_t s = 0; s < c->p.S; ++s) if (c->cells[s] == 0) { fb = s; break; }
@@ -658,11 +720,11 @@ int cudarl_get_stats(cudarl_ctx* c, cudarl_stats* out) {
     Ctl h; CK(cudaMemcpyAsync(&h, c->dctl, sizeof(Ctl), cudaMemcpyDeviceToHost, c->st));
     CK(cudaStreamSynchronize(c->st));
     std::memset(out, 0, sizeof(*out));
-    out->steps = (int64_t)h.step; out->env_steps = (int64_t)h.step * (int64_t)c->p.N;
+    out->steps = c->h_step; out->env_steps = c->h_step * (int64_t)c->p.N;
     out->episodes = (int64_t)h.episodes; out->goals = (int64_t)h.goals; out->timeouts = (int64_t)h.timeouts;
-    out->conflicts = (int64_t)h.conflicts; out->long_chains = (int64_t)h.long_chains;
+    out->conflicts = (int64_t)h.conflicts; out->long_chains = (int64_t)h.long_chains; out->chained = (int64_t)h.general;
     out->reward_sum = (double)out->goals * 1.0 - 0.01 * (double)(out->env_steps - out->goals);
-    out->epsilon = h.eps_used; out->device_error = (int32_t)h.error;
+    out->epsilon = c->eps_mode == 2 ? h.eps_used : c->eps_used; out->device_error = (int32_t)h.error;
     return 0;
 }
 

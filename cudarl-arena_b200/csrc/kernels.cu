@@ -1,25 +1,31 @@
 // kernels.cu -- hand-written sm_100a kernels of the batched grid-world + tabular Q-learning path.
 //
 // Data layout in HBM (per context = per GPU):
-//   x[N], y[N], t[N]   int32 structure-of-arrays environment state, read/written fully coalesced;
-//   Q                  one 32-byte sector per grid cell: two float4 halves.  Half `PAR(cell)` holds
-//                      Q_t[cell][0..3] (one vector load = the whole action row), the other half is
-//                      where Q_{t+1} of that cell is written.  Readers of step t therefore never see
-//                      a write of step t, and a 16-byte row costs the same DRAM sector as 32 bytes;
-//   ci                 one info byte per cell (obstacle, goal, row parity, occupancy of this and
-//                      of the next step), small enough to live in L2;
-//   ent / mailbox      collision entries and hashed chain heads for cells that hold several
-//                      environments in one step.
+//   x,y,t,id [N]   int32 structure-of-arrays environment state in SLOT order (slot k holds environment
+//                  id[k]); read/written fully coalesced.  Every few steps the slots are re-ordered by
+//                  cell (counting sort), so neighbouring threads touch neighbouring table rows and the
+//                  environments that share a cell sit in the same warp;
+//   Q              one 32-byte sector per grid cell: two float4 halves.  Half PAR(cell) holds
+//                  Q_t[cell][0..3] (one vector load = the whole action row), the other half is where
+//                  Q_{t+1} of that cell is written, so readers of step t never see a write of step t;
+//   cw             one 16-bit word per cell: obstacle, goal, row parity and two 4-bit occupant counters
+//                  (this step / next step, saturating), small enough to stay in L2;
+//   ent / mailbox  collision entries and chain heads for cells whose occupants are spread over
+//                  several warps.
 //
 // One batched step = two launches:
-//   train_main  one thread per environment: epsilon-greedy from a Philox4x32-10 stream keyed by
-//               (seed, global env, step) -> move with obstacle/goal lookup -> TD error against Q_t
-//               -> if the environment is alone on its cell, write the cell's Q_{t+1} row directly;
-//               otherwise append (cell, action, env, td_error) to the collision list -> auto-reset
-//               -> announce its next cell in the occupancy bits of the next step.
-//   train_fix   folds the collision entries of each shared cell in ascending environment index
-//               (fp32 fma chain, no float atomics), flips the row parity of every occupied cell,
-//               shifts next-step occupancy into place and advances the step / epsilon index.
+//   train_main  one thread per slot: epsilon-greedy from a Philox4x32-10 stream keyed by
+//               (seed, global env, step) -> move with obstacle/goal lookup -> TD error against Q_t.
+//               The warp groups its lanes by cell (match.any).  If the cell's occupant count equals
+//               the group size, every occupant is in this warp: the group folds its TD errors in
+//               ascending environment id with shuffles and its leader writes the cell's Q_{t+1} row.
+//               Otherwise the lanes append (cell, action, env, td_error) entries, linked inside the
+//               group, and the leader hooks the sub-chain into the cell's mailbox chain with one
+//               atomicExch.  Then auto-reset, and one saturating count per (warp, next cell) into the
+//               next step's counter.
+//   train_fix   folds the chained entries of each cell in ascending environment id (fp32 fma chain, no
+//               float atomics), flips the row parity of every occupied cell, clears the consumed
+//               counter plane and advances the step / epsilon index.
 //
 // Reference semantics (paths relative to the CudaRL-Arena project root):
 //   step        src/environment.cu:17-48, obstacle test src/kernels.cu:29-44, goal src/kernels.cu:56-59
@@ -31,6 +37,8 @@
 #include <cstdio>
 
 namespace cudarl {
+
+constexpr unsigned FULL = 0xFFFFFFFFu;
 
 // ------------------------------------------------------------------------------------------------
 // Philox4x32-10, counter-based: no generator state is stored anywhere.
@@ -54,7 +62,44 @@ constexpr unsigned TAG_START = 0x53545254u, TAG_QINIT = 0x51494E49u, TAG_POLICY 
 
 __device__ __forceinline__ float u01(unsigned w) { return (float)(w >> 8) * 5.9604644775390625e-08f; }
 
-__device__ __forceinline__ unsigned ci_load(const unsigned char* ci, unsigned cell) { return ci[cell]; }
+__device__ __forceinline__ unsigned cw_load(const unsigned short* cw, unsigned cell) { return cw[cell]; }
+__device__ __forceinline__ unsigned cnt_shift(unsigned long long step) { return (step & 1ull) ? CW_CNT_SHIFT1 : CW_CNT_SHIFT0; }
+__device__ __forceinline__ void flip_parity(const Params& p, unsigned cell) {
+    atomicXor(reinterpret_cast<unsigned*>(p.cw) + (cell >> 1), CW_PAR << ((cell & 1u) * 16u));
+}
+
+// Add `g` occupants to the 4-bit counter (field at `shift`) of `cell`, saturating at 15.
+__device__ __forceinline__ void count_add(const Params& p, unsigned cell, unsigned shift, unsigned g) {
+    unsigned* w = reinterpret_cast<unsigned*>(p.cw) + (cell >> 1);
+    const unsigned sh = shift + (cell & 1u) * 16u;
+    unsigned old = *reinterpret_cast<volatile unsigned*>(w);
+    for (int it = 0; it < 100000; ++it) {                 // lock-free; the bound only guards against a broken word
+        unsigned f = (old >> sh) & CW_CNT_MAX;
+        unsigned nf = f + g; if (nf > CW_CNT_MAX) nf = CW_CNT_MAX;
+        if (nf == f) return;
+        unsigned seen = atomicCAS(w, old, (old & ~(CW_CNT_MAX << sh)) | (nf << sh));
+        if (seen == old) return;
+        old = seen;
+    }
+    atomicOr(&p.ctl->error, ERR_CAS_LIMIT);
+}
+
+// Same for both cells of a 32-bit pair at once (even cell gets g0, odd cell g1).
+__device__ __forceinline__ void count_add2(const Params& p, unsigned pair, unsigned shift, unsigned g0, unsigned g1) {
+    unsigned* w = reinterpret_cast<unsigned*>(p.cw) + pair;
+    unsigned old = *reinterpret_cast<volatile unsigned*>(w);
+    for (int it = 0; it < 100000; ++it) {
+        unsigned f0 = (old >> shift) & CW_CNT_MAX, f1 = (old >> (shift + 16u)) & CW_CNT_MAX;
+        unsigned n0 = f0 + g0; if (n0 > CW_CNT_MAX) n0 = CW_CNT_MAX;
+        unsigned n1 = f1 + g1; if (n1 > CW_CNT_MAX) n1 = CW_CNT_MAX;
+        if (n0 == f0 && n1 == f1) return;
+        unsigned upd = (old & ~((CW_CNT_MAX << shift) | (CW_CNT_MAX << (shift + 16u)))) | (n0 << shift) | (n1 << (shift + 16u));
+        unsigned seen = atomicCAS(w, old, upd);
+        if (seen == old) return;
+        old = seen;
+    }
+    atomicOr(&p.ctl->error, ERR_CAS_LIMIT);
+}
 
 // Start cell of an episode.  CENTRE/FIXED: the configured cell (reference: src/environment.cu:9-10).
 // RANDOM: first free non-goal cell among 64 seeded candidates, else the precomputed fallback cell.
@@ -63,10 +108,10 @@ __device__ __forceinline__ unsigned sample_start(const Params& p, unsigned gi, u
     for (unsigned k = 0; k < 16; ++k) {
         U4 w = philox4x32_10(gi, k, (unsigned)nonce, (unsigned)(nonce >> 32), p.k0, p.k1 ^ tag);
         unsigned c;
-        c = __umulhi(w.x, p.S); if (!(ci_load(p.ci, c) & (CI_OBST | CI_GOAL))) return c;
-        c = __umulhi(w.y, p.S); if (!(ci_load(p.ci, c) & (CI_OBST | CI_GOAL))) return c;
-        c = __umulhi(w.z, p.S); if (!(ci_load(p.ci, c) & (CI_OBST | CI_GOAL))) return c;
-        c = __umulhi(w.w, p.S); if (!(ci_load(p.ci, c) & (CI_OBST | CI_GOAL))) return c;
+        c = __umulhi(w.x, p.S); if (!(cw_load(p.cw, c) & (CW_OBST | CW_GOAL))) return c;
+        c = __umulhi(w.y, p.S); if (!(cw_load(p.cw, c) & (CW_OBST | CW_GOAL))) return c;
+        c = __umulhi(w.z, p.S); if (!(cw_load(p.cw, c) & (CW_OBST | CW_GOAL))) return c;
+        c = __umulhi(w.w, p.S); if (!(cw_load(p.cw, c) & (CW_OBST | CW_GOAL))) return c;
     }
     return p.fallback_start;
 }
@@ -86,41 +131,35 @@ __device__ __forceinline__ float max4(float4 r) {
 __device__ __forceinline__ float pick(float4 r, int a) { return a == 0 ? r.x : a == 1 ? r.y : a == 2 ? r.z : r.w; }
 __device__ __forceinline__ void fold(float4& r, int a, float lr, float d) {
     // Q[s,a] <- fma(lr, d, Q[s,a]): what nvcc makes of `q += lr * (target - q)` (src/kernels.cu:114)
-    if (a == 0) r.x = __fmaf_rn(lr, d, r.x); else if (a == 1) r.y = __fmaf_rn(lr, d, r.y);
-    else if (a == 2) r.z = __fmaf_rn(lr, d, r.z); else r.w = __fmaf_rn(lr, d, r.w);
+    const float v = __fmaf_rn(lr, d, pick(r, a));
+    r.x = a == 0 ? v : r.x; r.y = a == 1 ? v : r.y; r.z = a == 2 ? v : r.z; r.w = a == 3 ? v : r.w;
 }
 
-// Move from (x,y) by `action`; returns the new cell and its info byte.
-__device__ __forceinline__ unsigned move_cell(const Params& p, int x, int y, unsigned s, unsigned ci_s, int action,
-                                              unsigned& ci_new) {
+// Move from (x,y) by `action`; returns the new cell and its cell word.
+__device__ __forceinline__ unsigned move_cell(const Params& p, int x, int y, unsigned s, unsigned cw_s, int action,
+                                              unsigned& cw_new) {
     int dx = (action == 1) - (action == 3), dy = (action == 2) - (action == 0);
     int nx = x + dx, ny = y + dy;
     bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
     unsigned tgt = inb ? (unsigned)ny * (unsigned)p.W + (unsigned)nx : s;
-    unsigned ct = (tgt != s) ? ci_load(p.ci, tgt) : ci_s;
-    bool moved = (tgt != s) && !(ct & CI_OBST);
-    ci_new = moved ? ct : ci_s;
+    unsigned ct = (tgt != s) ? cw_load(p.cw, tgt) : cw_s;
+    bool moved = (tgt != s) && !(ct & CW_OBST);
+    cw_new = moved ? ct : cw_s;
     return moved ? tgt : s;
 }
 
-__device__ __forceinline__ void announce(unsigned char* ci, unsigned cell, unsigned occ_bit, unsigned multi_bit) {
-    unsigned* w = reinterpret_cast<unsigned*>(ci) + (cell >> 2);
-    unsigned sh = (cell & 3u) * 8u;
-    unsigned old = atomicOr(w, occ_bit << sh);
-    if (old & (occ_bit << sh)) atomicOr(w, multi_bit << sh);
-}
-
-__device__ __forceinline__ unsigned mb_slot(const Params& p, unsigned cell) { return (cell * 0x9E3779B1u) >> p.mb_shift; }
+// chain heads are indexed by the low bits of the cell: neighbouring cells -> neighbouring slots
+__device__ __forceinline__ unsigned mb_slot(const Params& p, unsigned cell) { return cell & (p.mb_slots - 1u); }
 
 // ------------------------------------------------------------------------------------------------
-// Occupancy rebuild (after reset / caller-driven state changes): clear the dynamic bits, then every
-// environment announces its current cell in the CURRENT-step bits.
+// Occupancy rebuild (after reset / caller-driven state changes): clear both counters, then every
+// environment counts itself into the counter of the CURRENT step.
 __global__ void k_occ_clear(Params p) {
-    unsigned n16 = (p.S + 15u) / 16u;
-    uint4* w = reinterpret_cast<uint4*>(p.ci);
+    unsigned n16 = (2u * p.S + 15u) / 16u;
+    uint4* w = reinterpret_cast<uint4*>(p.cw);
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += gridDim.x * blockDim.x) {
         uint4 v = w[i];
-        const unsigned keep = 0x07070707u;
+        const unsigned keep = 0x000F000Fu;
         v.x &= keep; v.y &= keep; v.z &= keep; v.w &= keep;
         w[i] = v;
     }
@@ -129,82 +168,266 @@ __global__ void k_occ_announce(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
     unsigned s = (unsigned)p.y[i] * (unsigned)p.W + (unsigned)p.x[i];
-    announce(p.ci, s, CI_OCC, CI_MULTI);
+    count_add(p, s, cnt_shift(p.step), 1u);
 }
 
 __global__ void k_reset_all(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
-    unsigned c = sample_start(p, p.env_offset + i, p.ctl->step, TAG_START);
+    unsigned e = p.id[i];
+    unsigned c = sample_start(p, p.env_offset + e, p.step, TAG_START);
     p.x[i] = (int)(c % (unsigned)p.W); p.y[i] = (int)(c / (unsigned)p.W); p.t[i] = 0;
-    if (p.reward) { p.reward[i] = 0.0f; p.done[i] = 0; }
+    if (p.reward) { p.reward[e] = 0.0f; p.done[e] = 0; }
 }
 
 // ------------------------------------------------------------------------------------------------
-// The fused step: one thread per environment.
+// Slot order.  Counting sort of the slots by cell: count, exclusive scan over the cells, scatter.
+// The order inside one cell is whatever the atomics give; nothing depends on it (folds go by id).
+// sort key: the cell itself (shift 0) so that environments sharing a cell occupy consecutive slots, which
+// is what the warp-level grouping below looks for; coarser keys only when cells vastly outnumber environments
+__device__ __forceinline__ unsigned sort_key(const Params& p, int x, int y) { return ((unsigned)y * (unsigned)p.W + (unsigned)x) >> p.sort_shift; }
+
+// Maximal run of consecutive lanes holding the same value `v` as mine: returns its lane mask.
+__device__ __forceinline__ unsigned run_mask(unsigned v, unsigned lane) {
+    const unsigned up = __shfl_up_sync(FULL, v, 1);
+    const unsigned heads = __ballot_sync(FULL, lane == 0u || v != up);       // lanes that start a run
+    const unsigned at_or_below = heads & ((2u << lane) - 1u);
+    const unsigned start = 31u - __clz(at_or_below);
+    const unsigned above = heads & ~((2u << lane) - 1u);
+    const unsigned end = above ? (unsigned)__ffs(above) - 2u : 31u;           // last lane of my run
+    return ((end == 31u) ? FULL : ((1u << (end + 1u)) - 1u)) & ~((1u << start) - 1u);
+}
+
+__global__ void k_ids_identity(Params p) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < p.N) p.id[i] = i;
+}
+__global__ void k_sort_zero(Params p) {
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i <= p.nkeys; i += gridDim.x * blockDim.x) p.sort_cnt[i] = 0u;
+}
+__global__ void k_sort_count(Params p) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.N) return;
+    atomicAdd(p.sort_cnt + sort_key(p, p.x[i], p.y[i]), 1u);
+}
+constexpr unsigned SCAN_CHUNK = 4096;      // keys per block of the scan
+// phase 1: per-chunk totals; phase 2 (one block): exclusive scan of the totals; phase 3: exclusive scan inside chunks
+__global__ void __launch_bounds__(BLOCK) k_scan_totals(Params p) {
+    __shared__ unsigned s_sum[BLOCK / 32];
+    unsigned base = blockIdx.x * SCAN_CHUNK, acc = 0;
+    for (unsigned j = threadIdx.x; j < SCAN_CHUNK; j += BLOCK) { unsigned c = base + j; if (c < p.nkeys) acc += p.sort_cnt[c]; }
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(FULL, acc, o);
+    if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) { unsigned t = 0; for (int k = 0; k < BLOCK / 32; ++k) t += s_sum[k]; p.sort_blk[blockIdx.x] = t; }
+}
+__device__ __forceinline__ unsigned block_excl_scan(unsigned v, unsigned* s_warp) {   // exclusive prefix of v over the block
+    const unsigned lane = threadIdx.x & 31u, wid = threadIdx.x >> 5;
+    unsigned inc = v;
+    for (int o = 1; o < 32; o <<= 1) { unsigned t = __shfl_up_sync(FULL, inc, o); if (lane >= (unsigned)o) inc += t; }
+    if (lane == 31u) s_warp[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+        unsigned w = lane < blockDim.x / 32u ? s_warp[lane] : 0u, winc = w;
+        for (int o = 1; o < 32; o <<= 1) { unsigned t = __shfl_up_sync(FULL, winc, o); if (lane >= (unsigned)o) winc += t; }
+        if (lane < blockDim.x / 32u) s_warp[lane] = winc - w;
+    }
+    __syncthreads();
+    unsigned r = s_warp[wid] + inc - v;
+    __syncthreads();
+    return r;
+}
+__global__ void __launch_bounds__(1024) k_scan_blocks(Params p, unsigned nchunks) {
+    __shared__ unsigned s_warp[32];
+    __shared__ unsigned s_carry;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    for (unsigned base = 0; base < nchunks; base += 1024u) {
+        unsigned k = base + threadIdx.x;
+        unsigned v = k < nchunks ? p.sort_blk[k] : 0u;
+        unsigned ex = block_excl_scan(v, s_warp);
+        unsigned carry = s_carry;
+        if (k < nchunks) p.sort_blk[k] = carry + ex;
+        __syncthreads();
+        if (threadIdx.x == 1023u) s_carry = carry + ex + v;
+        __syncthreads();
+    }
+}
+__global__ void __launch_bounds__(BLOCK) k_scan_chunks(Params p) {
+    // 256 threads x 16 consecutive keys
+    __shared__ unsigned s_warp[32];
+    unsigned base = blockIdx.x * SCAN_CHUNK + threadIdx.x * 16u;
+    unsigned v[16], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { unsigned c = base + j; v[j] = c < p.nkeys ? p.sort_cnt[c] : 0u; sum += v[j]; }
+    unsigned run = p.sort_blk[blockIdx.x] + block_excl_scan(sum, s_warp);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { unsigned c = base + j; if (c < p.nkeys) p.sort_cnt[c] = run; run += v[j]; }
+}
+__global__ void k_sort_scatter(Params p) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.N) return;
+    int x = p.x[i], y = p.y[i];
+    unsigned pos = atomicAdd(p.sort_cnt + sort_key(p, x, y), 1u);   // offsets become cursors
+    p.x2[pos] = x; p.y2[pos] = y; p.t2[pos] = p.t[i]; p.id2[pos] = p.id[i];
+}
+__global__ void k_export_state(Params p) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.N) return;
+    unsigned e = p.id[i];
+    p.x2[e] = p.x[i]; p.y2[e] = p.y[i]; p.t2[e] = p.t[i];
+}
+
+// ------------------------------------------------------------------------------------------------
+// The fused step: one thread per slot.
 template <bool TRACE>
-__global__ void __launch_bounds__(BLOCK) k_train_main(Params p) {
-    __shared__ unsigned s_cnt, s_goals, s_timeouts;
-    if (threadIdx.x == 0) { s_cnt = 0; s_goals = 0; s_timeouts = 0; }
+__global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
+    __shared__ unsigned s_cnt, s_goals, s_timeouts, s_shared;
+    __shared__ int2 s_pair[BLOCK];
+    __shared__ unsigned s_act[BLOCK], s_nact, s_actbase;
+    if (threadIdx.x == 0) { s_cnt = 0; s_goals = 0; s_timeouts = 0; s_shared = 0; s_nact = 0; }
     __syncthreads();
     const unsigned i = blockIdx.x * BLOCK + threadIdx.x;
-    if (blockIdx.x == 0 && threadIdx.x == 0) p.ctl->scratch_cursor = 0;   // nobody reads it in this kernel
-    if (i < p.N) {
-        const unsigned long long g = p.ctl->step;
-        const float eps = p.eps_tab[p.ctl->eps_idx];
-        const int x = __ldcs(p.x + i), y = __ldcs(p.y + i), t = __ldcs(p.t + i);
-        const unsigned s = (unsigned)y * (unsigned)p.W + (unsigned)x;
-        const unsigned gi = p.env_offset + i;
-        const unsigned cs = ci_load(p.ci, s);
-        const unsigned par = (cs & CI_PAR) ? 1u : 0u;
-        float4 row = __ldcg(p.Q + 2u * s + par);
+    const unsigned lane = threadIdx.x & 31u;
+    const unsigned lt = (1u << lane) - 1u;                              // lanes below mine
+    if (blockIdx.x == 0 && threadIdx.x == 0) { p.ctl->scratch_cursor = 0; p.ctl->active_count[(p.step + 1ull) & 1ull] = 0; }   // nobody reads these in this kernel
+    const bool valid = i < p.N;
+    const unsigned long long g = p.step;
+    const unsigned shc = cnt_shift(g), shn = cnt_shift(g + 1ull);
+    const float eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx];
+    // ---- per-lane work (lanes past the end idle through it with harmless values) ----------------------
+    int x = 0, y = 0, t = 0, a = 0, nx = 0, ny = 0; unsigned e = 0, s = 0x80000000u | lane, s2 = 0, par = 0, cnt = 0;
+    float4 row = make_float4(0.f, 0.f, 0.f, 0.f); float d = 0.0f; bool done = false;
+    if (valid) {
+        x = __ldcs(p.x + i); y = __ldcs(p.y + i); t = __ldcs(p.t + i); e = __ldcs(p.id + i);
+        s = (unsigned)y * (unsigned)p.W + (unsigned)x;
+        const unsigned cs = cw_load(p.cw, s);
+        par = (cs & CW_PAR) ? 1u : 0u;
+        cnt = (cs >> shc) & CW_CNT_MAX;
+        row = __ldcg(p.Q + 2u * s + par);
         // epsilon-greedy
-        U4 w = philox4x32_10(gi, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
-        const int a = (u01(w.x) < eps) ? (int)(w.y & 3u) : argmax4(row);
+        U4 w = (p.dbg & 8) ? U4{e * 2654435761u, e, 0u, 0u} : philox4x32_10(p.env_offset + e, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
+        a = (u01(w.x) < eps) ? (int)(w.y & 3u) : argmax4(row);
         // environment transition
-        unsigned c2;
-        const unsigned s2 = move_cell(p, x, y, s, cs, a, c2);
-        const bool done = (c2 & CI_GOAL) != 0;
+        const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
+        nx = x + dx; ny = y + dy;
+        const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
+        const unsigned tgt = inb ? (unsigned)ny * (unsigned)p.W + (unsigned)nx : s;
+        const unsigned ct = inb ? cw_load(p.cw, tgt) : cs;
+        const bool moved = inb && !(ct & CW_OBST);
+        const unsigned c2 = moved ? ct : cs;
+        s2 = moved ? tgt : s; nx = moved ? nx : x; ny = moved ? ny : y;
+        done = (c2 & CW_GOAL) != 0;
         const float r = done ? 1.0f : -0.01f;
         float m = 0.0f;
         if (!done) {
-            float4 row2 = (s2 == s) ? row : __ldcg(p.Q + 2u * s2 + ((c2 & CI_PAR) ? 1u : 0u));
+            float4 row2 = moved ? __ldcg(p.Q + 2u * s2 + ((c2 & CW_PAR) ? 1u : 0u)) : row;
             m = max4(row2);
             if (p.legacy_clamp && m < 0.0f) m = 0.0f;
         }
-        const float target = __fmaf_rn(p.gamma, m, r);
-        const float d = __fsub_rn(target, pick(row, a));
-        if (!(cs & CI_MULTI)) {
-            fold(row, a, p.lr, d);
-            p.Q[2u * s + (par ^ 1u)] = row;          // Q_{t+1} row of a cell with a single occupant
-        } else {
-            unsigned rk = atomicAdd(&s_cnt, 1u);
-            unsigned pos = blockIdx.x * BLOCK + rk;  // entry slot inside this block's fixed segment
-            unsigned slot = mb_slot(p, s);
-            unsigned prev = atomicExch(p.mailbox + slot, pos + 1u);
-            p.ent[pos] = make_uint4((s << 3) | (par << 2) | (unsigned)a, i, __float_as_uint(d), prev);
+        d = __fsub_rn(__fmaf_rn(p.gamma, m, r), pick(row, a));
+        if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = r; p.tr_d[e] = done ? 1 : 0; }
+    }
+    // ---- TD update: consecutive lanes of the warp that stand on the same cell form a group -------------
+    const unsigned gmask = run_mask(s, lane);      // consecutive slots on the same cell (the slot order is by cell)
+    const unsigned gsize = __popc(gmask), gleader = __ffs(gmask) - 1u;
+    // every occupant of the cell is in this group <=> the cell's counter equals the group size
+    const bool complete = valid && cnt == gsize && gsize < CW_CNT_MAX;
+    {
+        // Fold the group's TD errors in ascending environment id.  Only full-warp collectives are used
+        // (collectives with a per-lane mask are several times slower on this part): every lane ranks its
+        // id inside its run with shuffles at growing distances, the (action, td_error) pairs are parked
+        // in shared memory at their rank, and the run's first lane folds them in that order.
+        const unsigned gend = gleader + gsize - 1u;
+        const unsigned maxlen = __reduce_max_sync(FULL, (complete && !(p.dbg & 1)) ? gsize : 0u);
+        unsigned rank = 0;
+        for (unsigned off = 1; off < maxlen; ++off) {
+            const unsigned eu = __shfl_up_sync(FULL, e, off), ed = __shfl_down_sync(FULL, e, off);
+            rank += (lane >= gleader + off && eu < e) ? 1u : 0u;
+            rank += (lane + off <= gend && ed < e) ? 1u : 0u;
         }
-        if (TRACE) { p.tr_a[i] = a; p.tr_r[i] = r; p.tr_d[i] = done ? 1 : 0; }
-        // episode bookkeeping + next-step occupancy
-        const bool timeout = p.max_steps > 0 && t + 1 >= p.max_steps;
-        int nx, ny, nt; unsigned sn;
+        const unsigned wbase = threadIdx.x & ~31u;
+        if (complete && gsize > 1u) s_pair[wbase + gleader + rank] = make_int2(a, __float_as_int(d));
+        __syncwarp();
+        if (complete && lane == gleader) {
+            if (gsize == 1u) fold(row, a, p.lr, d);
+            else for (unsigned k = 0; k < gsize; ++k) { const int2 pr = s_pair[wbase + gleader + k]; fold(row, pr.x, p.lr, __int_as_float(pr.y)); }
+            p.Q[2u * s + (par ^ 1u)] = row;                                   // Q_{t+1} row of the cell
+        }
+    }
+    {
+        // occupants in other warps too: entries, linked inside the group, hooked into the cell's chain
+        const bool gen = valid && !complete && !(p.dbg & 4);
+        const unsigned genmask = __ballot_sync(FULL, gen);
+        if (genmask) {
+            unsigned base = 0;
+            if (lane == __ffs(genmask) - 1u) base = atomicAdd(&s_cnt, __popc(genmask));
+            base = __shfl_sync(FULL, base, __ffs(genmask) - 1);
+            const unsigned pos = blockIdx.x * BLOCK + base + __popc(genmask & lt);
+            const unsigned higher = gmask & ~((2u << lane) - 1u);
+            const int nl = higher ? (int)(__ffs(higher) - 1u) : -1;
+            const unsigned pos_next = __shfl_sync(FULL, pos, nl >= 0 ? nl : (int)lane);
+            unsigned prev = 0u;
+            if (gen && lane == gleader) {
+                prev = atomicExch(p.mailbox + mb_slot(p, s), pos + 1u);
+                if (!prev) s_act[atomicAdd(&s_nact, 1u)] = mb_slot(p, s);    // first chain on this slot in this step
+            }
+            prev = __shfl_sync(FULL, prev, gleader);
+            if (gen) p.ent[pos] = make_uint4((s << 3) | (par << 2) | (unsigned)a, e, __float_as_uint(d), nl >= 0 ? pos_next + 1u : prev);
+        }
+    }
+    // ---- episode bookkeeping, next-step occupancy, state out ----------------------------------------------
+    unsigned sn = 0x80000000u | lane;
+    const bool timeout = valid && !done && p.max_steps > 0 && t + 1 >= p.max_steps;
+    if (valid) {
+        int nt = t + 1;
+        sn = s2;
         if (done || timeout) {
-            sn = sample_start(p, gi, g + 1ull, TAG_START);
+            sn = sample_start(p, p.env_offset + e, g + 1ull, TAG_START);
             nx = (int)(sn % (unsigned)p.W); ny = (int)(sn / (unsigned)p.W); nt = 0;
-            if (done) atomicAdd(&s_goals, 1u); else atomicAdd(&s_timeouts, 1u);
-        } else {
-            sn = s2; nx = (int)(s2 % (unsigned)p.W); ny = (int)(s2 / (unsigned)p.W); nt = t + 1;
         }
-        announce(p.ci, sn, CI_OCCN, CI_MULTIN);
         __stcs(p.x + i, nx); __stcs(p.y + i, ny); __stcs(p.t + i, nt);
     }
+    {
+        // neighbours whose next cells share a 32-bit cell-word pair announce together: one CAS per pair
+        const unsigned wmask = run_mask(sn >> 1, lane);
+        const unsigned odd = __ballot_sync(FULL, (sn & 1u) != 0u);
+        if (!(p.dbg & 2) && valid && lane == __ffs(wmask) - 1u) {
+            if (p.dbg & 16) atomicAdd(reinterpret_cast<unsigned*>(p.cw) + (sn >> 1), (__popc(wmask & ~odd) << shn) | (__popc(wmask & odd) << (shn + 16u)));
+            else count_add2(p, sn >> 1, shn, __popc(wmask & ~odd), __popc(wmask & odd));
+        }
+    }
+    {
+        const unsigned mg = __ballot_sync(FULL, valid && done), mt = __ballot_sync(FULL, timeout), ms = __ballot_sync(FULL, valid && cnt >= 2u);
+        if (lane == 0) {
+            if (mg) atomicAdd(&s_goals, __popc(mg));
+            if (mt) atomicAdd(&s_timeouts, __popc(mt));
+            if (ms) atomicAdd(&s_shared, __popc(ms));
+        }
+    }
     __syncthreads();
+    if (s_nact) {                                                     // publish this block's newly active slots
+        if (threadIdx.x == 0) s_actbase = atomicAdd(&p.ctl->active_count[p.step & 1ull], s_nact);
+        __syncthreads();
+        if (threadIdx.x < s_nact) p.active[s_actbase + threadIdx.x] = s_act[threadIdx.x];
+    }
     if (threadIdx.x == 0) {
-        if (s_cnt) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_cnt);
+        if (s_shared) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_shared);
+        if (s_cnt) atomicAdd(&p.ctl->general, (unsigned long long)s_cnt);
         if (s_goals) atomicAdd(&p.ctl->goals, (unsigned long long)s_goals);
         if (s_timeouts) atomicAdd(&p.ctl->timeouts, (unsigned long long)s_timeouts);
         if (s_goals + s_timeouts) atomicAdd(&p.ctl->episodes, (unsigned long long)(s_goals + s_timeouts));
     }
+}
+
+// Per-episode epsilon schedule: the table index follows the number of finished episodes, which only
+// the device knows.  One thread, launched after each step in that mode only.
+__global__ void k_eps_episode(Params p) {
+    Ctl* c = p.ctl;
+    c->eps_used = p.eps_tab[c->eps_idx];
+    unsigned long long kk = c->episodes / (unsigned long long)p.N;
+    unsigned long long rel = kk > c->eps_base_k ? kk - c->eps_base_k : 0ull;
+    c->eps_idx = (unsigned)(rel < (unsigned long long)(c->eps_len - 1u) ? rel : (unsigned long long)(c->eps_len - 1u));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -243,7 +466,7 @@ __device__ void apply_run(const Params& p, const unsigned long long* keys, const
         fold(row, (int)(wj & 3u), p.lr, vals[j]);
     }
     p.Q[2u * cell + (par ^ 1u)] = row;
-    if (FLIP) atomicXor(reinterpret_cast<unsigned*>(p.ci) + (cell >> 2), CI_PAR << ((cell & 3u) * 8u));
+    if (FLIP) flip_parity(p, cell);
 }
 
 constexpr unsigned LONG_SMEM = 1024;   // chain entries sorted in shared memory; longer chains use the global scratch
@@ -319,14 +542,15 @@ __device__ void process_medium(const Params& p, unsigned long long* keys, float*
     __syncwarp();
 }
 
-// Collision folding, one thread per mailbox slot.  A slot's chain holds every entry whose cell hashes
-// there; the thread that finds a non-empty slot owns the chain:
+// Collision folding, one thread per ACTIVE mailbox slot (the producers list every slot they were the
+// first to hook a chain into, so this kernel only visits slots that have work).  A slot's chain holds
+// every entry whose cell maps there; the thread that takes the slot owns the chain:
 //   <= 8 entries   gathered, ordered (sorting network) and folded in registers by that thread;
 //   <= 32 entries  staged in shared memory by that thread, ordered and folded by one warp;
 //   longer         walked by one thread, sorted by the whole block (shared memory up to 1024 entries,
 //                  the global scratch beyond that).
-// TRAIN = true : part of a train step -- also sweeps the info bytes (parity ^= occupied, next-step
-//                occupancy -> current) and, in the last block to finish, advances step and epsilon.
+// TRAIN = true : part of a train step -- also sweeps the cell words (parity ^= occupied, consumed
+//                counter cleared).
 // TRAIN = false: update_batch -- flips the row parity of every folded cell instead.
 template <bool TRAIN>
 __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
@@ -336,11 +560,13 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
     __shared__ unsigned s_long[BLOCK];
     __shared__ unsigned s_medlen[MED_CHUNKS];
     __shared__ unsigned s_nlong, s_nmed, s_bcast[3];
-    __shared__ bool s_last;
+    const unsigned nactive = p.ctl->active_count[p.step & 1ull];      // slots that received a chain in this step
+  for (unsigned tile = blockIdx.x; tile * BLOCK < nactive; tile += gridDim.x) {
     if (threadIdx.x == 0) { s_nlong = 0; s_nmed = 0; }
     __syncthreads();
-    const unsigned slot = blockIdx.x * BLOCK + threadIdx.x;
-    const unsigned head1 = slot < p.mb_slots ? p.mailbox[slot] : 0u;
+    const unsigned ai = tile * BLOCK + threadIdx.x;
+    const unsigned slot = ai < nactive ? p.active[ai] : 0u;
+    const unsigned head1 = ai < nactive ? p.mailbox[slot] : 0u;
     if (head1) {
         p.mailbox[slot] = 0u;                          // leave the mailbox empty for the next step
         unsigned long long k[SHORT_MAX]; float v[SHORT_MAX];
@@ -386,7 +612,7 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
                         if (curcp != 0xFFFFFFFFu) {
                             unsigned cell = curcp >> 1, par = curcp & 1u;
                             p.Q[2u * cell + (par ^ 1u)] = row;
-                            if (FLIP) atomicXor(reinterpret_cast<unsigned*>(p.ci) + (cell >> 2), CI_PAR << ((cell & 3u) * 8u));
+                            if (FLIP) flip_parity(p, cell);
                         }
                         curcp = cp;
                         row = __ldcg(p.Q + 2u * (cp >> 1) + (cp & 1u));
@@ -397,7 +623,7 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
             if (curcp != 0xFFFFFFFFu) {
                 unsigned cell = curcp >> 1, par = curcp & 1u;
                 p.Q[2u * cell + (par ^ 1u)] = row;
-                if (FLIP) atomicXor(reinterpret_cast<unsigned*>(p.ci) + (cell >> 2), CI_PAR << ((cell & 3u) * 8u));
+                if (FLIP) flip_parity(p, cell);
             }
         }
     }
@@ -413,58 +639,48 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
     const unsigned nlong = s_nlong;
     for (unsigned c = 0; c < nlong; ++c) process_long<FLIP>(p, s_long[c], s_keys, s_vals, s_bcast);
     if (threadIdx.x == 0 && nlong) atomicAdd(&p.ctl->long_chains, (unsigned long long)nlong);
+    __syncthreads();
+  }
 
     if (TRAIN) {
-        // sweep: parity ^= occupied, next-step occupancy becomes current, next bits cleared
-        const unsigned n16 = (p.S + 15u) / 16u;
-        uint4* wv = reinterpret_cast<uint4*>(p.ci);
+        // sweep: parity ^= (counter of this step != 0), then clear that counter (it becomes the
+        // "next step" counter of the following step)
+        const unsigned n16 = (2u * p.S + 15u) / 16u;
+        const unsigned shc = cnt_shift(p.step);
+        const unsigned fmask = (CW_CNT_MAX << shc) | (CW_CNT_MAX << (shc + 16u));
+        const unsigned low = (1u << shc) | (1u << (shc + 16u));
+        uint4* wv = reinterpret_cast<uint4*>(p.cw);
         for (unsigned i = blockIdx.x * BLOCK + threadIdx.x; i < n16; i += gridDim.x * BLOCK) {
             uint4 v = wv[i];
-#define CUDARL_SWEEP(w) w = (w & 0x03030303u) | ((w ^ ((w & 0x08080808u) >> 1)) & 0x04040404u) | ((w >> 2) & 0x18181818u)
+#define CUDARL_SWEEP(w) { unsigned f_ = w & fmask; if (f_) { unsigned nz_ = (f_ | (f_ >> 1) | (f_ >> 2) | (f_ >> 3)) & low; \
+                            w = (w ^ ((nz_ >> shc) << 2)) & ~fmask; } }
+            const uint4 o = v;
             CUDARL_SWEEP(v.x); CUDARL_SWEEP(v.y); CUDARL_SWEEP(v.z); CUDARL_SWEEP(v.w);
 #undef CUDARL_SWEEP
-            wv[i] = v;
-        }
-        // the last block to finish advances the step and the epsilon index
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned done_blocks = atomicAdd(&p.ctl->blocks_done, 1u);
-            s_last = (done_blocks == gridDim.x - 1u);
-        }
-        __syncthreads();
-        if (s_last && threadIdx.x == 0) {
-            Ctl* c = p.ctl;
-            c->blocks_done = 0;
-            c->eps_used = p.eps_tab[c->eps_idx];
-            c->step += 1ull;
-            if (c->eps_mode == 1u) { if (c->eps_idx + 1u < c->eps_len) c->eps_idx += 1u; }
-            else if (c->eps_mode == 2u) {
-                unsigned long long kk = *((volatile unsigned long long*)&c->episodes) / (unsigned long long)p.N;
-                unsigned long long rel = kk > c->eps_base_k ? kk - c->eps_base_k : 0ull;
-                c->eps_idx = (unsigned)(rel < (unsigned long long)(c->eps_len - 1u) ? rel : (unsigned long long)(c->eps_len - 1u));
-            }
+            if (o.x != v.x || o.y != v.y || o.z != v.z || o.w != v.w) wv[i] = v;
         }
     }
 }
 
 // ------------------------------------------------------------------------------------------------
 // Caller-driven step (no learning, sticky done, no auto-reset): Environment::step for all envs.
+// actions / rewards / dones are indexed by environment id.
 __global__ void k_step_actions(Params p, const int* actions, float* rewards, unsigned char* dones) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
+    unsigned e = p.id[i];
     int x = p.x[i], y = p.y[i];
     unsigned s = (unsigned)y * (unsigned)p.W + (unsigned)x;
-    unsigned cs = ci_load(p.ci, s), c2;
-    int a = actions[i];
+    unsigned cs = cw_load(p.cw, s), c2;
+    int a = actions[e];
     if (a < 0 || a > 3) a = -1;                         // any other value: no movement (src/gpu/environment.cu:31)
     unsigned s2 = move_cell(p, x, y, s, cs, a, c2);
-    float r = -0.01f; unsigned char dn = p.done[i];
-    if (c2 & CI_GOAL) { r = 1.0f; dn = 1; }
+    float r = -0.01f; unsigned char dn = p.done[e];
+    if (c2 & CW_GOAL) { r = 1.0f; dn = 1; }
     p.x[i] = (int)(s2 % (unsigned)p.W); p.y[i] = (int)(s2 / (unsigned)p.W); p.t[i] += 1;
-    p.reward[i] = r; p.done[i] = dn;
-    if (rewards) rewards[i] = r;
-    if (dones) dones[i] = dn;
+    p.reward[e] = r; p.done[e] = dn;
+    if (rewards) rewards[e] = r;
+    if (dones) dones[e] = dn;
 }
 
 // Greedy rollout of every environment from a fresh start cell; positions stay in registers, the
@@ -476,15 +692,15 @@ __global__ void __launch_bounds__(BLOCK) k_eval(Params p, int max_steps, unsigne
     unsigned i = blockIdx.x * BLOCK + threadIdx.x;
     if (i < p.N) {
         unsigned s = sample_start(p, p.env_offset + i, nonce, TAG_EVAL);
-        unsigned cs = ci_load(p.ci, s);
+        unsigned cs = cw_load(p.cw, s);
         unsigned steps = 0; bool reached = false;
         for (int k = 0; k < max_steps; ++k) {
-            float4 row = __ldg(p.Q + 2u * s + ((cs & CI_PAR) ? 1u : 0u));
+            float4 row = __ldg(p.Q + 2u * s + ((cs & CW_PAR) ? 1u : 0u));
             int a = argmax4(row);
             int x = (int)(s % (unsigned)p.W), y = (int)(s / (unsigned)p.W);
             unsigned c2; unsigned s2 = move_cell(p, x, y, s, cs, a, c2);
             ++steps; s = s2; cs = c2;
-            if (c2 & CI_GOAL) { reached = true; break; }
+            if (c2 & CW_GOAL) { reached = true; break; }
         }
         if (reached) atomicAdd(&s_reached, 1u);
         atomicAdd(&s_steps, (unsigned long long)steps);
@@ -496,29 +712,43 @@ __global__ void __launch_bounds__(BLOCK) k_eval(Params p, int max_steps, unsigne
     }
 }
 
+__global__ void k_active_reset(Params p) { p.ctl->active_count[p.step & 1ull] = 0; }
+
 // update_batch, phase 1: TD error of every transition against the table as it is now; every
 // transition becomes a collision entry (index order = fold order).
 __global__ void k_update_main(Params p, unsigned n, const int* sx, const int* sy, const int* act, const float* rew,
                               const int* nxs, const int* nys, const unsigned char* dn) {
-    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i == 0) p.ctl->scratch_cursor = 0;        // the long-chain scratch is per call; nobody reads it in this kernel
-    if (i >= n) return;
-    int x = sx[i], y = sy[i], a = act[i], nx = nxs[i], ny = nys[i];
-    unsigned s = (unsigned)y * (unsigned)p.W + (unsigned)x;
-    unsigned s2 = (unsigned)ny * (unsigned)p.W + (unsigned)nx;
-    unsigned cs = ci_load(p.ci, s);
-    unsigned par = (cs & CI_PAR) ? 1u : 0u;
-    float4 row = __ldcg(p.Q + 2u * s + par);
-    float m = 0.0f;
-    if (!dn[i]) {
-        unsigned c2 = ci_load(p.ci, s2);
-        m = max4(__ldcg(p.Q + 2u * s2 + ((c2 & CI_PAR) ? 1u : 0u)));
-        if (p.legacy_clamp && m < 0.0f) m = 0.0f;
+    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned lane = threadIdx.x & 31u;
+    if (i == 0) { p.ctl->scratch_cursor = 0; }     // the long-chain scratch is per call; nobody reads it in this kernel
+    bool first = false; unsigned slot = 0;
+    if (i < n) {
+        int x = sx[i], y = sy[i], a = act[i], nx = nxs[i], ny = nys[i];
+        unsigned s = (unsigned)y * (unsigned)p.W + (unsigned)x;
+        unsigned s2 = (unsigned)ny * (unsigned)p.W + (unsigned)nx;
+        unsigned cs = cw_load(p.cw, s);
+        unsigned par = (cs & CW_PAR) ? 1u : 0u;
+        float4 row = __ldcg(p.Q + 2u * s + par);
+        float m = 0.0f;
+        if (!dn[i]) {
+            unsigned c2 = cw_load(p.cw, s2);
+            m = max4(__ldcg(p.Q + 2u * s2 + ((c2 & CW_PAR) ? 1u : 0u)));
+            if (p.legacy_clamp && m < 0.0f) m = 0.0f;
+        }
+        float target = __fmaf_rn(p.gamma, m, rew[i]);
+        float d = __fsub_rn(target, pick(row, a));
+        slot = mb_slot(p, s);
+        unsigned prev = atomicExch(p.mailbox + slot, i + 1u);
+        p.ent[i] = make_uint4((s << 3) | (par << 2) | (unsigned)a, i, __float_as_uint(d), prev);
+        first = prev == 0u;
     }
-    float target = __fmaf_rn(p.gamma, m, rew[i]);
-    float d = __fsub_rn(target, pick(row, a));
-    unsigned prev = atomicExch(p.mailbox + mb_slot(p, s), i + 1u);
-    p.ent[i] = make_uint4((s << 3) | (par << 2) | (unsigned)a, i, __float_as_uint(d), prev);
+    const unsigned fm = __ballot_sync(FULL, first);                  // list the slots that just became active
+    if (fm) {
+        unsigned base = 0;
+        if (lane == __ffs(fm) - 1u) base = atomicAdd(&p.ctl->active_count[p.step & 1ull], __popc(fm));
+        base = __shfl_sync(FULL, base, __ffs(fm) - 1);
+        if (first) p.active[base + __popc(fm & ((1u << lane) - 1u))] = slot;
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -526,14 +756,14 @@ __global__ void k_update_main(Params p, unsigned n, const int* sx, const int* sy
 __global__ void k_q_gather(Params p, float4* dense) {
     unsigned s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= p.S) return;
-    dense[s] = p.Q[2u * s + ((p.ci[s] & CI_PAR) ? 1u : 0u)];
+    dense[s] = p.Q[2u * s + ((p.cw[s] & CW_PAR) ? 1u : 0u)];
 }
 __global__ void k_q_scatter(Params p, const float4* dense, float scale) {
     unsigned s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= p.S) return;
     float4 v = dense[s];
     v.x = __fmul_rn(v.x, scale); v.y = __fmul_rn(v.y, scale); v.z = __fmul_rn(v.z, scale); v.w = __fmul_rn(v.w, scale);
-    p.Q[2u * s + ((p.ci[s] & CI_PAR) ? 1u : 0u)] = v;
+    p.Q[2u * s + ((p.cw[s] & CW_PAR) ? 1u : 0u)] = v;
 }
 __global__ void k_q_init(Params p, int kind, float scale) {
     unsigned s = blockIdx.x * blockDim.x + threadIdx.x;
@@ -546,32 +776,40 @@ __global__ void k_q_init(Params p, int kind, float scale) {
     }
     p.Q[2u * s] = v; p.Q[2u * s + 1u] = v;
 }
-__global__ void k_cells_get(Params p, unsigned char* cells) {
-    unsigned s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= p.S) return;
-    unsigned c = p.ci[s];
-    cells[s] = (c & CI_GOAL) ? 2 : ((c & CI_OBST) ? 1 : 0);
-}
 __global__ void k_cell_set(Params p, unsigned cell, unsigned cls, int clear_goals) {
-    unsigned* w32 = reinterpret_cast<unsigned*>(p.ci);
+    unsigned* w32 = reinterpret_cast<unsigned*>(p.cw);
     if (clear_goals) {
-        unsigned n4 = (p.S + 3u) / 4u;
-        for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x)
-            atomicAnd(w32 + i, ~0x02020202u);
+        unsigned n2 = (p.S + 1u) / 2u;
+        for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n2; i += gridDim.x * blockDim.x)
+            atomicAnd(w32 + i, ~0x00020002u);
     } else if (blockIdx.x == 0 && threadIdx.x == 0) {
-        unsigned sh = (cell & 3u) * 8u;
-        atomicAnd(w32 + (cell >> 2), ~(3u << sh));
-        if (cls) atomicOr(w32 + (cell >> 2), cls << sh);
+        unsigned sh = (cell & 1u) * 16u;
+        atomicAnd(w32 + (cell >> 1), ~(3u << sh));
+        if (cls) atomicOr(w32 + (cell >> 1), cls << sh);
     }
 }
 
 // ------------------------------------------------------------------------------------------------
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
-static inline unsigned sweep_blocks(unsigned S) { unsigned b = nblk((S + 15u) / 16u); return b < 1u ? 1u : (b > 1184u ? 1184u : b); }
+static inline unsigned fix_blocks(const Params& p) { unsigned b = p.mb_slots / BLOCK; return b > 1184u ? 1184u : b; }
+static inline unsigned sweep_blocks(unsigned S) { unsigned b = nblk((2u * S + 15u) / 16u); return b < 1u ? 1u : (b > 1184u ? 1184u : b); }
 
 void launch_rebuild_occupancy(const Params& p, cudaStream_t st) {
     k_occ_clear<<<sweep_blocks(p.S), BLOCK, 0, st>>>(p);
     if (p.N) k_occ_announce<<<nblk(p.N), BLOCK, 0, st>>>(p);
+}
+void launch_identity_ids(const Params& p, cudaStream_t st) { if (p.N) k_ids_identity<<<nblk(p.N), BLOCK, 0, st>>>(p); }
+void launch_export_state(const Params& p, cudaStream_t st) { if (p.N) k_export_state<<<nblk(p.N), BLOCK, 0, st>>>(p); }
+void launch_sort_by_cell(const Params& p, cudaStream_t st) {
+    if (!p.N) return;
+    unsigned nchunks = (p.nkeys + SCAN_CHUNK - 1) / SCAN_CHUNK;
+    unsigned zb = nblk(p.nkeys + 1u); if (zb > 1184u) zb = 1184u;
+    k_sort_zero<<<zb, BLOCK, 0, st>>>(p);
+    k_sort_count<<<nblk(p.N), BLOCK, 0, st>>>(p);
+    k_scan_totals<<<nchunks, BLOCK, 0, st>>>(p);
+    k_scan_blocks<<<1, 1024, 0, st>>>(p, nchunks);
+    k_scan_chunks<<<nchunks, BLOCK, 0, st>>>(p);
+    k_sort_scatter<<<nblk(p.N), BLOCK, 0, st>>>(p);
 }
 void launch_reset_all(const Params& p, cudaStream_t st) {
     if (p.N) k_reset_all<<<nblk(p.N), BLOCK, 0, st>>>(p);
@@ -581,7 +819,8 @@ void launch_train_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t
     if (trace) k_train_main<true><<<p.nblocks_main, BLOCK, 0, st>>>(p);
     else       k_train_main<false><<<p.nblocks_main, BLOCK, 0, st>>>(p);
     if (ev_b) cudaEventRecord(ev_b, st);
-    k_fix<true><<<p.mb_slots / BLOCK, BLOCK, 0, st>>>(p);
+    k_fix<true><<<fix_blocks(p), BLOCK, 0, st>>>(p);
+    if (p.eps_from_ctl) k_eps_episode<<<1, 1, 0, st>>>(p);
     if (ev_c) cudaEventRecord(ev_c, st);
 }
 void launch_step_actions(const Params& p, const int* a, float* r, unsigned char* d, cudaStream_t st) {
@@ -593,13 +832,14 @@ void launch_eval(const Params& p, int max_steps, unsigned long long nonce, cudaS
 void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* sy, const int* a, const float* r,
                          const int* nx, const int* ny, const unsigned char* dn, cudaStream_t st) {
     if (!n) return;
+    k_active_reset<<<1, 1, 0, st>>>(p);
     k_update_main<<<nblk(n), BLOCK, 0, st>>>(p, n, sx, sy, a, r, nx, ny, dn);
-    k_fix<false><<<p.mb_slots / BLOCK, BLOCK, 0, st>>>(p);
+    k_fix<false><<<fix_blocks(p), BLOCK, 0, st>>>(p);
+    k_active_reset<<<1, 1, 0, st>>>(p);      // a following train step starts from an empty list
 }
 void launch_q_gather(const Params& p, float4* dense, cudaStream_t st) { k_q_gather<<<nblk(p.S), BLOCK, 0, st>>>(p, dense); }
 void launch_q_scatter(const Params& p, const float4* dense, float scale, cudaStream_t st) { k_q_scatter<<<nblk(p.S), BLOCK, 0, st>>>(p, dense, scale); }
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st) { k_q_init<<<nblk(p.S), BLOCK, 0, st>>>(p, kind, scale); }
-void launch_cells_get(const Params& p, unsigned char* d_cells, cudaStream_t st) { k_cells_get<<<nblk(p.S), BLOCK, 0, st>>>(p, d_cells); }
 void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st) {
     k_cell_set<<<clear_goals ? sweep_blocks(p.S) : 1, BLOCK, 0, st>>>(p, cell, cls, clear_goals);
 }

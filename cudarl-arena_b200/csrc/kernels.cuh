@@ -6,35 +6,35 @@
 
 namespace cudarl {
 
-// ---- per-cell info byte (one byte per grid cell, 16-byte padded array) -----------------------
-// One load of the byte of a target cell answers "obstacle?", "goal?", "which half of the Q row is
-// current?" and "is another environment standing there?" in a single L2 access.
+// ---- per-cell word (16 bits per grid cell, array padded to 16 bytes) ---------------------------
+// One 2-byte load of a cell answers "obstacle?", "goal?", "which half of the Q row is current?" and
+// "how many environments stand here in this step?" in a single L2 access.
 enum : unsigned {
-    CI_OBST   = 1u,   // static: cell blocks movement            (src/kernels.cu:29-36 of the reference)
-    CI_GOAL   = 2u,   // static: cell ends the episode, reward 1  (src/environment.cu:43-46)
-    CI_PAR    = 4u,   // which 16-byte half of the 32-byte Q row holds Q_t for this cell
-    CI_OCC    = 8u,   // >= 1 environment stands on the cell during the current step
-    CI_MULTI  = 16u,  // >= 2 environments stand on the cell during the current step
-    CI_OCCN   = 32u,  // the same two facts for the NEXT step, announced while the current one runs
-    CI_MULTIN = 64u,
+    CW_OBST = 1u,      // static: cell blocks movement            (src/kernels.cu:29-36 of the reference)
+    CW_GOAL = 2u,      // static: cell ends the episode, reward 1  (src/environment.cu:43-46)
+    CW_PAR  = 4u,      // which 16-byte half of the 32-byte Q row holds Q_t for this cell
+    CW_CNT_SHIFT0 = 4u,   // bits 4-7 : occupant count of even steps, saturating at 15
+    CW_CNT_SHIFT1 = 8u,   // bits 8-11: occupant count of odd steps; while one plane is read, the other is filled
+    CW_CNT_MAX = 15u,
 };
 
 // ---- control block in device memory ------------------------------------------------------------
 struct Ctl {
-    unsigned long long step;        // global batched step index g (keys the policy stream)
     unsigned long long episodes, goals, timeouts, conflicts, long_chains;
     unsigned long long eval_reached, eval_steps;
+    unsigned long long general;     // environment-steps that went through the entry/chain path
     unsigned int eps_idx;           // index of the current step's epsilon in the table
     unsigned int eps_mode;          // 0 fixed index, 1 advance by one per step, 2 per-episode index
     unsigned int eps_len;           // table length (clamp)
     unsigned long long eps_base_k;  // per-episode mode: table[0] belongs to episodes/N == eps_base_k
+    unsigned int active_count[2];   // mailbox slots holding a chain, per step parity
     unsigned int scratch_cursor;    // bump allocator of the long-chain scratch, reset every step
     unsigned int blocks_done;       // last-block detection of the fix kernel
     unsigned int error;             // sticky internal error bits
     float eps_used;                 // epsilon of the most recent step (for the stats call)
 };
 
-enum : unsigned { ERR_SCRATCH_OVERFLOW = 1u, ERR_BAD_STATE = 2u, ERR_BAD_TRANSITION = 4u, ERR_CHAIN_CYCLE = 8u };
+enum : unsigned { ERR_SCRATCH_OVERFLOW = 1u, ERR_BAD_STATE = 2u, ERR_BAD_TRANSITION = 4u, ERR_CHAIN_CYCLE = 8u, ERR_CAS_LIMIT = 16u };
 
 // ---- everything a kernel needs, passed by value ------------------------------------------------
 struct Params {
@@ -50,25 +50,40 @@ struct Params {
     float lr, gamma;
     int legacy_clamp;
     float4* Q;             // 2*S float4: row s = {half0, half1}, 32-byte aligned
-    unsigned char* ci;     // S bytes (padded to 16)
-    int *x, *y, *t;        // structure-of-arrays environment state
-    float* reward; unsigned char* done;       // only for caller-driven stepping
-    uint4* ent;            // collision entries, one slot per environment / transition
+    unsigned short* cw;    // S cell words (padded to 16 bytes)
+    // environment state, structure-of-arrays, in SLOT order: slot k holds environment id[k].  Slots
+    // are re-ordered by cell every few steps so that neighbouring threads touch neighbouring rows.
+    int *x, *y, *t; unsigned* id;
+    int *x2, *y2, *t2; unsigned* id2;          // the other half of the double buffer (sort target / export)
+    float* reward; unsigned char* done;        // per ENVIRONMENT (caller-driven stepping only)
+    uint4* ent;            // collision entries
     unsigned ent_cap;      // slots in ent
-    unsigned* mailbox;     // hashed chain heads (0 = empty), power-of-two size
-    unsigned mb_shift;     // 32 - log2(mailbox slots)
+    unsigned* mailbox;     // chain heads (0 = empty), power-of-two size
     unsigned mb_slots;     // mailbox slots (power of two, multiple of BLOCK)
+    unsigned* active;      // list of the mailbox slots that hold a chain in this step (mb_slots entries)
     Ctl* ctl;
     const float* eps_tab;
-    int* tr_a; float* tr_r; unsigned char* tr_d;   // optional trace of the last step
+    int* tr_a; float* tr_r; unsigned char* tr_d;   // optional trace of the last step, per ENVIRONMENT
     unsigned long long* sc_key; float* sc_val; unsigned sc_cap;   // long-chain scratch (global)
+    unsigned* sort_cnt;    // S+1 counters for the counting sort by cell
+    unsigned* sort_blk;    // per-4096-cell partial sums
+    unsigned nkeys;        // sort keys = ((S - 1) >> sort_shift) + 1
+    unsigned sort_shift;
     unsigned nblocks_main;
+    // per-launch values set by the host
+    unsigned long long step;   // global batched step index g (keys the policy stream, selects the counter plane)
+    unsigned eps_idx;          // index of this step's epsilon in eps_tab
+    int dbg;                   // timing experiments only (0 in normal use)
+    int eps_from_ctl;          // 1: take the index from ctl (per-episode schedule)
 };
 
 constexpr int BLOCK = 256;
 
 // launch wrappers (kernels.cu); all asynchronous on `st`
 void launch_rebuild_occupancy(const Params& p, cudaStream_t st);
+void launch_sort_by_cell(const Params& p, cudaStream_t st);       // writes x2/y2/t2/id2; caller swaps
+void launch_identity_ids(const Params& p, cudaStream_t st);
+void launch_export_state(const Params& p, cudaStream_t st);       // x2/y2/t2[id[k]] = x/y/t[k]
 void launch_reset_all(const Params& p, cudaStream_t st);
 void launch_train_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c);
 void launch_step_actions(const Params& p, const int* d_actions, float* d_rewards, unsigned char* d_dones, cudaStream_t st);
@@ -78,7 +93,6 @@ void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* 
 void launch_q_gather(const Params& p, float4* dense, cudaStream_t st);
 void launch_q_scatter(const Params& p, const float4* dense, float scale, cudaStream_t st);
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st);
-void launch_cells_get(const Params& p, unsigned char* d_cells, cudaStream_t st);
 void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st);
 int  kernel_attr_report(char* buf, int n);
 
