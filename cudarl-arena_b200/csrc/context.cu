@@ -73,7 +73,8 @@ struct cudarl_ctx {
     std::vector<uint8_t> cells;           // host copy of the cell classes
     // device buffers
     void *dQ = nullptr, *dci = nullptr, *dreward = nullptr, *ddone = nullptr;
-    void *dstate[2][4] = {{nullptr, nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr, nullptr}};   // x, y, t, id: two copies (sort / export target)
+    void *dstate[2] = {nullptr, nullptr};   // int4 {x,y,t,id} per slot: two copies (sort target / export scratch)
+    void *dimport = nullptr;              // staging for caller state arrays (3 x N int32)
     void *dsortcnt = nullptr, *dsortblk = nullptr, *dactive = nullptr;
     int cur = 0;                          // which copy of the state is live
     bool slots_identity = true;           // id[k] == k
@@ -176,8 +177,7 @@ int build_cells(cudarl_ctx* c, std::vector<uint8_t>& cells, uint32_t& start_cell
 
 void bind_state(cudarl_ctx* c) {
     Params& p = c->p; const int a = c->cur, b = 1 - c->cur;
-    p.x = (int*)c->dstate[a][0]; p.y = (int*)c->dstate[a][1]; p.t = (int*)c->dstate[a][2]; p.id = (unsigned*)c->dstate[a][3];
-    p.x2 = (int*)c->dstate[b][0]; p.y2 = (int*)c->dstate[b][1]; p.t2 = (int*)c->dstate[b][2]; p.id2 = (unsigned*)c->dstate[b][3];
+    p.st = (int4*)c->dstate[a]; p.st2 = (int4*)c->dstate[b];
 }
 
 int upload_cells(cudarl_ctx* c) {
@@ -203,9 +203,8 @@ int sort_slots(cudarl_ctx* c) {
 // Bring the state back to environment order (slot k = environment k), e.g. before the caller overwrites it.
 int normalize_slots(cudarl_ctx* c) {
     if (c->slots_identity) return 0;
-    launch_export_state(c->p, c->st);
+    launch_normalize(c->p, c->st);
     c->cur = 1 - c->cur; bind_state(c);
-    launch_identity_ids(c->p, c->st);
     CK(cudaGetLastError());
     c->slots_identity = true;
     return 0;
@@ -362,8 +361,7 @@ int run_steps(cudarl_ctx* c, int64_t n) {
 void free_all(cudarl_ctx* c) {
     if (c->st) cudaStreamSynchronize(c->st);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
-    void* bufs[] = {c->dQ, c->dci, c->dstate[0][0], c->dstate[0][1], c->dstate[0][2], c->dstate[0][3], c->dstate[1][0], c->dstate[1][1],
-                    c->dstate[1][2], c->dstate[1][3], c->dsortcnt, c->dsortblk, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
+    void* bufs[] = {c->dQ, c->dci, c->dstate[0], c->dstate[1], c->dimport, c->dsortcnt, c->dsortblk, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->ddense, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6]};
     for (void* b : bufs) if (b) cudaFree(b);
@@ -426,10 +424,10 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             const size_t S = p.S, N = p.N ? p.N : 1;
             CK(cudaMalloc(&c->dQ, S * 2 * sizeof(float4)));
             { int r0 = alloc_hot(c); if (r0) return r0; }
-            for (int cp = 0; cp < 2; ++cp) for (int k = 0; k < 4; ++k) CK(cudaMalloc(&c->dstate[cp][k], N * 4));
+            for (int cp = 0; cp < 2; ++cp) { CK(cudaMalloc(&c->dstate[cp], N * 16)); CK(cudaMemsetAsync(c->dstate[cp], 0, N * 16, c->st)); }
             p.sort_shift = 0; while (((S - 1) >> p.sort_shift) + 1 > 8 * N && ((S - 1) >> p.sort_shift) + 1 > (1u << 16)) ++p.sort_shift;
             p.nkeys = (unsigned)(((S - 1) >> p.sort_shift) + 1);
-            CK(cudaMalloc(&c->dsortcnt, ((size_t)p.nkeys + 1) * sizeof(unsigned)));
+            CK(cudaMalloc(&c->dsortcnt, (((size_t)p.nkeys + 4095) / 4096 * 4096 + 4) * sizeof(unsigned)));   // padded to whole scan chunks
             CK(cudaMalloc(&c->dsortblk, ((size_t)p.nkeys / 4096 + 2) * sizeof(unsigned)));
             CK(cudaMalloc(&c->dctl, sizeof(Ctl)));
             CK(cudaMemsetAsync(c->dctl, 0, sizeof(Ctl), c->st));
@@ -635,12 +633,13 @@ int cudarl_get_state(cudarl_ctx* c, int32_t* x, int32_t* y, int32_t* t) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));
     const size_t b = (size_t)c->p.N * 4;
-    // state lives in slot order; the export kernel writes it in environment order into the spare copy
-    const void *sx = c->p.x, *sy = c->p.y, *st = c->p.t;
-    if (!c->slots_identity) { launch_export_state(c->p, c->st); CK(cudaGetLastError()); sx = c->p.x2; sy = c->p.y2; st = c->p.t2; }
-    if (x) CK(cudaMemcpyAsync(x, sx, b, cudaMemcpyDeviceToHost, c->st));
-    if (y) CK(cudaMemcpyAsync(y, sy, b, cudaMemcpyDeviceToHost, c->st));
-    if (t) CK(cudaMemcpyAsync(t, st, b, cudaMemcpyDeviceToHost, c->st));
+    // state lives in slot order as int4 records; the export kernel writes x[N] | y[N] | t[N] in
+    // environment order into the spare copy
+    launch_export_state(c->p, c->st); CK(cudaGetLastError());
+    const char* base = (const char*)c->p.st2;
+    if (x) CK(cudaMemcpyAsync(x, base, b, cudaMemcpyDeviceToHost, c->st));
+    if (y) CK(cudaMemcpyAsync(y, base + b, b, cudaMemcpyDeviceToHost, c->st));
+    if (t) CK(cudaMemcpyAsync(t, base + 2 * b, b, cudaMemcpyDeviceToHost, c->st));
     CK(cudaStreamSynchronize(c->st));
     return 0;
 }
@@ -652,9 +651,13 @@ int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const in
     if (y) for (size_t i = 0; i < N; ++i) if (y[i] < 0 || y[i] >= c->p.H) return fail(c, -3, "Invalid state");
     CK(cudaSetDevice(c->cfg.device));
     { int rn = normalize_slots(c); if (rn) return rn; }
-    if (x) CK(cudaMemcpyAsync(c->p.x, x, N * 4, cudaMemcpyHostToDevice, c->st));
-    if (y) CK(cudaMemcpyAsync(c->p.y, y, N * 4, cudaMemcpyHostToDevice, c->st));
-    if (t) CK(cudaMemcpyAsync(c->p.t, t, N * 4, cudaMemcpyHostToDevice, c->st));
+    if (!c->dimport) CK(cudaMalloc(&c->dimport, (N ? N : 1) * 12));
+    int* dx = (int*)c->dimport; int* dy = dx + N; int* dt = dy + N;
+    if (x) CK(cudaMemcpyAsync(dx, x, N * 4, cudaMemcpyHostToDevice, c->st));
+    if (y) CK(cudaMemcpyAsync(dy, y, N * 4, cudaMemcpyHostToDevice, c->st));
+    if (t) CK(cudaMemcpyAsync(dt, t, N * 4, cudaMemcpyHostToDevice, c->st));
+    launch_import_state(c->p, x ? dx : nullptr, y ? dy : nullptr, t ? dt : nullptr, c->st);
+    CK(cudaGetLastError());
     CK(cudaStreamSynchronize(c->st));
     c->occ_valid = false;
     return 0;

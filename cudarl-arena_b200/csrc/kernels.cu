@@ -1,8 +1,8 @@
 // kernels.cu -- hand-written sm_100a kernels of the batched grid-world + tabular Q-learning path.
 //
 // Data layout in HBM (per context = per GPU):
-//   x,y,t,id [N]   int32 structure-of-arrays environment state in SLOT order (slot k holds environment
-//                  id[k]); read/written fully coalesced.  Every few steps the slots are re-ordered by
+//   st [N]         environment state, one int4 {x, y, t, id} per SLOT (slot k holds environment id);
+//                  one aligned 16-byte vector load/store per thread, fully coalesced.  Every few steps the slots are re-ordered by
 //                  cell (counting sort), so neighbouring threads touch neighbouring table rows and the
 //                  environments that share a cell sit in the same warp;
 //   Q              one 32-byte sector per grid cell: two float4 halves.  Half PAR(cell) holds
@@ -167,16 +167,17 @@ __global__ void k_occ_clear(Params p) {
 __global__ void k_occ_announce(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
-    unsigned s = (unsigned)p.y[i] * (unsigned)p.W + (unsigned)p.x[i];
+    const int4 r = p.st[i];
+    unsigned s = (unsigned)r.y * (unsigned)p.W + (unsigned)r.x;
     count_add(p, s, cnt_shift(p.step), 1u);
 }
 
 __global__ void k_reset_all(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
-    unsigned e = p.id[i];
+    unsigned e = (unsigned)p.st[i].w;
     unsigned c = sample_start(p, p.env_offset + e, p.step, TAG_START);
-    p.x[i] = (int)(c % (unsigned)p.W); p.y[i] = (int)(c / (unsigned)p.W); p.t[i] = 0;
+    p.st[i] = make_int4((int)(c % (unsigned)p.W), (int)(c / (unsigned)p.W), 0, (int)e);
     if (p.reward) { p.reward[e] = 0.0f; p.done[e] = 0; }
 }
 
@@ -200,22 +201,23 @@ __device__ __forceinline__ unsigned run_mask(unsigned v, unsigned lane) {
 
 __global__ void k_ids_identity(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < p.N) p.id[i] = i;
-}
-__global__ void k_sort_zero(Params p) {
-    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i <= p.nkeys; i += gridDim.x * blockDim.x) p.sort_cnt[i] = 0u;
+    if (i < p.N) p.st[i].w = (int)i;
 }
 __global__ void k_sort_count(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
-    atomicAdd(p.sort_cnt + sort_key(p, p.x[i], p.y[i]), 1u);
+    const int4 r = p.st[i];
+    atomicAdd(p.sort_cnt + sort_key(p, r.x, r.y), 1u);
 }
 constexpr unsigned SCAN_CHUNK = 4096;      // keys per block of the scan
 // phase 1: per-chunk totals; phase 2 (one block): exclusive scan of the totals; phase 3: exclusive scan inside chunks
 __global__ void __launch_bounds__(BLOCK) k_scan_totals(Params p) {
+    // the counter array is padded with zeros to a multiple of SCAN_CHUNK, so whole uint4 loads are safe
     __shared__ unsigned s_sum[BLOCK / 32];
-    unsigned base = blockIdx.x * SCAN_CHUNK, acc = 0;
-    for (unsigned j = threadIdx.x; j < SCAN_CHUNK; j += BLOCK) { unsigned c = base + j; if (c < p.nkeys) acc += p.sort_cnt[c]; }
+    const uint4* c4 = reinterpret_cast<const uint4*>(p.sort_cnt) + blockIdx.x * (SCAN_CHUNK / 4);
+    unsigned acc = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { uint4 v = c4[j * BLOCK + threadIdx.x]; acc += v.x + v.y + v.z + v.w; }
     for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(FULL, acc, o);
     if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = acc;
     __syncthreads();
@@ -254,28 +256,54 @@ __global__ void __launch_bounds__(1024) k_scan_blocks(Params p, unsigned nchunks
     }
 }
 __global__ void __launch_bounds__(BLOCK) k_scan_chunks(Params p) {
-    // 256 threads x 16 consecutive keys
+    // four slabs of 256 uint4 (coalesced); each thread scans its 4 keys, the block scans the thread sums
     __shared__ unsigned s_warp[32];
-    unsigned base = blockIdx.x * SCAN_CHUNK + threadIdx.x * 16u;
-    unsigned v[16], sum = 0;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) { unsigned c = base + j; v[j] = c < p.nkeys ? p.sort_cnt[c] : 0u; sum += v[j]; }
-    unsigned run = p.sort_blk[blockIdx.x] + block_excl_scan(sum, s_warp);
-#pragma unroll
-    for (int j = 0; j < 16; ++j) { unsigned c = base + j; if (c < p.nkeys) p.sort_cnt[c] = run; run += v[j]; }
+    __shared__ unsigned s_tot;
+    uint4* c4 = reinterpret_cast<uint4*>(p.sort_cnt) + blockIdx.x * (SCAN_CHUNK / 4);
+    unsigned carry = p.sort_blk[blockIdx.x];
+    for (int j = 0; j < 4; ++j) {
+        const uint4 v = c4[j * BLOCK + threadIdx.x];
+        const unsigned sum = v.x + v.y + v.z + v.w;
+        const unsigned ex = block_excl_scan(sum, s_warp);
+        if (threadIdx.x == BLOCK - 1) s_tot = ex + sum;
+        const unsigned r0 = carry + ex;
+        c4[j * BLOCK + threadIdx.x] = make_uint4(r0, r0 + v.x, r0 + v.x + v.y, r0 + v.x + v.y + v.z);
+        __syncthreads();
+        carry += s_tot;
+        __syncthreads();
+    }
 }
 __global__ void k_sort_scatter(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
-    int x = p.x[i], y = p.y[i];
-    unsigned pos = atomicAdd(p.sort_cnt + sort_key(p, x, y), 1u);   // offsets become cursors
-    p.x2[pos] = x; p.y2[pos] = y; p.t2[pos] = p.t[i]; p.id2[pos] = p.id[i];
+    const int4 r = p.st[i];
+    unsigned pos = atomicAdd(p.sort_cnt + sort_key(p, r.x, r.y), 1u);   // offsets become cursors
+    p.st2[pos] = r;
+}
+// st2[id] = st[slot]: back to environment order (slot k = environment k)
+__global__ void k_normalize(Params p) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.N) return;
+    const int4 r = p.st[i];
+    p.st2[r.w] = r;
+}
+// overwrite x / y / t of environment-ordered records from caller arrays (any of them may be null)
+__global__ void k_import_state(Params p, const int* x, const int* y, const int* t) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.N) return;
+    int4 r = p.st[i];
+    if (x) r.x = x[i];
+    if (y) r.y = y[i];
+    if (t) r.z = t[i];
+    r.w = (int)i;
+    p.st[i] = r;
 }
 __global__ void k_export_state(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
-    unsigned e = p.id[i];
-    p.x2[e] = p.x[i]; p.y2[e] = p.y[i]; p.t2[e] = p.t[i];
+    const int4 r = p.st[i];
+    int* out = reinterpret_cast<int*>(p.st2);          // the spare copy, viewed as x[N] | y[N] | t[N]
+    out[r.w] = r.x; out[p.N + r.w] = r.y; out[2u * p.N + r.w] = r.z;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -299,7 +327,8 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
     int x = 0, y = 0, t = 0, a = 0, nx = 0, ny = 0; unsigned e = 0, s = 0x80000000u | lane, s2 = 0, par = 0, cnt = 0;
     float4 row = make_float4(0.f, 0.f, 0.f, 0.f); float d = 0.0f; bool done = false;
     if (valid) {
-        x = __ldcs(p.x + i); y = __ldcs(p.y + i); t = __ldcs(p.t + i); e = __ldcs(p.id + i);
+        const int4 rec = __ldcs(p.st + i);
+        x = rec.x; y = rec.y; t = rec.z; e = (unsigned)rec.w;
         s = (unsigned)y * (unsigned)p.W + (unsigned)x;
         const unsigned cs = cw_load(p.cw, s);
         par = (cs & CW_PAR) ? 1u : 0u;
@@ -386,7 +415,7 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
             sn = sample_start(p, p.env_offset + e, g + 1ull, TAG_START);
             nx = (int)(sn % (unsigned)p.W); ny = (int)(sn / (unsigned)p.W); nt = 0;
         }
-        __stcs(p.x + i, nx); __stcs(p.y + i, ny); __stcs(p.t + i, nt);
+        __stcs(p.st + i, make_int4(nx, ny, nt, (int)e));
     }
     {
         // neighbours whose next cells share a 32-bit cell-word pair announce together: one CAS per pair
@@ -668,8 +697,9 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
 __global__ void k_step_actions(Params p, const int* actions, float* rewards, unsigned char* dones) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
-    unsigned e = p.id[i];
-    int x = p.x[i], y = p.y[i];
+    const int4 rec = p.st[i];
+    unsigned e = (unsigned)rec.w;
+    int x = rec.x, y = rec.y;
     unsigned s = (unsigned)y * (unsigned)p.W + (unsigned)x;
     unsigned cs = cw_load(p.cw, s), c2;
     int a = actions[e];
@@ -677,7 +707,7 @@ __global__ void k_step_actions(Params p, const int* actions, float* rewards, uns
     unsigned s2 = move_cell(p, x, y, s, cs, a, c2);
     float r = -0.01f; unsigned char dn = p.done[e];
     if (c2 & CW_GOAL) { r = 1.0f; dn = 1; }
-    p.x[i] = (int)(s2 % (unsigned)p.W); p.y[i] = (int)(s2 / (unsigned)p.W); p.t[i] += 1;
+    p.st[i] = make_int4((int)(s2 % (unsigned)p.W), (int)(s2 / (unsigned)p.W), rec.z + 1, rec.w);
     p.reward[e] = r; p.done[e] = dn;
     if (rewards) rewards[e] = r;
     if (dones) dones[e] = dn;
@@ -800,11 +830,12 @@ void launch_rebuild_occupancy(const Params& p, cudaStream_t st) {
 }
 void launch_identity_ids(const Params& p, cudaStream_t st) { if (p.N) k_ids_identity<<<nblk(p.N), BLOCK, 0, st>>>(p); }
 void launch_export_state(const Params& p, cudaStream_t st) { if (p.N) k_export_state<<<nblk(p.N), BLOCK, 0, st>>>(p); }
+void launch_normalize(const Params& p, cudaStream_t st) { if (p.N) k_normalize<<<nblk(p.N), BLOCK, 0, st>>>(p); }
+void launch_import_state(const Params& p, const int* x, const int* y, const int* t, cudaStream_t st) { if (p.N) k_import_state<<<nblk(p.N), BLOCK, 0, st>>>(p, x, y, t); }
 void launch_sort_by_cell(const Params& p, cudaStream_t st) {
     if (!p.N) return;
     unsigned nchunks = (p.nkeys + SCAN_CHUNK - 1) / SCAN_CHUNK;
-    unsigned zb = nblk(p.nkeys + 1u); if (zb > 1184u) zb = 1184u;
-    k_sort_zero<<<zb, BLOCK, 0, st>>>(p);
+    cudaMemsetAsync(p.sort_cnt, 0, (size_t)nchunks * SCAN_CHUNK * sizeof(unsigned), st);
     k_sort_count<<<nblk(p.N), BLOCK, 0, st>>>(p);
     k_scan_totals<<<nchunks, BLOCK, 0, st>>>(p);
     k_scan_blocks<<<1, 1024, 0, st>>>(p, nchunks);

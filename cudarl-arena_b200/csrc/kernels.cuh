@@ -51,10 +51,11 @@ struct Params {
     int legacy_clamp;
     float4* Q;             // 2*S float4: row s = {half0, half1}, 32-byte aligned
     unsigned short* cw;    // S cell words (padded to 16 bytes)
-    // environment state, structure-of-arrays, in SLOT order: slot k holds environment id[k].  Slots
-    // are re-ordered by cell every few steps so that neighbouring threads touch neighbouring rows.
-    int *x, *y, *t; unsigned* id;
-    int *x2, *y2, *t2; unsigned* id2;          // the other half of the double buffer (sort target / export)
+    // environment state in SLOT order: one int4 {x, y, t, id} per slot (all int32, one coalesced 16-byte
+    // vector per thread).  Slots are re-ordered by cell every few steps so that neighbouring threads touch
+    // neighbouring rows; the record moves as one vector.
+    int4* st;
+    int4* st2;             // the other half of the double buffer (sort target / export scratch)
     float* reward; unsigned char* done;        // per ENVIRONMENT (caller-driven stepping only)
     uint4* ent;            // collision entries
     unsigned ent_cap;      // slots in ent
@@ -81,9 +82,11 @@ constexpr int BLOCK = 256;
 
 // launch wrappers (kernels.cu); all asynchronous on `st`
 void launch_rebuild_occupancy(const Params& p, cudaStream_t st);
-void launch_sort_by_cell(const Params& p, cudaStream_t st);       // writes x2/y2/t2/id2; caller swaps
+void launch_sort_by_cell(const Params& p, cudaStream_t st);       // writes st2; caller swaps
 void launch_identity_ids(const Params& p, cudaStream_t st);
-void launch_export_state(const Params& p, cudaStream_t st);       // x2/y2/t2[id[k]] = x/y/t[k]
+void launch_export_state(const Params& p, cudaStream_t st);       // st2 viewed as x[N]|y[N]|t[N] in environment order
+void launch_normalize(const Params& p, cudaStream_t st);          // st2[id] = st[slot]; caller swaps
+void launch_import_state(const Params& p, const int* x, const int* y, const int* t, cudaStream_t st);
 void launch_reset_all(const Params& p, cudaStream_t st);
 void launch_train_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c);
 void launch_step_actions(const Params& p, const int* d_actions, float* d_rewards, unsigned char* d_dones, cudaStream_t st);
