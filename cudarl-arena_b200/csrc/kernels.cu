@@ -85,9 +85,9 @@ __device__ __forceinline__ void count_add(const Params& p, unsigned cell, unsign
 }
 
 // Same for both cells of a 32-bit pair at once (even cell gets g0, odd cell g1).
-__device__ __forceinline__ void count_add2(const Params& p, unsigned pair, unsigned shift, unsigned g0, unsigned g1) {
+// `old` is the caller's last view of the word (a stale view only costs one more round).
+__device__ __forceinline__ void count_add2(const Params& p, unsigned pair, unsigned shift, unsigned g0, unsigned g1, unsigned old) {
     unsigned* w = reinterpret_cast<unsigned*>(p.cw) + pair;
-    unsigned old = *reinterpret_cast<volatile unsigned*>(w);
     for (int it = 0; it < 100000; ++it) {
         unsigned f0 = (old >> shift) & CW_CNT_MAX, f1 = (old >> (shift + 16u)) & CW_CNT_MAX;
         unsigned n0 = f0 + g0; if (n0 > CW_CNT_MAX) n0 = CW_CNT_MAX;
@@ -312,8 +312,8 @@ template <bool TRACE>
 __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
     __shared__ unsigned s_cnt, s_goals, s_timeouts, s_shared;
     __shared__ int2 s_pair[BLOCK];
-    __shared__ unsigned s_act[BLOCK], s_nact, s_actbase;
-    if (threadIdx.x == 0) { s_cnt = 0; s_goals = 0; s_timeouts = 0; s_shared = 0; s_nact = 0; }
+    __shared__ unsigned s_act[BLOCK], s_nact, s_done;
+    if (threadIdx.x == 0) { s_cnt = 0; s_goals = 0; s_timeouts = 0; s_shared = 0; s_nact = 0; s_done = 0; }
     __syncthreads();
     const unsigned i = blockIdx.x * BLOCK + threadIdx.x;
     const unsigned lane = threadIdx.x & 31u;
@@ -324,13 +324,15 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
     const unsigned shc = cnt_shift(g), shn = cnt_shift(g + 1ull);
     const float eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx];
     // ---- per-lane work (lanes past the end idle through it with harmless values) ----------------------
-    int x = 0, y = 0, t = 0, a = 0, nx = 0, ny = 0; unsigned e = 0, s = 0x80000000u | lane, s2 = 0, par = 0, cnt = 0;
+    int x = 0, y = 0, t = 0, a = 0, nx = 0, ny = 0; unsigned e = 0, s = 0x80000000u | lane, s2 = 0, par = 0, cnt = 0, wguess = 0;
     float4 row = make_float4(0.f, 0.f, 0.f, 0.f); float d = 0.0f; bool done = false;
     if (valid) {
         const int4 rec = __ldcs(p.st + i);
         x = rec.x; y = rec.y; t = rec.z; e = (unsigned)rec.w;
         s = (unsigned)y * (unsigned)p.W + (unsigned)x;
-        const unsigned cs = cw_load(p.cw, s);
+        const unsigned* cw32 = reinterpret_cast<const unsigned*>(p.cw);
+        const unsigned ws = cw32[s >> 1];                     // the 32-bit word holding this cell and its pair mate
+        const unsigned cs = (ws >> ((s & 1u) * 16u)) & 0xFFFFu;
         par = (cs & CW_PAR) ? 1u : 0u;
         cnt = (cs >> shc) & CW_CNT_MAX;
         row = __ldcg(p.Q + 2u * s + par);
@@ -342,8 +344,10 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
         nx = x + dx; ny = y + dy;
         const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
         const unsigned tgt = inb ? (unsigned)ny * (unsigned)p.W + (unsigned)nx : s;
-        const unsigned ct = inb ? cw_load(p.cw, tgt) : cs;
+        const unsigned wt = inb ? cw32[tgt >> 1] : ws;
+        const unsigned ct = (wt >> ((tgt & 1u) * 16u)) & 0xFFFFu;
         const bool moved = inb && !(ct & CW_OBST);
+        wguess = moved ? wt : ws;                             // what the next cell's word looked like a moment ago
         const unsigned c2 = moved ? ct : cs;
         s2 = moved ? tgt : s; nx = moved ? nx : x; ny = moved ? ny : y;
         done = (c2 & CW_GOAL) != 0;
@@ -414,6 +418,7 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
         if (done || timeout) {
             sn = sample_start(p, p.env_offset + e, g + 1ull, TAG_START);
             nx = (int)(sn % (unsigned)p.W); ny = (int)(sn / (unsigned)p.W); nt = 0;
+            wguess = reinterpret_cast<const unsigned*>(p.cw)[sn >> 1];
         }
         __stcs(p.st + i, make_int4(nx, ny, nt, (int)e));
     }
@@ -423,29 +428,39 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
         const unsigned odd = __ballot_sync(FULL, (sn & 1u) != 0u);
         if (!(p.dbg & 2) && valid && lane == __ffs(wmask) - 1u) {
             if (p.dbg & 16) atomicAdd(reinterpret_cast<unsigned*>(p.cw) + (sn >> 1), (__popc(wmask & ~odd) << shn) | (__popc(wmask & odd) << (shn + 16u)));
-            else count_add2(p, sn >> 1, shn, __popc(wmask & ~odd), __popc(wmask & odd));
+            else count_add2(p, sn >> 1, shn, __popc(wmask & ~odd), __popc(wmask & odd), wguess);
         }
     }
+    if (valid && done) atomicAdd(&s_goals, 1u);                 // rare events
+    if (timeout) atomicAdd(&s_timeouts, 1u);
     {
-        const unsigned mg = __ballot_sync(FULL, valid && done), mt = __ballot_sync(FULL, timeout), ms = __ballot_sync(FULL, valid && cnt >= 2u);
-        if (lane == 0) {
-            if (mg) atomicAdd(&s_goals, __popc(mg));
-            if (mt) atomicAdd(&s_timeouts, __popc(mt));
-            if (ms) atomicAdd(&s_shared, __popc(ms));
+        const unsigned ms = __ballot_sync(FULL, valid && cnt >= 2u);
+        if (lane == 0 && ms) atomicAdd(&s_shared, __popc(ms));
+    }
+    // No block barrier at the end: the last warp of the block to get here publishes the block's
+    // counters and its list of newly active slots, so finished warps free their slots right away.
+    __syncwarp();
+    unsigned last = 0;
+    if (lane == 0) { __threadfence_block(); last = (atomicAdd(&s_done, 1u) == BLOCK / 32 - 1) ? 1u : 0u; }
+    last = __shfl_sync(FULL, last, 0);
+    if (last) {
+        __threadfence_block();
+        const unsigned nact = *(volatile unsigned*)&s_nact;
+        if (nact) {
+            unsigned base = 0;
+            if (lane == 0) base = atomicAdd(&p.ctl->active_count[p.step & 1ull], nact);
+            base = __shfl_sync(FULL, base, 0);
+            for (unsigned k = lane; k < nact; k += 32u) p.active[base + k] = ((volatile unsigned*)s_act)[k];
         }
-    }
-    __syncthreads();
-    if (s_nact) {                                                     // publish this block's newly active slots
-        if (threadIdx.x == 0) s_actbase = atomicAdd(&p.ctl->active_count[p.step & 1ull], s_nact);
-        __syncthreads();
-        if (threadIdx.x < s_nact) p.active[s_actbase + threadIdx.x] = s_act[threadIdx.x];
-    }
-    if (threadIdx.x == 0) {
-        if (s_shared) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_shared);
-        if (s_cnt) atomicAdd(&p.ctl->general, (unsigned long long)s_cnt);
-        if (s_goals) atomicAdd(&p.ctl->goals, (unsigned long long)s_goals);
-        if (s_timeouts) atomicAdd(&p.ctl->timeouts, (unsigned long long)s_timeouts);
-        if (s_goals + s_timeouts) atomicAdd(&p.ctl->episodes, (unsigned long long)(s_goals + s_timeouts));
+        if (lane == 0) {
+            const unsigned sh = *(volatile unsigned*)&s_shared, cn = *(volatile unsigned*)&s_cnt;
+            const unsigned go = *(volatile unsigned*)&s_goals, to = *(volatile unsigned*)&s_timeouts;
+            if (sh) atomicAdd(&p.ctl->conflicts, (unsigned long long)sh);
+            if (cn) atomicAdd(&p.ctl->general, (unsigned long long)cn);
+            if (go) atomicAdd(&p.ctl->goals, (unsigned long long)go);
+            if (to) atomicAdd(&p.ctl->timeouts, (unsigned long long)to);
+            if (go + to) atomicAdd(&p.ctl->episodes, (unsigned long long)(go + to));
+        }
     }
 }
 
