@@ -193,9 +193,8 @@ int upload_cells(cudarl_ctx* c) {
 // Re-order the slots by cell (counting sort into the other copy of the state, then swap).
 int sort_slots(cudarl_ctx* c) {
     if (c->p.N < 2048) return 0;                   // nothing to gain for a handful of environments
-    launch_sort_by_cell(c->p, c->st);
+    launch_sort_by_cell(c->p, c->st);                // scatter into the spare copy, rank back into the live one
     CK(cudaGetLastError());
-    c->cur = 1 - c->cur; bind_state(c);
     c->slots_identity = false; c->since_sort = 0;
     return 0;
 }
@@ -239,8 +238,8 @@ int alloc_hot(cudarl_ctx* c) {
     CK(cudaMemsetAsync(c->dci, 0, total, c->st));
     c->p.cw = (unsigned short*)c->dci;
     c->p.mailbox = (unsigned*)((char*)c->dci + ci_bytes); c->p.mb_slots = (unsigned)slots; (void)lg;
-    CK(cudaMalloc(&c->dactive, slots * sizeof(unsigned)));
-    c->p.active = (unsigned*)c->dactive;
+    CK(cudaMalloc(&c->dactive, 2 * slots * sizeof(unsigned)));
+    c->p.active = (unsigned*)c->dactive; c->p.longq = (unsigned*)c->dactive + slots;
     // L2 persistence (per context, released with it): best effort, a refusal is not an error.
     int dev = c->cfg.device, max_persist = 0, max_window = 0;
     cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev);
@@ -398,7 +397,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
     if (f->struct_size != sizeof(cudarl_config)) return fail(nullptr, -1, "cudarl_config.struct_size mismatch");
     if (f->width < 1 || f->height < 1) return fail(nullptr, -1, "grid must be at least 1x1");
     if ((uint64_t)f->width * (uint64_t)f->height >= (1ull << 28)) return fail(nullptr, -1, "grid larger than 2^28 cells");
-    if (f->num_envs < 0 || f->num_envs >= (1ll << 31)) return fail(nullptr, -1, "num_envs out of range");
+    if (f->num_envs < 0 || f->num_envs >= (1ll << 26)) return fail(nullptr, -1, "num_envs out of range (at most 2^26 - 1 per context)");
     if (f->env_offset < 0 || f->env_offset + f->num_envs >= (1ll << 32)) return fail(nullptr, -1, "env_offset out of range");
     if (f->max_steps < 0) return fail(nullptr, -1, "max_steps negative");
     if (f->eps_kind < 0 || f->eps_kind > 3) return fail(nullptr, -1, "bad eps_kind");
@@ -425,7 +424,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             CK(cudaMalloc(&c->dQ, S * 2 * sizeof(float4)));
             { int r0 = alloc_hot(c); if (r0) return r0; }
             for (int cp = 0; cp < 2; ++cp) { CK(cudaMalloc(&c->dstate[cp], N * 16)); CK(cudaMemsetAsync(c->dstate[cp], 0, N * 16, c->st)); }
-            p.sort_shift = 0; while (((S - 1) >> p.sort_shift) + 1 > 8 * N && ((S - 1) >> p.sort_shift) + 1 > (1u << 16)) ++p.sort_shift;
+            p.sort_shift = 0; while (((S - 1) >> p.sort_shift) + 1 > (1u << 21) || (((S - 1) >> p.sort_shift) + 1 > 2 * N && ((S - 1) >> p.sort_shift) + 1 > (1u << 12))) ++p.sort_shift;
             p.nkeys = (unsigned)(((S - 1) >> p.sort_shift) + 1);
             CK(cudaMalloc(&c->dsortcnt, (((size_t)p.nkeys + 4095) / 4096 * 4096 + 4) * sizeof(unsigned)));   // padded to whole scan chunks
             CK(cudaMalloc(&c->dsortblk, ((size_t)p.nkeys / 4096 + 2) * sizeof(unsigned)));
@@ -604,7 +603,7 @@ int cudarl_update_batch(cudarl_ctx* c, int64_t n, const int32_t* sx, const int32
     if (!c || n < 0) return fail(c, -1, "bad argument");
     if (n == 0) return 0;
     if (!sx || !sy || !a || !r || !nx || !ny || !dn) return fail(c, -1, "null argument");
-    if (n >= (1ll << 31)) return fail(c, -1, "batch too large");
+    if (n >= (1ll << 26)) return fail(c, -1, "batch too large (at most 2^26 - 1 transitions per call)");
     const int W = c->p.W, H = c->p.H;
     for (int64_t i = 0; i < n; ++i)   // src/q_learning.cu:192-194,212-214 reject these; the reference kernel would read out of bounds
         if (sx[i] < 0 || sx[i] >= W || sy[i] < 0 || sy[i] >= H || a[i] < 0 || a[i] >= CUDARL_ACTIONS ||

@@ -8,7 +8,7 @@
 //   Q              one 32-byte sector per grid cell: two float4 halves.  Half PAR(cell) holds
 //                  Q_t[cell][0..3] (one vector load = the whole action row), the other half is where
 //                  Q_{t+1} of that cell is written, so readers of step t never see a write of step t;
-//   cw             one 16-bit word per cell: obstacle, goal, row parity and two 4-bit occupant counters
+//   cw             one 16-bit word per cell: obstacle, goal, row parity and two 6-bit occupant counters
 //                  (this step / next step, saturating), small enough to stay in L2;
 //   ent / mailbox  collision entries and chain heads for cells whose occupants are spread over
 //                  several warps.
@@ -68,7 +68,7 @@ __device__ __forceinline__ void flip_parity(const Params& p, unsigned cell) {
     atomicXor(reinterpret_cast<unsigned*>(p.cw) + (cell >> 1), CW_PAR << ((cell & 1u) * 16u));
 }
 
-// Add `g` occupants to the 4-bit counter (field at `shift`) of `cell`, saturating at 15.
+// Add `g` occupants to the 6-bit counter (field at `shift`) of `cell`, saturating at 63.
 __device__ __forceinline__ void count_add(const Params& p, unsigned cell, unsigned shift, unsigned g) {
     unsigned* w = reinterpret_cast<unsigned*>(p.cw) + (cell >> 1);
     const unsigned sh = shift + (cell & 1u) * 16u;
@@ -159,7 +159,7 @@ __global__ void k_occ_clear(Params p) {
     uint4* w = reinterpret_cast<uint4*>(p.cw);
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += gridDim.x * blockDim.x) {
         uint4 v = w[i];
-        const unsigned keep = 0x000F000Fu;
+        const unsigned keep = 0x00070007u;
         v.x &= keep; v.y &= keep; v.z &= keep; v.w &= keep;
         w[i] = v;
     }
@@ -280,6 +280,31 @@ __global__ void k_sort_scatter(Params p) {
     unsigned pos = atomicAdd(p.sort_cnt + sort_key(p, r.x, r.y), 1u);   // offsets become cursors
     p.st2[pos] = r;
 }
+// Second half of the sort: inside every key segment of st2 order the records by (cell, id) and write
+// them to st.  Afterwards environments that share a cell sit in consecutive slots in ascending id, which
+// is the order their TD errors are folded in.  Segments longer than RANK_MAX are copied as they are
+// (still correct, only slower later: such cells take the sorting path of the fold kernel).
+constexpr unsigned RANK_MAX = 4096;
+__global__ void k_sort_rank(Params p) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.N) return;
+    const int4 r = p.st2[i];
+    const unsigned key = sort_key(p, r.x, r.y);
+    const unsigned lo = key ? p.sort_cnt[key - 1u] : 0u, hi = p.sort_cnt[key];     // cursors = segment ends after the scatter
+    unsigned dst = i;
+    if (hi - lo > 1u && hi - lo <= RANK_MAX) {
+        const unsigned long long mine = ((unsigned long long)((unsigned)r.y * (unsigned)p.W + (unsigned)r.x) << 32) | (unsigned)r.w;
+        unsigned rank = 0;
+        for (unsigned j = lo; j < hi; ++j) {
+            const int4 o = p.st2[j];
+            const unsigned long long k = ((unsigned long long)((unsigned)o.y * (unsigned)p.W + (unsigned)o.x) << 32) | (unsigned)o.w;
+            rank += k < mine ? 1u : 0u;
+        }
+        dst = lo + rank;
+    }
+    p.st[dst] = r;
+}
+
 // st2[id] = st[slot]: back to environment order (slot k = environment k)
 __global__ void k_normalize(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -318,7 +343,7 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
     const unsigned i = blockIdx.x * BLOCK + threadIdx.x;
     const unsigned lane = threadIdx.x & 31u;
     const unsigned lt = (1u << lane) - 1u;                              // lanes below mine
-    if (blockIdx.x == 0 && threadIdx.x == 0) { p.ctl->scratch_cursor = 0; p.ctl->active_count[(p.step + 1ull) & 1ull] = 0; }   // nobody reads these in this kernel
+    if (blockIdx.x == 0 && threadIdx.x == 0) { p.ctl->scratch_cursor = 0; p.ctl->active_count[(p.step + 1ull) & 1ull] = 0; p.ctl->long_count[(p.step + 1ull) & 1ull] = 0; }   // nobody reads these in this kernel
     const bool valid = i < p.N;
     const unsigned long long g = p.step;
     const unsigned shc = cnt_shift(g), shn = cnt_shift(g + 1ull);
@@ -337,7 +362,7 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
         cnt = (cs >> shc) & CW_CNT_MAX;
         row = __ldcg(p.Q + 2u * s + par);
         // epsilon-greedy
-        U4 w = (p.dbg & 8) ? U4{e * 2654435761u, e, 0u, 0u} : philox4x32_10(p.env_offset + e, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
+        U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
         a = (u01(w.x) < eps) ? (int)(w.y & 3u) : argmax4(row);
         // environment transition
         const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
@@ -367,17 +392,23 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
     // every occupant of the cell is in this group <=> the cell's counter equals the group size
     const bool complete = valid && cnt == gsize && gsize < CW_CNT_MAX;
     {
-        // Fold the group's TD errors in ascending environment id.  Only full-warp collectives are used
-        // (collectives with a per-lane mask are several times slower on this part): every lane ranks its
-        // id inside its run with shuffles at growing distances, the (action, td_error) pairs are parked
-        // in shared memory at their rank, and the run's first lane folds them in that order.
+        // Fold the group's TD errors in ascending environment id.  The slot order is (cell, id) as of the
+        // last re-ordering, so normally the lanes of a run already are in id order and the run's first lane
+        // simply folds the (action, td_error) pairs its lanes parked in shared memory.  If some complete run
+        // of the warp is out of order (environments met since), every lane first ranks its id inside its run
+        // with full-warp shuffles at growing distances and parks its pair at its rank.
         const unsigned gend = gleader + gsize - 1u;
-        const unsigned maxlen = __reduce_max_sync(FULL, (complete && !(p.dbg & 1)) ? gsize : 0u);
-        unsigned rank = 0;
-        for (unsigned off = 1; off < maxlen; ++off) {
-            const unsigned eu = __shfl_up_sync(FULL, e, off), ed = __shfl_down_sync(FULL, e, off);
-            rank += (lane >= gleader + off && eu < e) ? 1u : 0u;
-            rank += (lane + off <= gend && ed < e) ? 1u : 0u;
+        const unsigned up_e = __shfl_up_sync(FULL, e, 1);
+        const unsigned disorder = __ballot_sync(FULL, complete && lane > gleader && e < up_e);
+        unsigned rank = lane - gleader;
+        if (disorder) {                                     // warp-uniform
+            const unsigned maxlen = __reduce_max_sync(FULL, complete ? gsize : 0u);
+            rank = 0;
+            for (unsigned off = 1; off < maxlen; ++off) {
+                const unsigned eu = __shfl_up_sync(FULL, e, off), ed = __shfl_down_sync(FULL, e, off);
+                rank += (lane >= gleader + off && eu < e) ? 1u : 0u;
+                rank += (lane + off <= gend && ed < e) ? 1u : 0u;
+            }
         }
         const unsigned wbase = threadIdx.x & ~31u;
         if (complete && gsize > 1u) s_pair[wbase + gleader + rank] = make_int2(a, __float_as_int(d));
@@ -389,24 +420,21 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
         }
     }
     {
-        // occupants in other warps too: entries, linked inside the group, hooked into the cell's chain
-        const bool gen = valid && !complete && !(p.dbg & 4);
+        // occupants in other warps too: the run's lanes write consecutive entries and the run's first lane
+        // hooks the whole run into the cell's chain with one exchange
+        const bool gen = valid && !complete;
         const unsigned genmask = __ballot_sync(FULL, gen);
         if (genmask) {
             unsigned base = 0;
             if (lane == __ffs(genmask) - 1u) base = atomicAdd(&s_cnt, __popc(genmask));
             base = __shfl_sync(FULL, base, __ffs(genmask) - 1);
-            const unsigned pos = blockIdx.x * BLOCK + base + __popc(genmask & lt);
-            const unsigned higher = gmask & ~((2u << lane) - 1u);
-            const int nl = higher ? (int)(__ffs(higher) - 1u) : -1;
-            const unsigned pos_next = __shfl_sync(FULL, pos, nl >= 0 ? nl : (int)lane);
+            const unsigned pos = blockIdx.x * BLOCK + base + __popc(genmask & lt);      // a run's lanes get consecutive positions
             unsigned prev = 0u;
             if (gen && lane == gleader) {
-                prev = atomicExch(p.mailbox + mb_slot(p, s), pos + 1u);
+                prev = atomicExch(p.mailbox + mb_slot(p, s), ((gsize - 1u) << LINK_POS_BITS) | (pos + 1u));
                 if (!prev) s_act[atomicAdd(&s_nact, 1u)] = mb_slot(p, s);    // first chain on this slot in this step
             }
-            prev = __shfl_sync(FULL, prev, gleader);
-            if (gen) p.ent[pos] = make_uint4((s << 3) | (par << 2) | (unsigned)a, e, __float_as_uint(d), nl >= 0 ? pos_next + 1u : prev);
+            if (gen) p.ent[pos] = make_uint4((s << 3) | (par << 2) | (unsigned)a, e, __float_as_uint(d), prev);
         }
     }
     // ---- episode bookkeeping, next-step occupancy, state out ----------------------------------------------
@@ -426,10 +454,7 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
         // neighbours whose next cells share a 32-bit cell-word pair announce together: one CAS per pair
         const unsigned wmask = run_mask(sn >> 1, lane);
         const unsigned odd = __ballot_sync(FULL, (sn & 1u) != 0u);
-        if (!(p.dbg & 2) && valid && lane == __ffs(wmask) - 1u) {
-            if (p.dbg & 16) atomicAdd(reinterpret_cast<unsigned*>(p.cw) + (sn >> 1), (__popc(wmask & ~odd) << shn) | (__popc(wmask & odd) << (shn + 16u)));
-            else count_add2(p, sn >> 1, shn, __popc(wmask & ~odd), __popc(wmask & odd), wguess);
-        }
+        if (valid && lane == __ffs(wmask) - 1u) count_add2(p, sn >> 1, shn, __popc(wmask & ~odd), __popc(wmask & odd), wguess);
     }
     if (valid && done) atomicAdd(&s_goals, 1u);                 // rare events
     if (timeout) atomicAdd(&s_timeouts, 1u);
@@ -516,31 +541,25 @@ __device__ void apply_run(const Params& p, const unsigned long long* keys, const
 constexpr unsigned LONG_SMEM = 1024;   // chain entries sorted in shared memory; longer chains use the global scratch
 constexpr int SHORT_MAX = 8;           // chain entries folded in registers by one thread
 
+// One long chain, whole block: count its entries (one hop per run), pick shared memory or a slice of the
+// global scratch, copy the runs (one warp per run, batches of 256 runs), bitonic-sort by (cell, action, id)
+// and let the first thread of every cell run fold it.
 template <bool FLIP>
 __device__ void process_long(const Params& p, unsigned head1, unsigned long long* s_keys, float* s_vals,
                              unsigned* s_bcast) {
-    // thread 0 walks the chain (pointer chase through L2), everyone sorts, run leaders fold.
+    __shared__ unsigned s_run[BLOCK], s_off[BLOCK];
     if (threadIdx.x == 0) {
-        unsigned q = head1, L = 0;
-        while (q && L <= p.ent_cap) {            // a chain can never be longer than the entry array
-            uint4 e = p.ent[q - 1u];
-            if (L < LONG_SMEM) { s_keys[L] = ((unsigned long long)e.x << 32) | e.y; s_vals[L] = __uint_as_float(e.z); }
-            ++L; q = e.w;
+        unsigned q = head1, L = 0, hops = 0;
+        while (q && hops <= p.ent_cap) {          // a chain can never have more runs than the entry array has slots
+            L += (q >> LINK_POS_BITS) + 1u; ++hops;
+            q = p.ent[(q & LINK_POS_MASK) - 1u].w;
         }
         unsigned n2 = 1; while (n2 < L) n2 <<= 1;
         unsigned base = 0xFFFFFFFFu;
-        if (q) { atomicOr(&p.ctl->error, ERR_CHAIN_CYCLE); base = 0xFFFFFFFEu; }
+        if (q || L > p.ent_cap) { atomicOr(&p.ctl->error, ERR_CHAIN_CYCLE); base = 0xFFFFFFFEu; }
         else if (L > LONG_SMEM) {
             base = atomicAdd(&p.ctl->scratch_cursor, n2);
             if (base + n2 > p.sc_cap) { atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); base = 0xFFFFFFFEu; }
-            else {
-                q = head1; unsigned k = 0;
-                while (q && k < L) {
-                    uint4 e = p.ent[q - 1u];
-                    p.sc_key[base + k] = ((unsigned long long)e.x << 32) | e.y; p.sc_val[base + k] = __uint_as_float(e.z);
-                    ++k; q = e.w;
-                }
-            }
         }
         s_bcast[0] = L; s_bcast[1] = n2; s_bcast[2] = base;
     }
@@ -549,6 +568,31 @@ __device__ void process_long(const Params& p, unsigned head1, unsigned long long
     if (base != 0xFFFFFFFEu) {
         unsigned long long* keys = (base == 0xFFFFFFFFu) ? s_keys : p.sc_key + base;
         float* vals = (base == 0xFFFFFFFFu) ? s_vals : p.sc_val + base;
+        __shared__ unsigned s_q, s_nb, s_done_entries;
+        if (threadIdx.x == 0) { s_q = head1; s_done_entries = 0; }
+        __syncthreads();
+        while (true) {                               // batches of up to 256 runs; ends when the chain is exhausted
+            if (threadIdx.x == 0) {
+                unsigned q = s_q, nb = 0, off = s_done_entries;
+                while (q && nb < (unsigned)BLOCK) {
+                    s_run[nb] = q; s_off[nb] = off; off += (q >> LINK_POS_BITS) + 1u; ++nb;
+                    q = p.ent[(q & LINK_POS_MASK) - 1u].w;
+                }
+                s_q = q; s_nb = nb; s_done_entries = off;
+            }
+            __syncthreads();
+            const unsigned nb = s_nb;
+            if (nb == 0u) break;
+            for (unsigned r = threadIdx.x >> 5; r < nb; r += BLOCK / 32) {
+                const unsigned link = s_run[r], pos0 = (link & LINK_POS_MASK) - 1u, len = (link >> LINK_POS_BITS) + 1u;
+                const unsigned j = threadIdx.x & 31u;
+                if (j < len && s_off[r] + j < L) {
+                    const uint4 e = p.ent[pos0 + j];
+                    keys[s_off[r] + j] = ((unsigned long long)e.x << 32) | e.y; vals[s_off[r] + j] = __uint_as_float(e.z);
+                }
+            }
+            __syncthreads();
+        }
         for (unsigned i = L + threadIdx.x; i < n2; i += blockDim.x) { keys[i] = ~0ull; vals[i] = 0.0f; }
         __syncthreads();
         block_bitonic(keys, vals, n2);
@@ -587,87 +631,92 @@ __device__ void process_medium(const Params& p, unsigned long long* keys, float*
 }
 
 // Collision folding, one thread per ACTIVE mailbox slot (the producers list every slot they were the
-// first to hook a chain into, so this kernel only visits slots that have work).  A slot's chain holds
-// every entry whose cell maps there; the thread that takes the slot owns the chain:
-//   <= 8 entries   gathered, ordered (sorting network) and folded in registers by that thread;
+// first to hook a chain into, so this kernel only visits slots that have work).  A slot's chain links
+// RUNS of consecutive entries (one run = the lanes of one warp on one cell).  The owning thread gathers
+// the chain's entries:
+//   <= 8 entries   in registers, ordered by a sorting network and folded by that thread;
 //   <= 32 entries  staged in shared memory by that thread, ordered and folded by one warp;
-//   longer         walked by one thread, sorted by the whole block (shared memory up to 1024 entries,
-//                  the global scratch beyond that).
+//   longer         queued for k_fix_long, where one block per chain sorts it.
 // TRAIN = true : part of a train step -- also sweeps the cell words (parity ^= occupied, consumed
 //                counter cleared).
 // TRAIN = false: update_batch -- flips the row parity of every folded cell instead.
+template <bool FLIP>
+__device__ __forceinline__ void flush_row(const Params& p, unsigned cellpar, const float4& row) {
+    const unsigned cell = cellpar >> 1, par = cellpar & 1u;
+    p.Q[2u * cell + (par ^ 1u)] = row;
+    if (FLIP) flip_parity(p, cell);
+}
+
 template <bool TRAIN>
 __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
     constexpr bool FLIP = !TRAIN;
     __shared__ unsigned long long s_keys[LONG_SMEM];
     __shared__ float s_vals[LONG_SMEM];
-    __shared__ unsigned s_long[BLOCK];
     __shared__ unsigned s_medlen[MED_CHUNKS];
-    __shared__ unsigned s_nlong, s_nmed, s_bcast[3];
+    __shared__ unsigned s_nmed;
     const unsigned nactive = p.ctl->active_count[p.step & 1ull];      // slots that received a chain in this step
   for (unsigned tile = blockIdx.x; tile * BLOCK < nactive; tile += gridDim.x) {
-    if (threadIdx.x == 0) { s_nlong = 0; s_nmed = 0; }
+    if (threadIdx.x == 0) s_nmed = 0;
     __syncthreads();
     const unsigned ai = tile * BLOCK + threadIdx.x;
     const unsigned slot = ai < nactive ? p.active[ai] : 0u;
-    const unsigned head1 = ai < nactive ? p.mailbox[slot] : 0u;
-    if (head1) {
+    const unsigned head = ai < nactive ? p.mailbox[slot] : 0u;
+    if (head) {
         p.mailbox[slot] = 0u;                          // leave the mailbox empty for the next step
-        unsigned long long k[SHORT_MAX]; float v[SHORT_MAX];
-        unsigned q = head1;
+        unsigned long long k8[SHORT_MAX]; float v8[SHORT_MAX];
+        unsigned q = head, pos = 0, rem = 0; bool fresh = false;
 #pragma unroll
         for (int j = 0; j < SHORT_MAX; ++j) {
-            if (q) {
-                uint4 e = __ldcg(p.ent + (q - 1u));
-                k[j] = ((unsigned long long)e.x << 32) | e.y; v[j] = __uint_as_float(e.z); q = e.w;
-            } else { k[j] = ~0ull; v[j] = 0.0f; }
+            if (rem == 0u && q) { pos = (q & LINK_POS_MASK) - 1u; rem = (q >> LINK_POS_BITS) + 1u; fresh = true; }
+            if (rem) {
+                const uint4 e = __ldcg(p.ent + pos);
+                k8[j] = ((unsigned long long)e.x << 32) | e.y; v8[j] = __uint_as_float(e.z);
+                if (fresh) { q = e.w; fresh = false; }
+                ++pos; --rem;
+            } else { k8[j] = ~0ull; v8[j] = 0.0f; }
         }
-        if (q) {
-            unsigned chunk = atomicAdd(&s_nmed, 1u);
+        if (rem == 0u && q == 0u) {
+            cswap(k8[0],v8[0],k8[1],v8[1]); cswap(k8[2],v8[2],k8[3],v8[3]); cswap(k8[4],v8[4],k8[5],v8[5]); cswap(k8[6],v8[6],k8[7],v8[7]);
+            cswap(k8[0],v8[0],k8[2],v8[2]); cswap(k8[1],v8[1],k8[3],v8[3]); cswap(k8[4],v8[4],k8[6],v8[6]); cswap(k8[5],v8[5],k8[7],v8[7]);
+            cswap(k8[1],v8[1],k8[2],v8[2]); cswap(k8[5],v8[5],k8[6],v8[6]); cswap(k8[0],v8[0],k8[4],v8[4]); cswap(k8[3],v8[3],k8[7],v8[7]);
+            cswap(k8[1],v8[1],k8[5],v8[5]); cswap(k8[2],v8[2],k8[6],v8[6]);
+            cswap(k8[1],v8[1],k8[4],v8[4]); cswap(k8[3],v8[3],k8[6],v8[6]);
+            cswap(k8[2],v8[2],k8[4],v8[4]); cswap(k8[3],v8[3],k8[5],v8[5]);
+            cswap(k8[3],v8[3],k8[4],v8[4]);
+            unsigned curcp = 0xFFFFFFFFu; float4 row = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < SHORT_MAX; ++j) {
+                if (k8[j] != ~0ull) {
+                    const unsigned w0 = (unsigned)(k8[j] >> 32), cp = w0 >> 2;
+                    if (cp != curcp) {
+                        if (curcp != 0xFFFFFFFFu) flush_row<FLIP>(p, curcp, row);
+                        curcp = cp; row = __ldcg(p.Q + 2u * (cp >> 1) + (cp & 1u));
+                    }
+                    fold(row, (int)(w0 & 3u), p.lr, v8[j]);
+                }
+            }
+            if (curcp != 0xFFFFFFFFu) flush_row<FLIP>(p, curcp, row);
+        } else {
+            const unsigned chunk = atomicAdd(&s_nmed, 1u);
             bool staged = false;
             if (chunk < MED_CHUNKS) {
                 unsigned long long* mk = s_keys + chunk * MED_MAX; float* mv = s_vals + chunk * MED_MAX;
 #pragma unroll
-                for (int j = 0; j < SHORT_MAX; ++j) { mk[j] = k[j]; mv[j] = v[j]; }
+                for (int j = 0; j < SHORT_MAX; ++j) { mk[j] = k8[j]; mv[j] = v8[j]; }
                 unsigned L = SHORT_MAX;
-                while (q && L < MED_MAX) {
-                    uint4 e = __ldcg(p.ent + (q - 1u));
-                    mk[L] = ((unsigned long long)e.x << 32) | e.y; mv[L] = __uint_as_float(e.z); q = e.w; ++L;
+                while ((rem || q) && L < MED_MAX) {
+                    if (rem == 0u) { pos = (q & LINK_POS_MASK) - 1u; rem = (q >> LINK_POS_BITS) + 1u; fresh = true; }
+                    const uint4 e = __ldcg(p.ent + pos);
+                    mk[L] = ((unsigned long long)e.x << 32) | e.y; mv[L] = __uint_as_float(e.z);
+                    if (fresh) { q = e.w; fresh = false; }
+                    ++pos; --rem; ++L;
                 }
-                staged = (q == 0u);
+                staged = (rem == 0u && q == 0u);
                 s_medlen[chunk] = staged ? L : 0u;
             }
-            if (!staged) { unsigned li = atomicAdd(&s_nlong, 1u); s_long[li] = head1; }
-        } else {
-            // sorting network for 8 (19 comparators)
-            cswap(k[0],v[0],k[1],v[1]); cswap(k[2],v[2],k[3],v[3]); cswap(k[4],v[4],k[5],v[5]); cswap(k[6],v[6],k[7],v[7]);
-            cswap(k[0],v[0],k[2],v[2]); cswap(k[1],v[1],k[3],v[3]); cswap(k[4],v[4],k[6],v[6]); cswap(k[5],v[5],k[7],v[7]);
-            cswap(k[1],v[1],k[2],v[2]); cswap(k[5],v[5],k[6],v[6]); cswap(k[0],v[0],k[4],v[4]); cswap(k[3],v[3],k[7],v[7]);
-            cswap(k[1],v[1],k[5],v[5]); cswap(k[2],v[2],k[6],v[6]);
-            cswap(k[1],v[1],k[4],v[4]); cswap(k[3],v[3],k[6],v[6]);
-            cswap(k[2],v[2],k[4],v[4]); cswap(k[3],v[3],k[5],v[5]);
-            cswap(k[3],v[3],k[4],v[4]);
-            unsigned curcp = 0xFFFFFFFFu; float4 row = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < SHORT_MAX; ++j) {
-                if (k[j] != ~0ull) {
-                    unsigned w0 = (unsigned)(k[j] >> 32), cp = w0 >> 2;
-                    if (cp != curcp) {
-                        if (curcp != 0xFFFFFFFFu) {
-                            unsigned cell = curcp >> 1, par = curcp & 1u;
-                            p.Q[2u * cell + (par ^ 1u)] = row;
-                            if (FLIP) flip_parity(p, cell);
-                        }
-                        curcp = cp;
-                        row = __ldcg(p.Q + 2u * (cp >> 1) + (cp & 1u));
-                    }
-                    fold(row, (int)(w0 & 3u), p.lr, v[j]);
-                }
-            }
-            if (curcp != 0xFFFFFFFFu) {
-                unsigned cell = curcp >> 1, par = curcp & 1u;
-                p.Q[2u * cell + (par ^ 1u)] = row;
-                if (FLIP) flip_parity(p, cell);
+            if (!staged) {                              // hand the chain to k_fix_long
+                const unsigned li = atomicAdd(&p.ctl->long_count[p.step & 1ull], 1u);
+                p.longq[li] = head;
             }
         }
     }
@@ -679,10 +728,6 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
             if (L) process_medium<FLIP>(p, s_keys + c * MED_MAX, s_vals + c * MED_MAX, L);
         }
     }
-    __syncthreads();
-    const unsigned nlong = s_nlong;
-    for (unsigned c = 0; c < nlong; ++c) process_long<FLIP>(p, s_long[c], s_keys, s_vals, s_bcast);
-    if (threadIdx.x == 0 && nlong) atomicAdd(&p.ctl->long_chains, (unsigned long long)nlong);
     __syncthreads();
   }
 
@@ -696,7 +741,7 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
         uint4* wv = reinterpret_cast<uint4*>(p.cw);
         for (unsigned i = blockIdx.x * BLOCK + threadIdx.x; i < n16; i += gridDim.x * BLOCK) {
             uint4 v = wv[i];
-#define CUDARL_SWEEP(w) { unsigned f_ = w & fmask; if (f_) { unsigned nz_ = (f_ | (f_ >> 1) | (f_ >> 2) | (f_ >> 3)) & low; \
+#define CUDARL_SWEEP(w) { unsigned f_ = w & fmask; if (f_) { unsigned nz_ = (f_ | (f_ >> 1) | (f_ >> 2) | (f_ >> 3) | (f_ >> 4) | (f_ >> 5)) & low; \
                             w = (w ^ ((nz_ >> shc) << 2)) & ~fmask; } }
             const uint4 o = v;
             CUDARL_SWEEP(v.x); CUDARL_SWEEP(v.y); CUDARL_SWEEP(v.z); CUDARL_SWEEP(v.w);
@@ -704,6 +749,19 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
             if (o.x != v.x || o.y != v.y || o.z != v.z || o.w != v.w) wv[i] = v;
         }
     }
+}
+
+// Long chains (more than 32 entries: cells crowded with environments), one block per chain, spread over
+// the whole GPU: the runs are listed by one thread (one hop per run), copied by all threads, sorted by a
+// block-wide bitonic sort (shared memory up to 1024 entries, the global scratch beyond) and folded.
+template <bool FLIP>
+__global__ void __launch_bounds__(BLOCK) k_fix_long(Params p) {
+    __shared__ unsigned long long s_keys[LONG_SMEM];
+    __shared__ float s_vals[LONG_SMEM];
+    __shared__ unsigned s_bcast[3];
+    const unsigned n = p.ctl->long_count[p.step & 1ull];
+    for (unsigned c = blockIdx.x; c < n; c += gridDim.x) process_long<FLIP>(p, p.longq[c], s_keys, s_vals, s_bcast);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && n) atomicAdd(&p.ctl->long_chains, (unsigned long long)n);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -757,7 +815,7 @@ __global__ void __launch_bounds__(BLOCK) k_eval(Params p, int max_steps, unsigne
     }
 }
 
-__global__ void k_active_reset(Params p) { p.ctl->active_count[p.step & 1ull] = 0; }
+__global__ void k_active_reset(Params p) { p.ctl->active_count[p.step & 1ull] = 0; p.ctl->long_count[p.step & 1ull] = 0; }
 
 // update_batch, phase 1: TD error of every transition against the table as it is now; every
 // transition becomes a collision entry (index order = fold order).
@@ -783,7 +841,7 @@ __global__ void k_update_main(Params p, unsigned n, const int* sx, const int* sy
         float target = __fmaf_rn(p.gamma, m, rew[i]);
         float d = __fsub_rn(target, pick(row, a));
         slot = mb_slot(p, s);
-        unsigned prev = atomicExch(p.mailbox + slot, i + 1u);
+        unsigned prev = atomicExch(p.mailbox + slot, i + 1u);          // a run of one entry
         p.ent[i] = make_uint4((s << 3) | (par << 2) | (unsigned)a, i, __float_as_uint(d), prev);
         first = prev == 0u;
     }
@@ -856,6 +914,7 @@ void launch_sort_by_cell(const Params& p, cudaStream_t st) {
     k_scan_blocks<<<1, 1024, 0, st>>>(p, nchunks);
     k_scan_chunks<<<nchunks, BLOCK, 0, st>>>(p);
     k_sort_scatter<<<nblk(p.N), BLOCK, 0, st>>>(p);
+    k_sort_rank<<<nblk(p.N), BLOCK, 0, st>>>(p);     // result is back in p.st
 }
 void launch_reset_all(const Params& p, cudaStream_t st) {
     if (p.N) k_reset_all<<<nblk(p.N), BLOCK, 0, st>>>(p);
@@ -866,6 +925,7 @@ void launch_train_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t
     else       k_train_main<false><<<p.nblocks_main, BLOCK, 0, st>>>(p);
     if (ev_b) cudaEventRecord(ev_b, st);
     k_fix<true><<<fix_blocks(p), BLOCK, 0, st>>>(p);
+    k_fix_long<false><<<296, BLOCK, 0, st>>>(p);
     if (p.eps_from_ctl) k_eps_episode<<<1, 1, 0, st>>>(p);
     if (ev_c) cudaEventRecord(ev_c, st);
 }
@@ -881,6 +941,7 @@ void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* 
     k_active_reset<<<1, 1, 0, st>>>(p);
     k_update_main<<<nblk(n), BLOCK, 0, st>>>(p, n, sx, sy, a, r, nx, ny, dn);
     k_fix<false><<<fix_blocks(p), BLOCK, 0, st>>>(p);
+    k_fix_long<true><<<296, BLOCK, 0, st>>>(p);
     k_active_reset<<<1, 1, 0, st>>>(p);      // a following train step starts from an empty list
 }
 void launch_q_gather(const Params& p, float4* dense, cudaStream_t st) { k_q_gather<<<nblk(p.S), BLOCK, 0, st>>>(p, dense); }

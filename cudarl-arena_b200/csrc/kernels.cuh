@@ -13,10 +13,15 @@ enum : unsigned {
     CW_OBST = 1u,      // static: cell blocks movement            (src/kernels.cu:29-36 of the reference)
     CW_GOAL = 2u,      // static: cell ends the episode, reward 1  (src/environment.cu:43-46)
     CW_PAR  = 4u,      // which 16-byte half of the 32-byte Q row holds Q_t for this cell
-    CW_CNT_SHIFT0 = 4u,   // bits 4-7 : occupant count of even steps, saturating at 15
-    CW_CNT_SHIFT1 = 8u,   // bits 8-11: occupant count of odd steps; while one plane is read, the other is filled
-    CW_CNT_MAX = 15u,
+    CW_CNT_SHIFT0 = 3u,   // bits 3-8 : occupant count of even steps, saturating at 63
+    CW_CNT_SHIFT1 = 9u,   // bits 9-14: occupant count of odd steps; while one plane is read, the other is filled
+    CW_CNT_MAX = 63u,
 };
+
+// A chain link names a run of consecutive collision entries: low 26 bits = position of the first entry + 1
+// (0 = end of chain), bits 26-30 = run length - 1 (a run never exceeds one warp).
+constexpr unsigned LINK_POS_BITS = 26u;
+constexpr unsigned LINK_POS_MASK = (1u << LINK_POS_BITS) - 1u;
 
 // ---- control block in device memory ------------------------------------------------------------
 struct Ctl {
@@ -28,6 +33,7 @@ struct Ctl {
     unsigned int eps_len;           // table length (clamp)
     unsigned long long eps_base_k;  // per-episode mode: table[0] belongs to episodes/N == eps_base_k
     unsigned int active_count[2];   // mailbox slots holding a chain, per step parity
+    unsigned int long_count[2];     // chains queued for the block-per-chain kernel, per step parity
     unsigned int scratch_cursor;    // bump allocator of the long-chain scratch, reset every step
     unsigned int blocks_done;       // last-block detection of the fix kernel
     unsigned int error;             // sticky internal error bits
@@ -62,6 +68,7 @@ struct Params {
     unsigned* mailbox;     // chain heads (0 = empty), power-of-two size
     unsigned mb_slots;     // mailbox slots (power of two, multiple of BLOCK)
     unsigned* active;      // list of the mailbox slots that hold a chain in this step (mb_slots entries)
+    unsigned* longq;       // heads of the chains left to the block-per-chain kernel (mb_slots entries)
     Ctl* ctl;
     const float* eps_tab;
     int* tr_a; float* tr_r; unsigned char* tr_d;   // optional trace of the last step, per ENVIRONMENT
