@@ -204,7 +204,7 @@ def main():
     cfg.env_offset = rank * n_local
     window = args.window or (cfg.sync_every if cfg.sync_every > 0 else 256)
     env = pkg.VecGridWorld(cfg)
-    launches_per_step = 2
+    launches_per_step = 3      # k_train_main, k_fix, k_fix_long (+ 6 re-ordering kernels every 8th step)
 
     if args.profile_steps:                      # small fixed run for profilers: no timing, no JSON
         env.train_steps(args.profile_steps)
@@ -278,8 +278,8 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(args.config, cfg), "window": window, "l2": "inputs_exceed_l2" if cfg.width * cfg.height * 32 > 126e6 else "l2_resident",
                    "parallelism": "env-sharded x%d, Q replica per GPU, NCCL average every %d steps" % (world, cfg.sync_every)},
-        "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": int(window * 4), "d2h_bytes_per_step": 104},
-        "gpu_launches": int(args.steps * (window * launches_per_step + launches_per_step_window_extra)),
+        "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": int(window * 4), "d2h_bytes_per_step": 128},
+        "gpu_launches": int(args.steps * (window * launches_per_step + (window // 8) * 6 + launches_per_step_window_extra)),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                      "peak_kind": peak_kind, "kernel": "k_train_main", "algorithmic_bytes_per_env_step": ALGO_BYTES_TRAIN,
@@ -287,7 +287,8 @@ def main():
                      "whole_step_frac": ALGO_BYTES_TRAIN * n_local / (ms * 1e-3 / (args.steps * window)) / 1e9 / peak},
         "cpu_baseline": cpu,
         "run_stats": {"steps": stats.steps, "goals": stats.goals, "timeouts": stats.timeouts,
-                      "conflict_fraction": stats.conflicts / max(stats.env_steps, 1), "long_chains": stats.long_chains},
+                      "conflict_fraction": stats.conflicts / max(stats.env_steps, 1), "chained_fraction": stats.chained / max(stats.env_steps, 1),
+                      "long_chains": stats.long_chains},
     }
     print(json.dumps(line))
 

@@ -78,7 +78,7 @@ struct cudarl_ctx {
     void *dsortcnt = nullptr, *dsortblk = nullptr, *dactive = nullptr;
     int cur = 0;                          // which copy of the state is live
     bool slots_identity = true;           // id[k] == k
-    int64_t sort_every = 16, since_sort = 0;
+    int64_t sort_every = 8, since_sort = 0;
     void *dent = nullptr, *dctl = nullptr, *deps = nullptr;
     void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
     void *ddense = nullptr;               // S float4: table in the caller's layout / allreduce buffer
@@ -443,9 +443,8 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             CK(cudaStreamSynchronize(c->st));
             return 0;
         };
-        c->sort_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 16);
+        c->sort_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 8);
         if (const char* ev = getenv("CUDARL_SORT_EVERY")) c->sort_every = atoll(ev);
-        if (const char* ev = getenv("CUDARL_DBG")) c->p.dbg = atoi(ev);
         rc = body();
     } while (0);
     if (rc) { g_err = c->err; free_all(c); delete c; return rc; }

@@ -81,7 +81,6 @@ struct Params {
     // per-launch values set by the host
     unsigned long long step;   // global batched step index g (keys the policy stream, selects the counter plane)
     unsigned eps_idx;          // index of this step's epsilon in eps_tab
-    int dbg;                   // timing experiments only (0 in normal use)
     int eps_from_ctl;          // 1: take the index from ctl (per-episode schedule)
 };
 

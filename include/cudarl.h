@@ -73,7 +73,7 @@ typedef struct cudarl_config {
     float    q_init_scale;
     int32_t  legacy_clamp;  /* 1: max_next = max(0, max_a' Q) as in src/kernels.cu:102-110 */
     int32_t  sync_every;    /* average the replicas every this many train steps; 0 = never */
-    int32_t  reserved[4];   /* reserved[0]: re-order the slots by cell every this many train steps (0 = default 16, <0 = never) */
+    int32_t  reserved[4];   /* reserved[0]: re-order the slots by cell every this many train steps (0 = default 8, <0 = never; the environment variable CUDARL_SORT_EVERY overrides it) */
 } cudarl_config;
 
 typedef struct cudarl_stats {
