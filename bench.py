@@ -216,7 +216,7 @@ def main():
         ids = [pkg.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         env.comm_init(ids[0], rank, world)
-        launches_per_step_window_extra = 2      # gather + scatter kernels around each allreduce
+        launches_per_step_window_extra = 32     # gather + average kernels around each all-gather round (16 rounds at C5)
     else:
         launches_per_step_window_extra = 0
 

@@ -42,6 +42,7 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     bool load(std::string& err) {
         if (h) return true;
@@ -51,8 +52,9 @@ struct NcclApi {
         CommInitRank = (decltype(CommInitRank))dlsym(h, "ncclCommInitRank");
         CommDestroy = (decltype(CommDestroy))dlsym(h, "ncclCommDestroy");
         AllReduce = (decltype(AllReduce))dlsym(h, "ncclAllReduce");
+        AllGather = (decltype(AllGather))dlsym(h, "ncclAllGather");
         GetErrorString = (decltype(GetErrorString))dlsym(h, "ncclGetErrorString");
-        if (!GetUniqueId || !CommInitRank || !CommDestroy || !AllReduce) { err = "NCCL symbols missing"; h = nullptr; return false; }
+        if (!GetUniqueId || !CommInitRank || !CommDestroy || !AllReduce || !AllGather) { err = "NCCL symbols missing"; h = nullptr; return false; }
         return true;
     }
 };
@@ -81,7 +83,8 @@ struct cudarl_ctx {
     int64_t sort_every = 8, since_sort = 0;
     void *dent = nullptr, *dctl = nullptr, *deps = nullptr;
     void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
-    void *ddense = nullptr;               // S float4: table in the caller's layout / allreduce buffer
+    void *ddense = nullptr;               // S float4: table in the caller's layout
+    void *dgather = nullptr, *dsend = nullptr;   // replica averaging: all-gather landing zone and send chunk
     void* dub[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; size_t ub_cap = 0;   // update_batch staging
     void* dact = nullptr;                 // actions staging for the host form of step_actions
     size_t ent_cap = 0, eps_cap = 0, l2_window_bytes = 0;
@@ -327,12 +330,24 @@ int drain_kernel_events(cudarl_ctx* c) {
     return 0;
 }
 
+// Q <- (Q_0 + Q_1 + ... + Q_{R-1}) * (1/R), summed in rank order on every GPU.  The rows travel with an
+// NCCL all-gather in chunks (NVLink / NVSwitch); the reduction itself is our kernel, so the result is the
+// same bits on every rank and the same bits as the CPU oracle for any R (an all-reduce would leave the
+// summation order to the library).
 int average_now(cudarl_ctx* c) {
     if (!c->comm || c->nranks <= 1) return 0;
-    int rc = ensure_dense(c); if (rc) return rc;
-    launch_q_gather(c->p, (float4*)c->ddense, c->st);
-    NK(g_nccl.AllReduce(c->ddense, c->ddense, (size_t)c->p.S * 4, ncclFloat, ncclSum, c->comm, c->st));
-    launch_q_scatter(c->p, (const float4*)c->ddense, 1.0f / (float)c->nranks, c->st);
+    const size_t S = c->p.S, R = (size_t)c->nranks;
+    const size_t chunk = S < (1u << 20) ? S : (1u << 20);            // cells per round: 16 MiB per rank
+    if (!c->dgather) {
+        CK(cudaMalloc(&c->dgather, R * chunk * sizeof(float4)));
+        CK(cudaMalloc(&c->dsend, chunk * sizeof(float4)));
+    }
+    for (size_t c0 = 0; c0 < S; c0 += chunk) {
+        const size_t n = S - c0 < chunk ? S - c0 : chunk;
+        launch_q_gather_range(c->p, (float4*)c->dsend, (unsigned)c0, (unsigned)n, c->st);
+        NK(g_nccl.AllGather(c->dsend, c->dgather, n * 4, ncclFloat, c->comm, c->st));
+        launch_q_average(c->p, (const float4*)c->dgather, (unsigned)R, (unsigned)c0, (unsigned)n, 1.0f / (float)R, c->st);
+    }
     CK(cudaGetLastError());
     return 0;
 }
@@ -361,7 +376,7 @@ void free_all(cudarl_ctx* c) {
     if (c->st) cudaStreamSynchronize(c->st);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     void* bufs[] = {c->dQ, c->dci, c->dstate[0], c->dstate[1], c->dimport, c->dsortcnt, c->dsortblk, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
-                    c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->ddense, c->dact,
+                    c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->ddense, c->dgather, c->dsend, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6]};
     for (void* b : bufs) if (b) cudaFree(b);
     if (c->h_eps) cudaFreeHost(c->h_eps);
@@ -745,7 +760,7 @@ int cudarl_comm_init(cudarl_ctx* c, const void* id128, int32_t rank, int32_t nra
     ncclUniqueId id; std::memcpy(&id, id128, sizeof(id));
     NK(g_nccl.CommInitRank(&c->comm, nranks, id, rank));
     c->rank = rank; c->nranks = nranks;
-    return ensure_dense(c);
+    return 0;
 }
 int cudarl_average_replicas(cudarl_ctx* c) {
     if (!c) return -1;

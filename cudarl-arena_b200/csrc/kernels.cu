@@ -868,6 +868,27 @@ __global__ void k_q_scatter(Params p, const float4* dense, float scale) {
     v.x = __fmul_rn(v.x, scale); v.y = __fmul_rn(v.y, scale); v.z = __fmul_rn(v.z, scale); v.w = __fmul_rn(v.w, scale);
     p.Q[2u * s + ((p.cw[s] & CW_PAR) ? 1u : 0u)] = v;
 }
+// Replica averaging, second half: `gathered` holds the rows [cell0, cell0+n) of every rank's table, rank after
+// rank.  Sum them in rank order 0..R-1 in fp32 (the order of the CPU oracle, whatever the transport did),
+// scale by 1/R and store into the current half.
+__global__ void k_q_average(Params p, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float4 acc = gathered[i];
+    for (unsigned r = 1; r < R; ++r) {
+        const float4 v = gathered[(size_t)r * n + i];
+        acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+    }
+    acc.x = __fmul_rn(acc.x, scale); acc.y = __fmul_rn(acc.y, scale); acc.z = __fmul_rn(acc.z, scale); acc.w = __fmul_rn(acc.w, scale);
+    const unsigned s = cell0 + i;
+    p.Q[2u * s + ((p.cw[s] & CW_PAR) ? 1u : 0u)] = acc;
+}
+__global__ void k_q_gather_range(Params p, float4* dense, unsigned cell0, unsigned n) {
+    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned s = cell0 + i;
+    dense[i] = p.Q[2u * s + ((p.cw[s] & CW_PAR) ? 1u : 0u)];
+}
 __global__ void k_q_init(Params p, int kind, float scale) {
     unsigned s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= p.S) return;
@@ -946,6 +967,10 @@ void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* 
 }
 void launch_q_gather(const Params& p, float4* dense, cudaStream_t st) { k_q_gather<<<nblk(p.S), BLOCK, 0, st>>>(p, dense); }
 void launch_q_scatter(const Params& p, const float4* dense, float scale, cudaStream_t st) { k_q_scatter<<<nblk(p.S), BLOCK, 0, st>>>(p, dense, scale); }
+void launch_q_gather_range(const Params& p, float4* dense, unsigned cell0, unsigned n, cudaStream_t st) { if (n) k_q_gather_range<<<nblk(n), BLOCK, 0, st>>>(p, dense, cell0, n); }
+void launch_q_average(const Params& p, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale, cudaStream_t st) {
+    if (n) k_q_average<<<nblk(n), BLOCK, 0, st>>>(p, gathered, R, cell0, n, scale);
+}
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st) { k_q_init<<<nblk(p.S), BLOCK, 0, st>>>(p, kind, scale); }
 void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st) {
     k_cell_set<<<clear_goals ? sweep_blocks(p.S) : 1, BLOCK, 0, st>>>(p, cell, cls, clear_goals);

@@ -101,6 +101,8 @@ void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* 
                          const int* nx, const int* ny, const unsigned char* dn, cudaStream_t st);
 void launch_q_gather(const Params& p, float4* dense, cudaStream_t st);
 void launch_q_scatter(const Params& p, const float4* dense, float scale, cudaStream_t st);
+void launch_q_gather_range(const Params& p, float4* dense, unsigned cell0, unsigned n, cudaStream_t st);
+void launch_q_average(const Params& p, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale, cudaStream_t st);
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st);
 void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st);
 int  kernel_attr_report(char* buf, int n);

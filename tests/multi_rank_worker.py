@@ -72,9 +72,9 @@ def main():
     want_q, want_state = shards[rank].get_q(), shards[rank].get_state()
     for u, v in zip(mine_state, want_state):
         assert np.array_equal(u, v), "rank %d: shard state differs" % rank
-    if world <= 2:
+    if a.mode == "gpu" or world <= 2:      # the GPU path sums in rank order itself: bit-exact for any world size
         assert np.array_equal(mine_q, want_q), "rank %d: averaged table differs" % rank
-    else:   # a sum of more than two terms has no fixed order in NCCL / gloo
+    else:   # the gloo all-reduce of the CPU stand-in has no fixed order beyond two ranks
         np.testing.assert_allclose(mine_q, want_q, rtol=1e-5, atol=1e-7)
     dist.barrier()
     if rank == 0:
