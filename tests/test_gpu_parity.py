@@ -302,3 +302,35 @@ def test_full_size_c5_lockstep_and_properties(pkg, orc):
     assert s.episodes == s.goals + s.timeouts
     q = gpu.get_q()
     assert np.isfinite(q).all() and q.max() <= 1.0 and q.min() >= -1.0
+
+
+def test_slot_reordering_never_changes_results(pkg, orc):
+    """The slots are re-ordered by cell every few steps purely for locality; any period (and none) must give the
+    same bits, and the state must come back in environment order."""
+    base = pkg.preset("C3", num_envs=20000)
+    base.width = base.height = 96
+    ref = orc.Oracle(base, threads=4)
+    ref.train_steps(70)
+    want_state, want_q = ref.get_state(), ref.get_q()
+    for period in (1, 3, 8, 50, -1):
+        cfg = base.copy()
+        cfg.reserved[0] = period
+        g = pkg.VecGridWorld(cfg)
+        for n in (1, 9, 60):
+            g.train_steps(n)
+        for a, b in zip(g.get_state(), want_state):
+            assert np.array_equal(a, b), "period %d" % period
+        assert np.array_equal(g.get_q(), want_q), "period %d" % period
+        assert g.get_stats().device_error == 0
+        g.close()
+
+
+def test_odd_sizes_and_tiny_populations(pkg, orc):
+    for w, h, n in [(1, 7, 5), (7, 1, 33), (13, 11, 1), (31, 3, 257), (5, 5, 0)]:
+        cfg = pkg.make_config(w, h, n, start_mode=pkg.START_RANDOM, goal_mode=pkg.GOAL_SEEDED, num_goals=1,
+                              obstacle_kind=pkg.OBST_BERNOULLI, obstacle_p=0.1, eps_kind=pkg.EPS_FIXED, eps0=0.4, max_steps=9)
+        gpu, cpu = pair(pkg, orc, cfg)
+        gpu.train_steps(25); cpu.train_steps(25)
+        assert_same(gpu, cpu, "%dx%d n=%d" % (w, h, n))
+        a, b = gpu.eval_rollout(20), cpu.eval_rollout(20)
+        assert (a.reached, a.total_steps) == (b.reached, b.total_steps)
