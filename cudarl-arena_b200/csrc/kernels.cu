@@ -15,11 +15,11 @@
 //
 // One batched step = two launches:
 //   train_main  one thread per slot: epsilon-greedy from a Philox4x32-10 stream keyed by
-//               (seed, global env, step) -> move with obstacle/goal lookup -> TD error against Q_t.
+//               (seed, global env, step) -> move with obstacle/goal lookup -> TD target from Q_t.
 //               The warp groups its lanes by cell (match.any).  If the cell's occupant count equals
-//               the group size, every occupant is in this warp: the group folds its TD errors in
+//               the group size, every occupant is in this warp: the group applies its updates in
 //               ascending environment id with shuffles and its leader writes the cell's Q_{t+1} row.
-//               Otherwise the lanes append (cell, action, env, td_error) entries, linked inside the
+//               Otherwise the lanes append (cell, action, env, td_target) entries, linked inside the
 //               group, and the leader hooks the sub-chain into the cell's mailbox chain with one
 //               atomicExch.  Then auto-reset, and one saturating count per (warp, next cell) into the
 //               next step's counter.
@@ -129,9 +129,13 @@ __device__ __forceinline__ float max4(float4 r) {
     return m;
 }
 __device__ __forceinline__ float pick(float4 r, int a) { return a == 0 ? r.x : a == 1 ? r.y : a == 2 ? r.z : r.w; }
-__device__ __forceinline__ void fold(float4& r, int a, float lr, float d) {
-    // Q[s,a] <- fma(lr, d, Q[s,a]): what nvcc makes of `q += lr * (target - q)` (src/kernels.cu:114)
-    const float v = __fmaf_rn(lr, d, pick(r, a));
+// One update of Q[s,a] toward `target`: q <- fma(lr, target - q, q), which is what nvcc makes of the reference's
+// `q += lr * (target - q)` (src/kernels.cu:113-114).  Updates of the same (s,a) within a step are applied one
+// after the other in ascending environment id, each seeing the value the previous one left (the targets come
+// from Q_t), so any number of environments on one cell keeps the step a contraction.
+__device__ __forceinline__ void fold(float4& r, int a, float lr, float target) {
+    const float q = pick(r, a);
+    const float v = __fmaf_rn(lr, __fsub_rn(target, q), q);
     r.x = a == 0 ? v : r.x; r.y = a == 1 ? v : r.y; r.z = a == 2 ? v : r.z; r.w = a == 3 ? v : r.w;
 }
 
@@ -282,7 +286,7 @@ __global__ void k_sort_scatter(Params p) {
 }
 // Second half of the sort: inside every key segment of st2 order the records by (cell, id) and write
 // them to st.  Afterwards environments that share a cell sit in consecutive slots in ascending id, which
-// is the order their TD errors are folded in.  Segments longer than RANK_MAX are copied as they are
+// is the order their updates are applied in.  Segments longer than RANK_MAX are copied as they are
 // (still correct, only slower later: such cells take the sorting path of the fold kernel).
 constexpr unsigned RANK_MAX = 4096;
 __global__ void k_sort_rank(Params p) {
@@ -383,7 +387,7 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
             m = max4(row2);
             if (p.legacy_clamp && m < 0.0f) m = 0.0f;
         }
-        d = __fsub_rn(__fmaf_rn(p.gamma, m, r), pick(row, a));
+        d = __fmaf_rn(p.gamma, m, r);                       // the TD target; the error is taken against the running value in fold()
         if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = r; p.tr_d[e] = done ? 1 : 0; }
     }
     // ---- TD update: consecutive lanes of the warp that stand on the same cell form a group -------------
@@ -392,9 +396,9 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
     // every occupant of the cell is in this group <=> the cell's counter equals the group size
     const bool complete = valid && cnt == gsize && gsize < CW_CNT_MAX;
     {
-        // Fold the group's TD errors in ascending environment id.  The slot order is (cell, id) as of the
+        // Apply the group's updates in ascending environment id.  The slot order is (cell, id) as of the
         // last re-ordering, so normally the lanes of a run already are in id order and the run's first lane
-        // simply folds the (action, td_error) pairs its lanes parked in shared memory.  If some complete run
+        // simply applies the (action, td_target) pairs its lanes parked in shared memory.  If some complete run
         // of the warp is out of order (environments met since), every lane first ranks its id inside its run
         // with full-warp shuffles at growing distances and parks its pair at its rank.
         const unsigned gend = gleader + gsize - 1u;
@@ -817,7 +821,7 @@ __global__ void __launch_bounds__(BLOCK) k_eval(Params p, int max_steps, unsigne
 
 __global__ void k_active_reset(Params p) { p.ctl->active_count[p.step & 1ull] = 0; p.ctl->long_count[p.step & 1ull] = 0; }
 
-// update_batch, phase 1: TD error of every transition against the table as it is now; every
+// update_batch, phase 1: TD target of every transition from the table as it is now; every
 // transition becomes a collision entry (index order = fold order).
 __global__ void k_update_main(Params p, unsigned n, const int* sx, const int* sy, const int* act, const float* rew,
                               const int* nxs, const int* nys, const unsigned char* dn) {
@@ -838,8 +842,7 @@ __global__ void k_update_main(Params p, unsigned n, const int* sx, const int* sy
             m = max4(__ldcg(p.Q + 2u * s2 + ((c2 & CW_PAR) ? 1u : 0u)));
             if (p.legacy_clamp && m < 0.0f) m = 0.0f;
         }
-        float target = __fmaf_rn(p.gamma, m, rew[i]);
-        float d = __fsub_rn(target, pick(row, a));
+        float d = __fmaf_rn(p.gamma, m, rew[i]);           // TD target
         slot = mb_slot(p, s);
         unsigned prev = atomicExch(p.mailbox + slot, i + 1u);          // a run of one entry
         p.ent[i] = make_uint4((s << 3) | (par << 2) | (unsigned)a, i, __float_as_uint(d), prev);

@@ -22,9 +22,9 @@
 //     GPU can use).  That first call per device should therefore be made outside any stream
 //     capture.
 //
-// Semantics are those of cudarl_update_batch: every TD error is computed from the table as it was
-// before the call, and updates of one (state, action) are applied as an fp32 fma chain in ascending
-// transition index.  The table is the caller's dense layout, (y*width + x)*4 + a, 16-byte aligned.
+// Semantics are those of cudarl_update_batch: every TD target is computed from the table as it was
+// before the call, and updates of one (state, action) are applied one after the other in ascending
+// transition index, q <- fma(lr, target - q, q).  The table is the caller's dense layout, (y*width + x)*4 + a, 16-byte aligned.
 // Transitions whose state, next state or action is out of range are skipped.
 #include "../../include/cudarl.h"
 #include <cuda_runtime.h>
@@ -89,7 +89,8 @@ __global__ void ks_main(unsigned char* base, const float4* q, int W, int H, unsi
         m = r2.x; m = r2.y > m ? r2.y : m; m = r2.z > m ? r2.z : m; m = r2.w > m ? r2.w : m;
         if (clamp && m < 0.0f) m = 0.0f;
     }
-    float d = __fsub_rn(__fmaf_rn(gamma, m, rew[i]), cur);
+    (void)cur;
+    float d = __fmaf_rn(gamma, m, rew[i]);               // TD target from the untouched table
     unsigned prev = atomicExch(s.head + slot_of(cell), i + 1u);
     s.ent[i] = make_uint4((cell << 2) | a, i, __float_as_uint(d), prev);
 }
@@ -143,7 +144,7 @@ __global__ void ks_fix(unsigned char* base, float* q, float lr, unsigned n) {
     for (j = 0; j < L; ++j) {
         unsigned qi = (unsigned)(k[j] >> 32);                        // (cell << 2) | action == index into the dense table
         if (qi != cur) { if (cur != 0xFFFFFFFFu) q[cur] = acc; cur = qi; acc = q[qi]; }
-        acc = __fmaf_rn(lr, v[j], acc);
+        acc = __fmaf_rn(lr, __fsub_rn(v[j], acc), acc);     // each update sees the value the previous one left
     }
     if (cur != 0xFFFFFFFFu) q[cur] = acc;
 }

@@ -2,8 +2,8 @@
 //
 // Sequential CPU restatement of the batched grid-world step + epsilon-greedy + tabular TD update
 // path of life423/CudaRL-Arena, with the batched semantics of the GPU library (N environments per
-// step, all reads see the table as it was at the start of the step, updates of one (state, action)
-// are folded in ascending environment index).  Only tests, the smoke check and the CPU-baseline
+// step, all TD targets see the table as it was at the start of the step, updates of one (state, action)
+// are applied one after the other in ascending environment index).  Only tests, the smoke check and the CPU-baseline
 // leg of the benchmark may load this file's shared object; the product never does.
 //
 // It is written independently of the CUDA sources (own Philox, own grid generator, own step) so
@@ -255,8 +255,7 @@ void train_step(Oracle& o, float eps) {
             float m = 0.0f;                                  // src/kernels.cu:100-110
             if (!done) { m = max4(&o.q[s2 * 4]); if (c.legacy_clamp && m < 0.0f) m = 0.0f; }
             float target = std::fmaf(c.gamma, m, r);         // src/kernels.cu:113 as nvcc contracts it
-            float d = target - row[a];
-            o.ps[i] = (int32_t)s; o.pa[i] = (uint8_t)a; o.pd[i] = d;
+            o.ps[i] = (int32_t)s; o.pa[i] = (uint8_t)a; o.pd[i] = target;
             o.tr_a[i] = a; o.tr_r[i] = r; o.tr_d[i] = done ? 1 : 0;
             // episode bookkeeping: src/train.py:191-222 (reset on done or after max_steps)
             bool timeout = c.max_steps > 0 && o.t[i] + 1 >= c.max_steps;
@@ -269,12 +268,14 @@ void train_step(Oracle& o, float eps) {
             }
         }
     });
-    // Phase 2: Q[s,a] = fma(lr, d, Q[s,a]) in environment order (src/kernels.cu:114 as compiled;
-    // the reference kernel leaves same-(s,a) collisions to a data race).
+    // Phase 2: the reference update Q[s,a] = fma(lr, target - Q[s,a], Q[s,a]) (src/kernels.cu:113-114 as compiled)
+    // applied one transition after the other in environment order: an update of the same (s,a) sees the value
+    // the previous one left; the targets were taken from Q_t in phase 1.  (The reference kernel leaves
+    // same-(s,a) collisions to a data race.)
     if (o.threads <= 1) {
         for (int64_t i = 0; i < o.N; ++i) {
             float* p = &o.q[(int64_t)o.ps[i] * 4 + o.pa[i]];
-            *p = std::fmaf(c.lr, o.pd[i], *p);
+            *p = std::fmaf(c.lr, o.pd[i] - *p, *p);
         }
     } else {
         // Same fold, split by cell stripe: each thread applies, in environment order, the updates
@@ -287,7 +288,7 @@ void train_step(Oracle& o, float eps) {
             th.emplace_back([&o, &c, clo, chi] {
                 for (int64_t i = 0; i < o.N; ++i) {
                     int64_t s = o.ps[i];
-                    if (s >= clo && s < chi) { float* p = &o.q[s * 4 + o.pa[i]]; *p = std::fmaf(c.lr, o.pd[i], *p); }
+                    if (s >= clo && s < chi) { float* p = &o.q[s * 4 + o.pa[i]]; *p = std::fmaf(c.lr, o.pd[i] - *p, *p); }
                 }
             });
         }
@@ -396,12 +397,12 @@ int orc_update_batch(void* h, int64_t n, const int32_t* sx, const int32_t* sy, c
         int64_t s = (int64_t)sy[i] * o.W + sx[i], s2 = (int64_t)ny[i] * o.W + nx[i];
         float m = 0.0f;
         if (!dn[i]) { m = max4(&o.q[s2 * 4]); if (c.legacy_clamp && m < 0.0f) m = 0.0f; }
-        float target = std::fmaf(c.gamma, m, r[i]);
-        d[i] = target - o.q[s * 4 + a[i]];
+        (void)s;
+        d[i] = std::fmaf(c.gamma, m, r[i]);                 // TD target from the table before the call
     }
     for (int64_t i = 0; i < n; ++i) {
         float* p = &o.q[((int64_t)sy[i] * o.W + sx[i]) * 4 + a[i]];
-        *p = std::fmaf(c.lr, d[i], *p);
+        *p = std::fmaf(c.lr, d[i] - *p, *p);
     }
     return 0;
 }

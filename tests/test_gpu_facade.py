@@ -65,8 +65,8 @@ def test_cuda_q_learning(core):
     assert len(q.get_q_table()) == 96 and max(q.get_q_table()) == 0.0
     q.update_batch([(1, 1), (1, 1), (2, 3)], [2, 2, 0], [1.0, 1.0, -0.01], [(1, 2), (1, 2), (2, 2)], [True, True, False])
     f = np.float32
-    v1 = f(0.5) * f(1.0)
-    v2 = f(np.float64(f(0.5)) * np.float64(f(1.0)) + np.float64(v1))           # second fold sees the first
+    v1 = f(0.5) * f(1.0)                                                         # 0 + 0.5 * (1 - 0)
+    v2 = f(np.float64(f(0.5)) * np.float64(f(1.0) - v1) + np.float64(v1))       # the second update sees the first: 0.75
     assert q.get_q_value(1, 1, 2) == float(v2) and q.get_best_action(1, 1) == 2
     assert q.get_best_action(0, 0) == 0                                          # ties -> lowest index (src/q_learning.cu:196-206)
     with pytest.raises(RuntimeError, match="Inconsistent batch sizes"):

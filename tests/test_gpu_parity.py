@@ -334,3 +334,20 @@ def test_odd_sizes_and_tiny_populations(pkg, orc):
         assert_same(gpu, cpu, "%dx%d n=%d" % (w, h, n))
         a, b = gpu.eval_rollout(20), cpu.eval_rollout(20)
         assert (a.reached, a.total_steps) == (b.reached, b.total_steps)
+
+
+def test_c2_long_run(pkg, orc):
+    """C2 for 10^5 batched steps (4.1e8 environment-steps) in one go: still bit-identical, counters included."""
+    cfg = pkg.preset("C2")
+    gpu, cpu = pair(pkg, orc, cfg, threads=min(8, os.cpu_count() or 1))
+    cpu.count_conflicts(False)
+    for _ in range(4):
+        gpu.train_steps(25000); cpu.train_steps(25000)
+    assert_same(gpu, cpu, "C2 after 1e5 steps")
+    sa, sb = gpu.get_stats(), cpu.get_stats()
+    assert (sa.steps, sa.episodes, sa.goals, sa.timeouts) == (sb.steps, sb.episodes, sb.goals, sb.timeouts)
+    assert sa.device_error == 0 and sa.goals > 100000
+    q = gpu.get_q()
+    assert np.isfinite(q).all() and q.max() <= 1.0 + 1e-6 and q.min() >= -1.0 - 1e-6     # bounded however crowded a cell gets
+    a, b = gpu.eval_rollout(1024), cpu.eval_rollout(1024)
+    assert (a.reached, a.total_steps) == (b.reached, b.total_steps) and a.reached > 3000     # it has learnt the way

@@ -140,7 +140,7 @@ def test_epsilon_decay_matches_reference_python(pkg, orc):
 
 
 def test_collision_fold_order(pkg, orc):
-    """Same (state, action) several times in one batch: fp32 fma chain in index order."""
+    """Same (state, action) several times in one batch: the reference update applied in index order."""
     e = orc.Oracle(pkg.make_config(4, 4, 1, lr=0.5, gamma=0.9))
     q0 = np.linspace(-1, 1, 64).astype(np.float32)
     e.set_q(q0)
@@ -153,14 +153,13 @@ def test_collision_fold_order(pkg, orc):
 
     def fma(x, y, z):
         return f32(np.float64(x) * np.float64(y) + np.float64(z))   # exact product of two fp32 fits fp64; one rounding
-    ds = []
+    targets = []
     for i in range(4):
         m = f32(0) if dn[i] else q0.reshape(16, 4)[ny[i] * 4 + nx[i]].max()
-        target = fma(f32(0.9), m, r[i])
-        ds.append(f32(target - q0.reshape(16, 4)[sy[i] * 4 + sx[i], a[i]]))
-    for i in range(4):
+        targets.append(fma(f32(0.9), m, r[i]))            # targets come from the table before the batch
+    for i in range(4):                                     # applied one after the other: each sees the previous result
         s = sy[i] * 4 + sx[i]
-        q[s, a[i]] = fma(f32(0.5), ds[i], q[s, a[i]])
+        q[s, a[i]] = fma(f32(0.5), f32(targets[i] - q[s, a[i]]), q[s, a[i]])
     assert np.array_equal(e.get_q(), q.reshape(-1))
 
 
