@@ -204,7 +204,7 @@ def main():
     cfg.env_offset = rank * n_local
     window = args.window or (cfg.sync_every if cfg.sync_every > 0 else 256)
     env = pkg.VecGridWorld(cfg)
-    launches_per_step = 3      # k_train_main, k_fix, k_fix_long (+ 6 re-ordering kernels every 8th step)
+    launches_per_step = 4      # k_train_main, k_fix, k_fix_long, k_fix_long2 (+ 6 re-ordering kernels every 8th step)
 
     if args.profile_steps:                      # small fixed run for profilers: no timing, no JSON
         env.train_steps(args.profile_steps)

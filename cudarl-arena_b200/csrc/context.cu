@@ -241,8 +241,8 @@ int alloc_hot(cudarl_ctx* c) {
     CK(cudaMemsetAsync(c->dci, 0, total, c->st));
     c->p.cw = (unsigned short*)c->dci;
     c->p.mailbox = (unsigned*)((char*)c->dci + ci_bytes); c->p.mb_slots = (unsigned)slots; (void)lg;
-    CK(cudaMalloc(&c->dactive, 2 * slots * sizeof(unsigned)));
-    c->p.active = (unsigned*)c->dactive; c->p.longq = (unsigned*)c->dactive + slots;
+    CK(cudaMalloc(&c->dactive, 3 * slots * sizeof(unsigned)));
+    c->p.active = (unsigned*)c->dactive; c->p.longq = (unsigned*)c->dactive + slots; c->p.longq2 = (unsigned*)c->dactive + 2 * slots;
     // L2 persistence (per context, released with it): best effort, a refusal is not an error.
     int dev = c->cfg.device, max_persist = 0, max_window = 0;
     cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev);

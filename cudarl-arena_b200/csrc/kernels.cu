@@ -207,11 +207,13 @@ __global__ void k_ids_identity(Params p) {
     unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < p.N) p.st[i].w = (int)i;
 }
+// The input is nearly ordered already, so neighbouring lanes mostly share a key: one atomic per run of lanes.
 __global__ void k_sort_count(Params p) {
-    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= p.N) return;
-    const int4 r = p.st[i];
-    atomicAdd(p.sort_cnt + sort_key(p, r.x, r.y), 1u);
+    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
+    unsigned key = 0xFFFFFFFFu - lane;
+    if (i < p.N) { const int4 r = p.st[i]; key = sort_key(p, r.x, r.y); }
+    const unsigned m = run_mask(key, lane);
+    if (i < p.N && lane == __ffs(m) - 1u) atomicAdd(p.sort_cnt + key, __popc(m));
 }
 constexpr unsigned SCAN_CHUNK = 4096;      // keys per block of the scan
 // phase 1: per-chunk totals; phase 2 (one block): exclusive scan of the totals; phase 3: exclusive scan inside chunks
@@ -278,12 +280,17 @@ __global__ void __launch_bounds__(BLOCK) k_scan_chunks(Params p) {
     }
 }
 __global__ void k_sort_scatter(Params p) {
-    unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= p.N) return;
-    const int4 r = p.st[i];
-    unsigned pos = atomicAdd(p.sort_cnt + sort_key(p, r.x, r.y), 1u);   // offsets become cursors
-    p.st2[pos] = r;
+    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
+    unsigned key = 0xFFFFFFFFu - lane; int4 r = make_int4(0, 0, 0, 0);
+    if (i < p.N) { r = p.st[i]; key = sort_key(p, r.x, r.y); }
+    const unsigned m = run_mask(key, lane);
+    const unsigned leader = __ffs(m) - 1u;
+    unsigned base = 0;
+    if (i < p.N && lane == leader) base = atomicAdd(p.sort_cnt + key, __popc(m));   // offsets become cursors
+    base = __shfl_sync(FULL, base, leader);
+    if (i < p.N) p.st2[base + (lane - leader)] = r;
 }
+
 // Second half of the sort: inside every key segment of st2 order the records by (cell, id) and write
 // them to st.  Afterwards environments that share a cell sit in consecutive slots in ascending id, which
 // is the order their updates are applied in.  Segments longer than RANK_MAX are copied as they are
@@ -347,7 +354,7 @@ __global__ void __launch_bounds__(BLOCK, 8) k_train_main(Params p) {
     const unsigned i = blockIdx.x * BLOCK + threadIdx.x;
     const unsigned lane = threadIdx.x & 31u;
     const unsigned lt = (1u << lane) - 1u;                              // lanes below mine
-    if (blockIdx.x == 0 && threadIdx.x == 0) { p.ctl->scratch_cursor = 0; p.ctl->active_count[(p.step + 1ull) & 1ull] = 0; p.ctl->long_count[(p.step + 1ull) & 1ull] = 0; }   // nobody reads these in this kernel
+    if (blockIdx.x == 0 && threadIdx.x == 0) { p.ctl->scratch_cursor = 0; p.ctl->active_count[(p.step + 1ull) & 1ull] = 0; p.ctl->long_count[(p.step + 1ull) & 1ull] = 0; p.ctl->long2_count[(p.step + 1ull) & 1ull] = 0; }   // nobody reads these in this kernel
     const bool valid = i < p.N;
     const unsigned long long g = p.step;
     const unsigned shc = cnt_shift(g), shn = cnt_shift(g + 1ull);
@@ -640,7 +647,7 @@ __device__ void process_medium(const Params& p, unsigned long long* keys, float*
 // the chain's entries:
 //   <= 8 entries   in registers, ordered by a sorting network and folded by that thread;
 //   <= 32 entries  staged in shared memory by that thread, ordered and folded by one warp;
-//   longer         queued for k_fix_long, where one block per chain sorts it.
+//   longer         queued for k_fix_long (one warp per chain up to 256 entries, then one block per chain).
 // TRAIN = true : part of a train step -- also sweeps the cell words (parity ^= occupied, consumed
 //                counter cleared).
 // TRAIN = false: update_batch -- flips the row parity of every folded cell instead.
@@ -755,17 +762,74 @@ __global__ void __launch_bounds__(BLOCK) k_fix(Params p) {
     }
 }
 
-// Long chains (more than 32 entries: cells crowded with environments), one block per chain, spread over
-// the whole GPU: the runs are listed by one thread (one hop per run), copied by all threads, sorted by a
-// block-wide bitonic sort (shared memory up to 1024 entries, the global scratch beyond) and folded.
+// Long chains (more than 32 entries: cells crowded with environments).  First tier: one WARP per chain for up
+// to 256 entries -- lane 0 hops from run to run, all lanes copy the run's entries into the warp's slice of
+// shared memory, a warp-wide bitonic sort orders them by (cell, action, id), the first lane of every cell run
+// applies it.  Chains that do not fit are queued for k_fix_long2 (one block per chain).
+constexpr unsigned WARP_LONG = 256;
+
+template <bool FLIP>
+__device__ bool process_long_warp(const Params& p, unsigned head, unsigned long long* keys, float* vals) {
+    const unsigned lane = threadIdx.x & 31u;
+    unsigned q = head, L = 0, hops = 0; bool fits = true;
+    while (q && hops <= p.ent_cap) {                  // q is warp-uniform
+        const unsigned pos0 = (q & LINK_POS_MASK) - 1u, len = (q >> LINK_POS_BITS) + 1u;
+        if (L + len > WARP_LONG) { fits = false; break; }
+        uint4 e = make_uint4(0u, 0u, 0u, 0u);
+        if (lane < len) { e = __ldcg(p.ent + pos0 + lane); keys[L + lane] = ((unsigned long long)e.x << 32) | e.y; vals[L + lane] = __uint_as_float(e.z); }
+        q = __shfl_sync(FULL, e.w, 0);                // the run's first entry carries the link to the next run
+        L += len; ++hops;
+    }
+    if (!fits || q) return false;
+    unsigned n2 = 32; while (n2 < L) n2 <<= 1;
+    for (unsigned i = L + lane; i < n2; i += 32u) { keys[i] = ~0ull; vals[i] = 0.0f; }
+    __syncwarp();
+    for (unsigned k = 2; k <= n2; k <<= 1) {
+        for (unsigned j = k >> 1; j > 0; j >>= 1) {
+            for (unsigned i = lane; i < n2; i += 32u) {
+                const unsigned ixj = i ^ j;
+                if (ixj > i) {
+                    const unsigned long long a = keys[i], b = keys[ixj];
+                    const bool up = (i & k) == 0;
+                    if ((a > b) == up) { keys[i] = b; keys[ixj] = a; const float t = vals[i]; vals[i] = vals[ixj]; vals[ixj] = t; }
+                }
+            }
+            __syncwarp();
+        }
+    }
+    for (unsigned j = lane; j < L; j += 32u) {
+        const unsigned cp = (unsigned)(keys[j] >> 34);
+        if (j == 0 || (unsigned)(keys[j - 1] >> 34) != cp) apply_run<FLIP>(p, keys, vals, j, L);
+    }
+    __syncwarp();
+    return true;
+}
+
 template <bool FLIP>
 __global__ void __launch_bounds__(BLOCK) k_fix_long(Params p) {
+    __shared__ unsigned long long s_keys[(BLOCK / 32) * WARP_LONG];
+    __shared__ float s_vals[(BLOCK / 32) * WARP_LONG];
+    const unsigned n = p.ctl->long_count[p.step & 1ull];
+    const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    unsigned done = 0;
+    for (unsigned c = blockIdx.x * (BLOCK / 32) + warp; c < n; c += gridDim.x * (BLOCK / 32)) {
+        const unsigned head = p.longq[c];
+        if (!process_long_warp<FLIP>(p, head, s_keys + warp * WARP_LONG, s_vals + warp * WARP_LONG)) {
+            if (lane == 0) p.longq2[atomicAdd(&p.ctl->long2_count[p.step & 1ull], 1u)] = head;
+        }
+        ++done;
+    }
+    if (lane == 0 && done) atomicAdd(&p.ctl->long_chains, (unsigned long long)done);
+}
+
+// Second tier: one block per chain, any length (shared memory up to 1024 entries, the global scratch beyond).
+template <bool FLIP>
+__global__ void __launch_bounds__(BLOCK) k_fix_long2(Params p) {
     __shared__ unsigned long long s_keys[LONG_SMEM];
     __shared__ float s_vals[LONG_SMEM];
     __shared__ unsigned s_bcast[3];
-    const unsigned n = p.ctl->long_count[p.step & 1ull];
-    for (unsigned c = blockIdx.x; c < n; c += gridDim.x) process_long<FLIP>(p, p.longq[c], s_keys, s_vals, s_bcast);
-    if (blockIdx.x == 0 && threadIdx.x == 0 && n) atomicAdd(&p.ctl->long_chains, (unsigned long long)n);
+    const unsigned n = p.ctl->long2_count[p.step & 1ull];
+    for (unsigned c = blockIdx.x; c < n; c += gridDim.x) process_long<FLIP>(p, p.longq2[c], s_keys, s_vals, s_bcast);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -819,7 +883,7 @@ __global__ void __launch_bounds__(BLOCK) k_eval(Params p, int max_steps, unsigne
     }
 }
 
-__global__ void k_active_reset(Params p) { p.ctl->active_count[p.step & 1ull] = 0; p.ctl->long_count[p.step & 1ull] = 0; }
+__global__ void k_active_reset(Params p) { p.ctl->active_count[p.step & 1ull] = 0; p.ctl->long_count[p.step & 1ull] = 0; p.ctl->long2_count[p.step & 1ull] = 0; }
 
 // update_batch, phase 1: TD target of every transition from the table as it is now; every
 // transition becomes a collision entry (index order = fold order).
@@ -950,6 +1014,7 @@ void launch_train_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t
     if (ev_b) cudaEventRecord(ev_b, st);
     k_fix<true><<<fix_blocks(p), BLOCK, 0, st>>>(p);
     k_fix_long<false><<<296, BLOCK, 0, st>>>(p);
+    k_fix_long2<false><<<296, BLOCK, 0, st>>>(p);
     if (p.eps_from_ctl) k_eps_episode<<<1, 1, 0, st>>>(p);
     if (ev_c) cudaEventRecord(ev_c, st);
 }
@@ -966,6 +1031,7 @@ void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* 
     k_update_main<<<nblk(n), BLOCK, 0, st>>>(p, n, sx, sy, a, r, nx, ny, dn);
     k_fix<false><<<fix_blocks(p), BLOCK, 0, st>>>(p);
     k_fix_long<true><<<296, BLOCK, 0, st>>>(p);
+    k_fix_long2<true><<<296, BLOCK, 0, st>>>(p);
     k_active_reset<<<1, 1, 0, st>>>(p);      // a following train step starts from an empty list
 }
 void launch_q_gather(const Params& p, float4* dense, cudaStream_t st) { k_q_gather<<<nblk(p.S), BLOCK, 0, st>>>(p, dense); }

@@ -33,7 +33,8 @@ struct Ctl {
     unsigned int eps_len;           // table length (clamp)
     unsigned long long eps_base_k;  // per-episode mode: table[0] belongs to episodes/N == eps_base_k
     unsigned int active_count[2];   // mailbox slots holding a chain, per step parity
-    unsigned int long_count[2];     // chains queued for the block-per-chain kernel, per step parity
+    unsigned int long_count[2];     // chains queued for the warp-per-chain kernel, per step parity
+    unsigned int long2_count[2];    // chains too long for a warp, queued for the block-per-chain kernel
     unsigned int scratch_cursor;    // bump allocator of the long-chain scratch, reset every step
     unsigned int blocks_done;       // last-block detection of the fix kernel
     unsigned int error;             // sticky internal error bits
@@ -68,7 +69,8 @@ struct Params {
     unsigned* mailbox;     // chain heads (0 = empty), power-of-two size
     unsigned mb_slots;     // mailbox slots (power of two, multiple of BLOCK)
     unsigned* active;      // list of the mailbox slots that hold a chain in this step (mb_slots entries)
-    unsigned* longq;       // heads of the chains left to the block-per-chain kernel (mb_slots entries)
+    unsigned* longq;       // heads of the chains left to the warp-per-chain kernel (mb_slots entries)
+    unsigned* longq2;      // heads of the chains left to the block-per-chain kernel (mb_slots entries)
     Ctl* ctl;
     const float* eps_tab;
     int* tr_a; float* tr_r; unsigned char* tr_d;   // optional trace of the last step, per ENVIRONMENT
