@@ -179,6 +179,32 @@ def preset(name, num_envs=None, env_offset=0, device=0, seed=0xC0DA2025):
     return c
 
 
+def q_to_reference_layout(q, width, height):
+    """Table as the reference's Python agent stores and saves it (src/train.py:63,150-168): float64, shape
+    (width, height, 4), indexed [x, y, a].  Input: the native fp32 layout (y*width + x)*4 + a."""
+    return np.ascontiguousarray(np.asarray(q, np.float32).reshape(height, width, 4).transpose(1, 0, 2)).astype(np.float64)
+
+
+def q_from_reference_layout(q_xya):
+    """Inverse of q_to_reference_layout: (width, height, 4) indexed [x, y, a] -> native fp32 vector."""
+    q = np.asarray(q_xya)
+    assert q.ndim == 3 and q.shape[2] == 4
+    return np.ascontiguousarray(q.transpose(1, 0, 2)).astype(np.float32).reshape(-1)
+
+
+def save_q_npy(path, world):
+    """Write the table of a VecGridWorld as the .npy file QTableAgent.save of the reference produces."""
+    np.save(path, q_to_reference_layout(world.get_q(), world.W, world.H))
+
+
+def load_q_npy(path, world):
+    """Load a .npy written by the reference's QTableAgent.save (or save_q_npy) into a VecGridWorld."""
+    q = np.load(path)
+    if q.shape != (world.W, world.H, 4):
+        raise ValueError("table shape %r does not match a %dx%d grid with 4 actions" % (q.shape, world.W, world.H))
+    world.set_q(q_from_reference_layout(q))
+
+
 class CudarlError(RuntimeError):
     def __init__(self, code, msg):
         super().__init__("cudarl error %d: %s" % (code, msg))

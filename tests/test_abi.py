@@ -47,3 +47,25 @@ def test_create_rejects_bad_arguments(pkg):
     c.width = 0
     assert lib.cudarl_create(ctypes.byref(c), ctypes.byref(h)) < 0
     assert not h.value
+
+
+def test_reference_checkpoint_layout_roundtrip(pkg, tmp_path):
+    """.npy interop with QTableAgent.save/load of the reference (src/train.py:150-168): float64 (W,H,A) [x,y,a]."""
+    import numpy as np
+    w, h = 7, 5
+    native = np.arange(w * h * 4, dtype=np.float32) * 0.25
+    ref = pkg.q_to_reference_layout(native, w, h)
+    assert ref.shape == (w, h, 4) and ref.dtype == np.float64
+    for x, y, a in [(0, 0, 0), (6, 4, 3), (3, 2, 1)]:
+        assert ref[x, y, a] == native[(y * w + x) * 4 + a]
+    assert np.array_equal(pkg.q_from_reference_layout(ref), native)
+
+    class FakeWorld:
+        W, H = w, h
+        def get_q(self): return native
+        def set_q(self, q): self.got = q
+    fw = FakeWorld()
+    path = str(tmp_path / "qtable_agent.npy")
+    pkg.save_q_npy(path, fw)
+    pkg.load_q_npy(path, fw)
+    assert np.array_equal(fw.got, native)
