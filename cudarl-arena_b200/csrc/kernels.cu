@@ -1045,12 +1045,4 @@ void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goa
     k_cell_set<<<clear_goals ? sweep_blocks(p.S) : 1, BLOCK, 0, st>>>(p, cell, cls, clear_goals);
 }
 
-int kernel_attr_report(char* buf, int n) {
-    cudaFuncAttributes a, b;
-    if (cudaFuncGetAttributes(&a, k_train_main<false>) != cudaSuccess) return -1;
-    if (cudaFuncGetAttributes(&b, k_fix<true>) != cudaSuccess) return -1;
-    return snprintf(buf, n, "train_main: %d regs, %zu B smem; train_fix: %d regs, %zu B smem",
-                    a.numRegs, a.sharedSizeBytes, b.numRegs, b.sharedSizeBytes);
-}
-
 }  // namespace cudarl

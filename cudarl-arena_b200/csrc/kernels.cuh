@@ -107,6 +107,5 @@ void launch_q_gather_range(const Params& p, float4* dense, unsigned cell0, unsig
 void launch_q_average(const Params& p, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale, cudaStream_t st);
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st);
 void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st);
-int  kernel_attr_report(char* buf, int n);
 
 }  // namespace cudarl
