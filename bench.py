@@ -284,7 +284,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one k_train_main launch on this workload, from the ncu
                      # capture summarised in profiles/k_train_main_C5.md (not measured by this run)
-                     "traffic": 567.1e6 if (args.config == "C5" and not args.envs) else None,
+                     "traffic": 574.1e6 if (args.config == "C5" and not args.envs) else None,
                      "peak_kind": peak_kind, "kernel": "k_train_main", "algorithmic_bytes_per_env_step": ALGO_BYTES_TRAIN,
                      "main_kernel_us": main_avg_s * 1e6, "fix_kernel_us": fix_avg_s * 1e6,
                      "whole_step_frac": ALGO_BYTES_TRAIN * n_local / (ms * 1e-3 / (args.steps * window)) / 1e9 / peak},
