@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generate tests/golden/*.npz from the reference's OWN Python CPU code.
 
-Run where the reference checkout exists (default /root/reference, or CUDARL_REFERENCE=<path>):
+Run where a checkout of the reference project exists (CUDARL_REFERENCE=<path> selects it):
 
     python tests/golden/make_golden.py
 
