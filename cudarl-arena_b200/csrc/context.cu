@@ -234,7 +234,8 @@ int ensure_entry_capacity(cudarl_ctx* c, size_t cap) {
 int alloc_hot(cudarl_ctx* c) {
     const size_t S = c->p.S, N = c->p.N ? c->p.N : 1;
     const size_t ci_bytes = (2 * S + 255) / 256 * 256;      // one 16-bit word per cell
-    size_t slots = pow2ceil(N); if (slots < (1u << 16)) slots = 1u << 16; if (slots > (1u << 24)) slots = 1u << 24;
+    // one slot per two environments: chains stay short, and every MiB taken from the L2 window is a MiB more for table rows
+    size_t slots = pow2ceil(N) / 2; if (slots < (1u << 16)) slots = 1u << 16; if (slots > (1u << 24)) slots = 1u << 24;
     unsigned lg = 0; while ((1ull << lg) < slots) ++lg;
     const size_t total = ci_bytes + slots * sizeof(unsigned);
     CK(cudaMalloc(&c->dci, total));
