@@ -52,8 +52,8 @@ def _run(cmd, log=None):
 
 
 def build_lib(force=False):
-    srcs = [os.path.join(CSRC, f) for f in ("kernels.cu", "context.cu", "update_static.cu", "facade.cpp")]
-    deps = srcs + [os.path.join(CSRC, "kernels.cuh"), os.path.join(CSRC, "facade.h"), os.path.join(ROOT, "include", "cudarl.h")]
+    srcs = [os.path.join(CSRC, f) for f in ("kernels.cu", "tile_engine.cu", "context.cu", "update_static.cu", "facade.cpp")]
+    deps = srcs + [os.path.join(CSRC, "kernels.cuh"), os.path.join(CSRC, "rules.cuh"), os.path.join(CSRC, "facade.h"), os.path.join(ROOT, "include", "cudarl.h")]
     deps = [d for d in deps if os.path.exists(d)]
     srcs = [s for s in srcs if os.path.exists(s)]
     if not force and _newer(LIB, deps):

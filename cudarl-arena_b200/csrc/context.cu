@@ -78,6 +78,12 @@ struct cudarl_ctx {
     void *dstate[2] = {nullptr, nullptr};   // int4 {x,y,t,id} per slot: two copies (sort target / export scratch)
     void *dimport = nullptr;              // staging for caller state arrays (3 x N int32)
     void *dsortcnt = nullptr, *dsortblk = nullptr, *dactive = nullptr;
+    // tile engine (the layout the train step runs on)
+    void *dQd[2] = {nullptr, nullptr}, *drec[2] = {nullptr, nullptr}, *dovf[2] = {nullptr, nullptr};
+    void *dtmeta = nullptr, *dtscratch = nullptr, *dtcls = nullptr;   // per-tile offsets / capacities / counters; fold entries of crowded tiles
+    bool tile_mode = false;               // true: records live in tile regions and the table in Qd[h_step & 1]
+    bool legacy_engine = true;
+    int64_t bucket_every = 32, since_bucket = 0;
     int cur = 0;                          // which copy of the state is live
     bool slots_identity = true;           // id[k] == k
     int64_t sort_every = 8, since_sort = 0;
@@ -331,6 +337,76 @@ int drain_kernel_events(cudarl_ctx* c) {
     return 0;
 }
 
+
+// ---- tile engine: buffers, entering and leaving the tile layout ------------------------------------
+// Tile edge: the largest of 32 / 16 / 8 cells that still gives every SM several tiles and keeps the
+// average tile population within what a block sorts in shared memory.
+int alloc_tiles(cudarl_ctx* c) {
+    Params& p = c->p; TileP& tp = p.tp;
+    const size_t S = p.S, N = p.N ? p.N : 1;
+    unsigned tsh = 3;
+    for (unsigned cand = 5; cand >= 3; --cand) {
+        const size_t nt = (((size_t)p.W + (1u << cand) - 1) >> cand) * (((size_t)p.H + (1u << cand) - 1) >> cand);
+        if (nt >= 592 && N / nt <= 768) { tsh = cand; break; }
+    }
+    if (const char* ev = getenv("CUDARL_TILE_SHIFT")) { int v = atoi(ev); if (v >= 2 && v <= 6) tsh = (unsigned)v; }
+    tp.tshift = tsh; tp.T = 1u << tsh;
+    tp.tiles_x = (unsigned)((p.W + (int)tp.T - 1) >> tsh); tp.tiles_y = (unsigned)((p.H + (int)tp.T - 1) >> tsh);
+    tp.ntiles = tp.tiles_x * tp.tiles_y;
+    tp.ch = 1024;       // = entries per thread x threads of the step kernel
+    for (int k = 0; k < 2; ++k) {
+        CK(cudaMalloc(&c->dQd[k], S * sizeof(float4)));
+        CK(cudaMalloc(&c->drec[k], (N + N / 2 + 96 * (size_t)tp.ntiles + 64) * sizeof(int4)));
+        CK(cudaMalloc(&c->dovf[k], N * sizeof(int4)));
+        tp.Qd[k] = (float4*)c->dQd[k]; tp.rec[k] = (int4*)c->drec[k]; tp.ovf[k] = (int4*)c->dovf[k];
+    }
+    const size_t nt = tp.ntiles, meta = (nt + 1) + nt + 4 * nt + 8;
+    CK(cudaMalloc(&c->dtmeta, meta * sizeof(unsigned)));
+    CK(cudaMemsetAsync(c->dtmeta, 0, meta * sizeof(unsigned), c->st));
+    unsigned* m = (unsigned*)c->dtmeta;
+    tp.reg_off = m; m += nt + 1; tp.front_cap = m; m += nt;
+    tp.seg_cnt[0] = m; m += nt; tp.seg_cnt[1] = m; m += nt; tp.arr_cnt[0] = m; m += nt; tp.arr_cnt[1] = m; m += nt;
+    tp.tctl = m;
+    tp.cls_stride = (unsigned)((((size_t)tp.T + 2) * (tp.T + 2) + 15) / 16 * 16);
+    CK(cudaMalloc(&c->dtcls, nt * tp.cls_stride));
+    tp.tcls = (unsigned char*)c->dtcls;
+    CK(cudaMalloc(&c->dtscratch, N * sizeof(uint2)));
+    tp.scratch = (uint2*)c->dtscratch;
+    if (tile_engine_configure(p) != 0) { cudaGetLastError(); return fail(c, -5, "tile step: shared memory request refused"); }
+    return 0;
+}
+
+// canonical layout (records in slot order, 32-byte table rows with a parity bit) -> tile layout
+int enter_tiles(cudarl_ctx* c) {
+    if (c->tile_mode) return 0;
+    c->p.step = (unsigned long long)c->h_step;
+    launch_q_gather(c->p, c->p.tp.Qd[c->h_step & 1], c->st);
+    launch_tile_classes(c->p, c->st);
+    launch_tile_bucket(c->p, c->st);
+    CK(cudaGetLastError());
+    c->tile_mode = true; c->since_bucket = 0;
+    return 0;
+}
+// tile layout -> canonical layout, records back in environment order
+int leave_tiles(cudarl_ctx* c) {
+    if (!c->tile_mode) return 0;
+    c->p.step = (unsigned long long)c->h_step;
+    launch_tile_export(c->p, c->st);
+    launch_q_scatter(c->p, c->p.tp.Qd[c->h_step & 1], 1.0f, c->st);
+    CK(cudaGetLastError());
+    c->tile_mode = false; c->slots_identity = true; c->occ_valid = false;
+    return 0;
+}
+// re-size the tile regions from the current populations (records only; the table stays where it is)
+int rebucket_tiles(cudarl_ctx* c) {
+    c->p.step = (unsigned long long)c->h_step;
+    launch_tile_export(c->p, c->st);
+    launch_tile_bucket(c->p, c->st);
+    CK(cudaGetLastError());
+    c->slots_identity = true; c->since_bucket = 0;
+    return 0;
+}
+
 // Q <- (Q_0 + Q_1 + ... + Q_{R-1}) * (1/R), summed in rank order on every GPU.  The rows travel with an
 // NCCL all-gather in chunks (NVLink / NVSwitch); the reduction itself is our kernel, so the result is the
 // same bits on every rank and the same bits as the CPU oracle for any R (an all-reduce would leave the
@@ -343,6 +419,16 @@ int average_now(cudarl_ctx* c) {
         CK(cudaMalloc(&c->dgather, R * chunk * sizeof(float4)));
         CK(cudaMalloc(&c->dsend, chunk * sizeof(float4)));
     }
+    if (c->tile_mode) {                       // the dense table is contiguous: rows go out as they lie
+        float4* table = c->p.tp.Qd[c->h_step & 1];
+        for (size_t c0 = 0; c0 < S; c0 += chunk) {
+            const size_t n = S - c0 < chunk ? S - c0 : chunk;
+            NK(g_nccl.AllGather(table + c0, c->dgather, n * 4, ncclFloat, c->comm, c->st));
+            launch_q_average_dense(c->p, table, (const float4*)c->dgather, (unsigned)R, (unsigned)c0, (unsigned)n, 1.0f / (float)R, c->st);
+        }
+        CK(cudaGetLastError());
+        return 0;
+    }
     for (size_t c0 = 0; c0 < S; c0 += chunk) {
         const size_t n = S - c0 < chunk ? S - c0 : chunk;
         launch_q_gather_range(c->p, (float4*)c->dsend, (unsigned)c0, (unsigned)n, c->st);
@@ -354,19 +440,23 @@ int average_now(cudarl_ctx* c) {
 }
 
 int run_steps(cudarl_ctx* c, int64_t n) {
+    if (!c->legacy_engine) { int re = enter_tiles(c); if (re) return re; }
+    else { int ro = ensure_occupancy(c); if (ro) return ro; }
     for (int64_t k = 0; k < n; ++k) {
         cudaEvent_t a = nullptr, b = nullptr, d = nullptr;
         if (c->ktiming) {
             if (c->kev_used + 3 > c->kev.size()) { int rc = drain_kernel_events(c); if (rc) return rc; }
             a = c->kev[c->kev_used]; b = c->kev[c->kev_used + 1]; d = c->kev[c->kev_used + 2]; c->kev_used += 3;
         }
-        if (c->sort_every > 0 && c->since_sort >= c->sort_every) { int rs = sort_slots(c); if (rs) return rs; }
+        if (c->legacy_engine) { if (c->sort_every > 0 && c->since_sort >= c->sort_every) { int rs = sort_slots(c); if (rs) return rs; } }
+        else if (c->bucket_every > 0 && c->since_bucket >= c->bucket_every) { int rs = rebucket_tiles(c); if (rs) return rs; }
         c->p.step = (unsigned long long)c->h_step;
         c->p.eps_idx = c->eps_mode == 1 ? (unsigned)k : 0u;
         c->p.eps_from_ctl = c->eps_mode == 2 ? 1 : 0;
         if (c->eps_mode != 2 && c->h_eps) c->eps_used = c->h_eps[c->p.eps_idx];
-        launch_train_step(c->p, c->trace, c->st, a, b, d);
-        c->h_step += 1; c->since_sort += 1;
+        if (c->legacy_engine) launch_train_step(c->p, c->trace, c->st, a, b, d);
+        else launch_tile_step(c->p, c->trace, c->st, a, b, d);
+        c->h_step += 1; c->since_sort += 1; c->since_bucket += 1;
         if (c->cfg.sync_every > 0 && c->comm && (c->h_step % c->cfg.sync_every) == 0) { int rc = average_now(c); if (rc) return rc; }
     }
     CK(cudaGetLastError());
@@ -378,7 +468,8 @@ void free_all(cudarl_ctx* c) {
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     void* bufs[] = {c->dQ, c->dci, c->dstate[0], c->dstate[1], c->dimport, c->dsortcnt, c->dsortblk, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->ddense, c->dgather, c->dsend, c->dact,
-                    c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6]};
+                    c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6],
+                    c->dQd[0], c->dQd[1], c->drec[0], c->drec[1], c->dovf[0], c->dovf[1], c->dtmeta, c->dtscratch, c->dtcls};
     for (void* b : bufs) if (b) cudaFree(b);
     if (c->h_eps) cudaFreeHost(c->h_eps);
     for (auto e : c->kev) cudaEventDestroy(e);
@@ -449,6 +540,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             p.Q = (float4*)c->dQ; bind_state(c); p.sort_cnt = (unsigned*)c->dsortcnt; p.sort_blk = (unsigned*)c->dsortblk;
             p.ctl = (Ctl*)c->dctl;
             int r2 = ensure_entry_capacity(c, N); if (r2) return r2;
+            r2 = alloc_tiles(c); if (r2) return r2;
             r2 = upload_cells(c); if (r2) return r2;
             launch_q_init(p, f->q_init_kind, f->q_init_scale, c->st);
             float e0 = (float)f->eps0; r2 = upload_eps(c, &e0, 1); if (r2) return r2;
@@ -461,6 +553,9 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
         };
         c->sort_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 8);
         if (const char* ev = getenv("CUDARL_SORT_EVERY")) c->sort_every = atoll(ev);
+        c->bucket_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 32);
+        if (const char* ev = getenv("CUDARL_BUCKET_EVERY")) c->bucket_every = atoll(ev);
+        if (const char* ev = getenv("CUDARL_ENGINE")) c->legacy_engine = std::strcmp(ev, "tile") != 0;
         rc = body();
     } while (0);
     if (rc) { g_err = c->err; free_all(c); delete c; return rc; }
@@ -483,6 +578,7 @@ int cudarl_synchronize(cudarl_ctx* c) { if (!c) return -1; CK(cudaStreamSynchron
 int cudarl_reset_all(cudarl_ctx* c) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     c->p.step = (unsigned long long)c->h_step;
     launch_reset_all(c->p, c->st);
     CK(cudaGetLastError());
@@ -493,6 +589,7 @@ int cudarl_reset_all(cudarl_ctx* c) {
 int cudarl_step_actions_device(cudarl_ctx* c, const int32_t* d_actions, float* d_rewards, uint8_t* d_dones) {
     if (!c || !d_actions) return fail(c, -1, "null argument");
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     int rc = ensure_step_buffers(c); if (rc) return rc;
     launch_step_actions(c->p, d_actions, d_rewards, d_dones, c->st);
     CK(cudaGetLastError());
@@ -503,6 +600,7 @@ int cudarl_step_actions_device(cudarl_ctx* c, const int32_t* d_actions, float* d
 int cudarl_step_actions(cudarl_ctx* c, const int32_t* actions, float* rewards, uint8_t* dones) {
     if (!c || !actions) return fail(c, -1, "null argument");
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     int rc = ensure_step_buffers(c); if (rc) return rc;
     const size_t N = c->p.N;
     CK(cudaMemcpyAsync(c->dact, actions, N * sizeof(int), cudaMemcpyHostToDevice, c->st));
@@ -529,7 +627,7 @@ int cudarl_train_steps(cudarl_ctx* c, int64_t n) {
     if (!c || n < 0) return fail(c, -1, "bad argument");
     if (n == 0 || c->p.N == 0) return 0;
     CK(cudaSetDevice(c->cfg.device));
-    int rc = ensure_occupancy(c); if (rc) return rc;
+    int rc = 0;
     const cudarl_config& f = c->cfg;
     if (f.eps_kind == CUDARL_EPS_FIXED) {
         if (!c->eps_fixed_valid) {
@@ -570,8 +668,7 @@ int cudarl_train_steps_eps(cudarl_ctx* c, int64_t n, const float* eps_host) {
     if (!c || n < 0 || (n > 0 && !eps_host)) return fail(c, -1, "bad argument");
     if (n == 0 || c->p.N == 0) return 0;
     CK(cudaSetDevice(c->cfg.device));
-    int rc = ensure_occupancy(c); if (rc) return rc;
-    rc = upload_eps(c, eps_host, (size_t)n); if (rc) return rc;
+    int rc = upload_eps(c, eps_host, (size_t)n); if (rc) return rc;
     k_ctl_eps<<<1, 1, 0, c->st>>>(c->p.ctl, 1u, (unsigned)n, 0ull);
     c->eps_mode = 1;
     return run_steps(c, n);
@@ -602,6 +699,7 @@ int cudarl_get_trace(cudarl_ctx* c, int32_t* a, float* r, uint8_t* d) {
 int cudarl_eval_rollout(cudarl_ctx* c, int32_t max_steps, cudarl_eval_stats* out) {
     if (!c || !out || max_steps < 0) return fail(c, -1, "bad argument");
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     k_ctl_eval_clear<<<1, 1, 0, c->st>>>(c->p.ctl);
     launch_eval(c->p, max_steps, (unsigned long long)c->eval_calls, c->st);
     CK(cudaGetLastError());
@@ -624,6 +722,7 @@ int cudarl_update_batch(cudarl_ctx* c, int64_t n, const int32_t* sx, const int32
         if (sx[i] < 0 || sx[i] >= W || sy[i] < 0 || sy[i] >= H || a[i] < 0 || a[i] >= CUDARL_ACTIONS ||
             nx[i] < 0 || nx[i] >= W || ny[i] < 0 || ny[i] >= H) return fail(c, -3, "Invalid state or action");
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     int rc = ensure_entry_capacity(c, (size_t)n); if (rc) return rc;
     if ((size_t)n > c->ub_cap) {
         CK(cudaStreamSynchronize(c->st));
@@ -646,6 +745,7 @@ int cudarl_update_batch(cudarl_ctx* c, int64_t n, const int32_t* sx, const int32
 int cudarl_get_state(cudarl_ctx* c, int32_t* x, int32_t* y, int32_t* t) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     const size_t b = (size_t)c->p.N * 4;
     // state lives in slot order as int4 records; the export kernel writes x[N] | y[N] | t[N] in
     // environment order into the spare copy
@@ -664,6 +764,7 @@ int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const in
     if (x) for (size_t i = 0; i < N; ++i) if (x[i] < 0 || x[i] >= c->p.W) return fail(c, -3, "Invalid state");
     if (y) for (size_t i = 0; i < N; ++i) if (y[i] < 0 || y[i] >= c->p.H) return fail(c, -3, "Invalid state");
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     { int rn = normalize_slots(c); if (rn) return rn; }
     if (!c->dimport) CK(cudaMalloc(&c->dimport, (N ? N : 1) * 12));
     int* dx = (int*)c->dimport; int* dy = dx + N; int* dt = dy + N;
@@ -680,6 +781,7 @@ int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const in
 int cudarl_get_q(cudarl_ctx* c, float* q) {
     if (!c || !q) return fail(c, -1, "null argument");
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     int rc = ensure_dense(c); if (rc) return rc;
     launch_q_gather(c->p, (float4*)c->ddense, c->st);
     CK(cudaGetLastError());
@@ -690,6 +792,7 @@ int cudarl_get_q(cudarl_ctx* c, float* q) {
 int cudarl_set_q(cudarl_ctx* c, const float* q) {
     if (!c || !q) return fail(c, -1, "null argument");
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     int rc = ensure_dense(c); if (rc) return rc;
     CK(cudaMemcpyAsync(c->ddense, q, (size_t)c->p.S * sizeof(float4), cudaMemcpyHostToDevice, c->st));
     launch_q_scatter(c->p, (const float4*)c->ddense, 1.0f, c->st);
@@ -708,6 +811,7 @@ static int set_cell(cudarl_ctx* c, int32_t x, int32_t y, unsigned cls, bool sing
     if (!c) return -1;
     if (x < 0 || x >= c->p.W || y < 0 || y >= c->p.H) return fail(c, -3, "Invalid state");
     CK(cudaSetDevice(c->cfg.device));
+    { int rl = leave_tiles(c); if (rl) return rl; }
     const unsigned cell = (unsigned)y * (unsigned)c->p.W + (unsigned)x;
     if (single_goal) {
         for (auto& v : c->cells) if (v == 2) v = 0;

@@ -41,7 +41,30 @@ struct Ctl {
     float eps_used;                 // epsilon of the most recent step (for the stats call)
 };
 
-enum : unsigned { ERR_SCRATCH_OVERFLOW = 1u, ERR_BAD_STATE = 2u, ERR_BAD_TRANSITION = 4u, ERR_CHAIN_CYCLE = 8u, ERR_CAS_LIMIT = 16u };
+enum : unsigned { ERR_SCRATCH_OVERFLOW = 1u, ERR_BAD_STATE = 2u, ERR_BAD_TRANSITION = 4u, ERR_CHAIN_CYCLE = 8u, ERR_CAS_LIMIT = 16u, ERR_COPY_TIMEOUT = 32u };
+
+// ---- tile engine (tile_engine.cu): the layout the train step runs on ---------------------------
+// The grid is cut into T x T tiles.  Every tile owns a REGION of the record array: a front part that
+// only the tile's own block writes (environments that stay) and a back part that other blocks append
+// to with an atomic cursor (environments that walk or restart into the tile).  Two copies of the
+// records, of the per-tile counters and of the dense table alternate by step parity, so a step reads
+// one set and writes the other.
+struct TileP {
+    unsigned tshift, T;        // tile edge = 1 << tshift cells
+    unsigned tiles_x, tiles_y, ntiles;
+    unsigned ch;               // entries a block can sort in shared memory; fuller tiles use `scratch`
+    float4* Qd[2];             // dense table, one float4 (4 action values) per cell; [step & 1] is current
+    int4* rec[2];              // records {x, y, t, id}; [step & 1] is current
+    unsigned* reg_off;         // ntiles + 1: start of each tile's region
+    unsigned* front_cap;       // ntiles: slots of the front part (the back part is the rest of the region)
+    unsigned* seg_cnt[2];      // ntiles: records in the front part
+    unsigned* arr_cnt[2];      // ntiles: records appended to the back part
+    int4* ovf[2];              // records that found their tile's back part full, any tile, N slots
+    unsigned* tctl;            // [0..2] overflow counts (read step%3, append (step+1)%3, clear (step+2)%3); [3..4] scratch cursors by parity
+    unsigned char* tcls;       // ntiles x cls_stride: class bytes of each tile with its halo, row-major (T+2)^2, padded to 16
+    unsigned cls_stride;
+    uint2* scratch;            // N fold entries {id << 2 | action, td target bits} for tiles beyond `ch`
+};
 
 // ---- everything a kernel needs, passed by value ------------------------------------------------
 struct Params {
@@ -84,6 +107,7 @@ struct Params {
     unsigned long long step;   // global batched step index g (keys the policy stream, selects the counter plane)
     unsigned eps_idx;          // index of this step's epsilon in eps_tab
     int eps_from_ctl;          // 1: take the index from ctl (per-episode schedule)
+    TileP tp;
 };
 
 constexpr int BLOCK = 256;
@@ -106,6 +130,14 @@ void launch_q_scatter(const Params& p, const float4* dense, float scale, cudaStr
 void launch_q_gather_range(const Params& p, float4* dense, unsigned cell0, unsigned n, cudaStream_t st);
 void launch_q_average(const Params& p, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale, cudaStream_t st);
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st);
+// tile engine (tile_engine.cu)
+size_t tile_step_smem(const Params& p);
+int  tile_engine_configure(const Params& p);                        // opt in to the dynamic shared memory the step needs
+void launch_tile_bucket(const Params& p, cudaStream_t st);         // p.st (any slot order) -> tile regions of parity p.step & 1
+void launch_tile_classes(const Params& p, cudaStream_t st);       // cell words -> per-tile class bytes (after any change of the grid)
+void launch_tile_export(const Params& p, cudaStream_t st);         // tile regions -> p.st in environment order
+void launch_tile_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c);
+void launch_q_average_dense(const Params& p, float4* table, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale, cudaStream_t st);
 void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st);
 
 }  // namespace cudarl
