@@ -82,7 +82,7 @@ struct cudarl_ctx {
     void *dQd[2] = {nullptr, nullptr}, *drec[2] = {nullptr, nullptr}, *dovf[2] = {nullptr, nullptr};
     void *dtmeta = nullptr, *dtscratch = nullptr, *dtcls = nullptr;   // per-tile offsets / capacities / counters; fold entries of crowded tiles
     bool tile_mode = false;               // true: records live in tile regions and the table in Qd[h_step & 1]
-    bool legacy_engine = true;
+    bool legacy_engine = false;
     int64_t bucket_every = 32, since_bucket = 0;
     int cur = 0;                          // which copy of the state is live
     bool slots_identity = true;           // id[k] == k
@@ -349,11 +349,11 @@ int alloc_tiles(cudarl_ctx* c) {
         const size_t nt = (((size_t)p.W + (1u << cand) - 1) >> cand) * (((size_t)p.H + (1u << cand) - 1) >> cand);
         if (nt >= 592 && N / nt <= 768) { tsh = cand; break; }
     }
-    if (const char* ev = getenv("CUDARL_TILE_SHIFT")) { int v = atoi(ev); if (v >= 2 && v <= 6) tsh = (unsigned)v; }
+    if (const char* ev = getenv("CUDARL_TILE_SHIFT")) { int v = atoi(ev); if (v >= 3 && v <= 5) tsh = (unsigned)v; }
     tp.tshift = tsh; tp.T = 1u << tsh;
     tp.tiles_x = (unsigned)((p.W + (int)tp.T - 1) >> tsh); tp.tiles_y = (unsigned)((p.H + (int)tp.T - 1) >> tsh);
     tp.ntiles = tp.tiles_x * tp.tiles_y;
-    tp.ch = 1024;       // = entries per thread x threads of the step kernel
+    tp.ch = 512;
     for (int k = 0; k < 2; ++k) {
         CK(cudaMalloc(&c->dQd[k], S * sizeof(float4)));
         CK(cudaMalloc(&c->drec[k], (N + N / 2 + 96 * (size_t)tp.ntiles + 64) * sizeof(int4)));
@@ -372,7 +372,7 @@ int alloc_tiles(cudarl_ctx* c) {
     tp.tcls = (unsigned char*)c->dtcls;
     CK(cudaMalloc(&c->dtscratch, N * sizeof(uint2)));
     tp.scratch = (uint2*)c->dtscratch;
-    if (tile_engine_configure(p) != 0) { cudaGetLastError(); return fail(c, -5, "tile step: shared memory request refused"); }
+    if (tile_engine_configure(p, c->cfg.device) != 0) { cudaGetLastError(); return fail(c, -5, "tile step: shared memory request refused"); }
     return 0;
 }
 
@@ -555,7 +555,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
         if (const char* ev = getenv("CUDARL_SORT_EVERY")) c->sort_every = atoll(ev);
         c->bucket_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 32);
         if (const char* ev = getenv("CUDARL_BUCKET_EVERY")) c->bucket_every = atoll(ev);
-        if (const char* ev = getenv("CUDARL_ENGINE")) c->legacy_engine = std::strcmp(ev, "tile") != 0;
+        if (const char* ev = getenv("CUDARL_ENGINE")) c->legacy_engine = std::strcmp(ev, "legacy") == 0;
         rc = body();
     } while (0);
     if (rc) { g_err = c->err; free_all(c); delete c; return rc; }

@@ -53,6 +53,7 @@ struct TileP {
     unsigned tshift, T;        // tile edge = 1 << tshift cells
     unsigned tiles_x, tiles_y, ntiles;
     unsigned ch;               // entries a block can sort in shared memory; fuller tiles use `scratch`
+    unsigned grid;             // blocks of the persistent step kernel (SMs x resident blocks per SM)
     float4* Qd[2];             // dense table, one float4 (4 action values) per cell; [step & 1] is current
     int4* rec[2];              // records {x, y, t, id}; [step & 1] is current
     unsigned* reg_off;         // ntiles + 1: start of each tile's region
@@ -132,7 +133,7 @@ void launch_q_average(const Params& p, const float4* gathered, unsigned R, unsig
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st);
 // tile engine (tile_engine.cu)
 size_t tile_step_smem(const Params& p);
-int  tile_engine_configure(const Params& p);                        // opt in to the dynamic shared memory the step needs
+int  tile_engine_configure(Params& p, int device);                  // opt in to the dynamic shared memory the step needs; sets tp.grid
 void launch_tile_bucket(const Params& p, cudaStream_t st);         // p.st (any slot order) -> tile regions of parity p.step & 1
 void launch_tile_classes(const Params& p, cudaStream_t st);       // cell words -> per-tile class bytes (after any change of the grid)
 void launch_tile_export(const Params& p, cudaStream_t st);         // tile regions -> p.st in environment order

@@ -120,297 +120,467 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 
 constexpr unsigned WAIT_LIMIT = 1u << 22;    // polls of the copy barrier before the block gives up and flags an error
 
-// ------------------------------------------------------------------------------------------------
-// Shared memory of one block (T = tile edge, HS = T + 2):
-//   s_q    HS*HS float4   Q_t of the tile and its halo (read-only after the copy lands)
-//   s_qn   T*T   float4   Q_{t+1} of the tile: starts as a copy of Q_t, updated cells are overwritten
-//   s_sorted ch  uint2    fold entries {id << 2 | action, target} of the cells with several occupants
-//   s_cnt  T*T   u32      occupants per cell
-//   s_cur  T*T   u32      per cell: cursor into s_sorted (ends one past the cell's last entry)
-//   s_list T*T   u16      cells with several occupants
-//   s_ecell ch   u16      cell of each entry in s_sorted
-//   s_cls  HS*HS u8       cell classes of the tile and its halo
-constexpr unsigned TBLOCK = 256;
-constexpr unsigned EPT = 4;          // entries a thread ranks in registers: ch = EPT * TBLOCK
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+// Wait for the phase with the given parity; false if the poll limit ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    for (unsigned it = 0; it < WAIT_LIMIT; ++it) if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
 
-template <bool TRACE>
-__global__ void __launch_bounds__(TBLOCK, 4) k_tile_step(Params p) {
+// ------------------------------------------------------------------------------------------------
+// The step kernel is persistent: a block walks over tiles blockIdx, blockIdx + gridDim, ...  It has eight
+// CONSUMER warps, which do all the arithmetic on shared memory, and one PRODUCER warp (one active thread),
+// which only moves data: while the consumers work on tile k in one stage of shared memory, the producer has
+// the bulk copies of tile k+1 in flight into the other stage and the rows of tile k-1 on their way out.
+//
+// Per stage:  s_q    HS*HS float4   Q_t of the tile and its halo; the consumers turn the interior into
+//                                   Q_{t+1} in place once every read of Q_t is done
+//             s_rec  RC    int4     the first records of the front part of the tile's region
+//             s_recb RCB   int4     the first records of the back part
+//             s_cls  HS*HS u8       cell classes of the tile and its halo
+// Consumer work space, shared by both stages.  A tile with at most NL records (the normal case) chains the
+// records of a cell through shared memory:
+//             s_head T*T   u32      last record that arrived at the cell (slot + 1; 0 = none)
+//             s_cb   T*T   u32      shared cells: first entry in s_sorted | occupants << 16
+//             s_key / s_val / s_next / s_cell  NL   per record slot: id << 2 | action, target, previous arrival at
+//                                   the same cell, cell
+//             s_sorted NL  uint2    entries of shared cells in (cell, id) order
+//             s_mlist NL/2 u16      shared cells
+// A more crowded tile groups its entries with a counting sort instead (the same bytes seen as
+// s_sorted[CH], s_cnt[T*T], s_cur[T*T], s_list[T*T], s_ecell[CH]), spilling to global scratch beyond CH entries.
+// full[stage] : the producer's copies have landed (transaction barrier);  done[stage] : every consumer thread
+// has finished the tile in that stage.
+constexpr unsigned CT = 256;         // consumer threads
+constexpr unsigned TBLOCK = CT + 32; // + the producer warp
+constexpr unsigned NL = 2 * CT;      // records of a tile handled by the chained path: at most two per consumer thread
+constexpr unsigned CH = 512;         // entries the counting-sort path orders in shared memory
+constexpr unsigned EPT = CH / CT;    // ... per consumer thread, in registers
+constexpr unsigned RC = 352, RCB = 96;   // records staged in shared memory (front part, back part); the rest is read from global memory
+
+struct TileHdr {                     // what the producer tells the consumers about the tile in a stage
+    unsigned tile, roff, fcap, n_front, n_in, n_all, nf_s, nb_s;
+    int tx0, ty0;
+};
+
+__device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// consumer-only version of block_sort_u2 (the producer warp does not take part in barriers)
+__device__ void cons_sort_u2(uint2* a, unsigned n) {
+    for (unsigned k = 2; (k >> 1) < n; k <<= 1) {
+        for (unsigned i = threadIdx.x; i < n; i += CT) {
+            const unsigned l = i ^ (k - 1u);
+            if (l > i && l < n) { uint2 u = a[i], v = a[l]; if (u.x > v.x) { a[i] = v; a[l] = u; } }
+        }
+        cons_sync();
+        for (unsigned j = k >> 2; j > 0; j >>= 1) {
+            for (unsigned i = threadIdx.x; i < n; i += CT) {
+                const unsigned l = i ^ j;
+                if (l > i && l < n) { uint2 u = a[i], v = a[l]; if (u.x > v.x) { a[i] = v; a[l] = u; } }
+            }
+            cons_sync();
+        }
+    }
+}
+
+// Everything the per-environment step needs about the tile being processed.
+struct StepCtx {
+    const float4* s_q; const unsigned char* s_cls;
+    int tx0, ty0; unsigned tile, roff, fcap;
+    float eps; unsigned long long g;
+    int4* out; int4* ovf_out; unsigned* arr_next; unsigned* ovf_cnt_next;
+    unsigned* s_stay; unsigned* s_goals; unsigned* s_timeouts;
+};
+
+// One environment, one step: epsilon-greedy, move, TD target from Q_t; writes the record of the next step to the
+// region of the tile it will stand on.  Returns the cell (tile-local), the fold entry key (id << 2 | action) and
+// the target bits.  false: the record does not lie in this tile (never seen; flagged by the caller).
+template <bool TRACE, unsigned TSH>
+__device__ __forceinline__ bool step_env(const Params& p, const StepCtx& c, const int4 rec, unsigned& ic, unsigned& key, unsigned& val) {
+    constexpr unsigned T = 1u << TSH, HS = T + 2u;
+    const TileP& tp = p.tp;
+    const int x = rec.x, y = rec.y, t = rec.z; const unsigned e = (unsigned)rec.w;
+    const unsigned lx = (unsigned)(x - c.tx0), ly = (unsigned)(y - c.ty0);
+    if (lx >= T || ly >= T) return false;
+    ic = (ly << TSH) + lx;
+    const unsigned hh = (ly + 1u) * HS + lx + 1u;
+    const float4 row = c.s_q[hh];
+    const U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)c.g, (unsigned)(c.g >> 32), p.k0, p.k1 ^ TAG_POLICY);
+    const int a = (u01(w.x) < c.eps) ? (int)(w.y & 3u) : argmax4(row);
+    const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
+    int nx = x + dx, ny = y + dy;
+    const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
+    const unsigned ht = (unsigned)((int)hh + dy * (int)HS + dx);          // inside the halo whenever the move is in bounds
+    const bool moved = inb && !(c.s_cls[inb ? ht : hh] & CW_OBST);
+    const unsigned h2 = moved ? ht : hh;
+    nx = moved ? nx : x; ny = moved ? ny : y;
+    const bool done = (c.s_cls[h2] & CW_GOAL) != 0;
+    const float r = done ? 1.0f : -0.01f;
+    float m = 0.0f;
+    if (!done) { m = max4(c.s_q[h2]); if (p.legacy_clamp && m < 0.0f) m = 0.0f; }
+    const float d = __fmaf_rn(p.gamma, m, r);                             // TD target from Q_t; the error is taken in fold()
+    if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = r; p.tr_d[e] = done ? 1 : 0; }
+    key = (e << 2) | (unsigned)a; val = __float_as_uint(d);
+    // episode bookkeeping and the record of the next step
+    const bool timeout = !done && p.max_steps > 0 && t + 1 >= p.max_steps;
+    int nt = t + 1;
+    if (done || timeout) {
+        const unsigned sn = sample_start(p, p.env_offset + e, c.g + 1ull, TAG_START);
+        nx = (int)(sn % (unsigned)p.W); ny = (int)(sn / (unsigned)p.W); nt = 0;
+        atomicAdd(done ? c.s_goals : c.s_timeouts, 1u);
+    }
+    const int4 nrec = make_int4(nx, ny, nt, (int)e);
+    const unsigned dt = ((unsigned)ny >> TSH) * tp.tiles_x + ((unsigned)nx >> TSH);
+    bool placed = false;
+    if (dt == c.tile) {
+        cg::coalesced_group cgp = cg::coalesced_threads();
+        unsigned pos = 0;
+        if (cgp.thread_rank() == 0) pos = atomicAdd(c.s_stay, cgp.size());
+        pos = cgp.shfl(pos, 0) + cgp.thread_rank();
+        if (pos < c.fcap) { c.out[c.roff + pos] = nrec; placed = true; }
+    }
+    if (!placed) {
+        const unsigned doff = tp.reg_off[dt], dfc = tp.front_cap[dt], dbc = tp.reg_off[dt + 1u] - doff - dfc;
+        const unsigned pos = atomicAdd(&c.arr_next[dt], 1u);
+        if (pos < dbc) c.out[doff + dfc + pos] = nrec;
+        else {
+            const unsigned q = atomicAdd(c.ovf_cnt_next, 1u);
+            if (q < p.N) c.ovf_out[q] = nrec; else atomicOr(&p.ctl->error, ERR_BAD_STATE);
+        }
+    }
+    return true;
+}
+
+template <bool TRACE, unsigned TSH>
+__global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
+    constexpr unsigned T = 1u << TSH, HS = T + 2u, T2 = T * T, HS2 = HS * HS;
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_bar;
-    __shared__ unsigned s_stay, s_goals, s_timeouts, s_conf, s_nmulti, s_nent, s_nbig, s_nbigent, s_base, s_bad;
+    __shared__ __align__(8) unsigned long long s_full[2], s_done[2];
+    __shared__ TileHdr s_hdr[2];
+    __shared__ unsigned s_stay, s_nocc, s_nent, s_base, s_abort, s_nb;
+    __shared__ unsigned s_goals, s_timeouts, s_conf, s_nbig, s_nbigent, s_bad;     // accumulated over the block's tiles
     __shared__ unsigned s_big[BIG_LIST];
 
     const TileP& tp = p.tp;
-    const unsigned T = tp.T, HS = T + 2u, T2 = T * T, HS2 = HS * HS, tsh = tp.tshift;
-    float4* s_q = reinterpret_cast<float4*>(smem);
-    float4* s_qn = s_q + HS2;
-    uint2* s_sorted = reinterpret_cast<uint2*>(s_qn + T2);
-    unsigned* s_cnt = reinterpret_cast<unsigned*>(s_sorted + tp.ch);
+    const unsigned stage_bytes = HS2 * 16u + RC * 16u + RCB * 16u + tp.cls_stride;
+    unsigned char* work = smem + 2u * stage_bytes;
+    // chained path
+    unsigned* s_head = reinterpret_cast<unsigned*>(work);
+    unsigned* s_cb = s_head + T2;
+    unsigned* s_key = s_cb + T2;
+    unsigned* s_val = s_key + NL;
+    uint2* s_sorted2 = reinterpret_cast<uint2*>(s_val + NL);
+    unsigned short* s_next = reinterpret_cast<unsigned short*>(s_sorted2 + NL);
+    unsigned short* s_cell = s_next + NL;
+    unsigned short* s_mlist = s_cell + NL;
+    // counting-sort path (same bytes)
+    uint2* s_sorted = reinterpret_cast<uint2*>(work);
+    unsigned* s_cnt = reinterpret_cast<unsigned*>(s_sorted + CH);
     unsigned* s_cur = s_cnt + T2;
     unsigned short* s_list = reinterpret_cast<unsigned short*>(s_cur + T2);
     unsigned short* s_ecell = s_list + T2;
-    unsigned char* s_cls = reinterpret_cast<unsigned char*>(s_ecell + tp.ch);
 
-    const unsigned tid = threadIdx.x, lane = tid & 31u, tile = blockIdx.x;
+    const unsigned tid = threadIdx.x, lane = tid & 31u;
     const unsigned long long g = p.step;
     const unsigned par = (unsigned)(g & 1ull);
-    const int tx0 = (int)((tile % tp.tiles_x) << tsh), ty0 = (int)((tile / tp.tiles_x) << tsh);
     const float4* __restrict__ Qin = tp.Qd[par];
     float4* __restrict__ Qout = tp.Qd[par ^ 1u];
     const int4* __restrict__ in = tp.rec[par];
-    int4* __restrict__ out = tp.rec[par ^ 1u];
     const int4* __restrict__ ovf_in = tp.ovf[par];
-    int4* __restrict__ ovf_out = tp.ovf[par ^ 1u];
-    unsigned* arr_next = tp.arr_cnt[par ^ 1u];
-    unsigned* ovf_cnt_next = tp.tctl + (unsigned)((g + 1ull) % 3ull);
-
-    // rows of the table this tile reads: halo rows [gy_lo, gy_hi] x columns [xs, xe], interior rows [0, ri) x [0, wi)
-    const int xs = max(tx0 - 1, 0), xe = min(tx0 + (int)T, p.W - 1);
-    const int gy_lo = max(ty0 - 1, 0), gy_hi = min(ty0 + (int)T, p.H - 1);
-    const unsigned bytes_h = (unsigned)(xe - xs + 1) * 16u, rows_h = (unsigned)(gy_hi - gy_lo + 1);
-    const unsigned wi = (unsigned)min((int)T, p.W - tx0), ri = (unsigned)min((int)T, p.H - ty0), bytes_i = wi * 16u;
+    const unsigned ntl = blockIdx.x < tp.ntiles ? (tp.ntiles - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;   // tiles of this block
 
     if (tid == 0) {
-        s_stay = 0; s_goals = 0; s_timeouts = 0; s_conf = 0; s_nmulti = 0; s_nent = 0; s_nbig = 0; s_nbigent = 0; s_bad = 0; s_base = 0xFFFFFFFFu;
-        mbar_init(&s_bar, 1u);
-    }
-    if (tile == 0 && tid == 0) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
-    for (unsigned k = 4u * tid; k < T2; k += 4u * TBLOCK) *reinterpret_cast<uint4*>(s_cnt + k) = make_uint4(0u, 0u, 0u, 0u);
-    __syncthreads();
-
-    // ---- Q_t tile + halo, a second copy of the interior, the class bytes: bulk copies onto one barrier --
-    if (tid == 0) mbar_arrive_expect_tx(&s_bar, rows_h * bytes_h + ri * bytes_i + tp.cls_stride);
-    if (tid < HS) {
-        const int gy = ty0 + (int)tid - 1;
-        if (gy >= gy_lo && gy <= gy_hi)
-            bulk_g2s(s_q + tid * HS + (unsigned)(xs - (tx0 - 1)), Qin + (size_t)gy * (size_t)p.W + (size_t)xs, bytes_h, &s_bar);
-    } else if (tid < HS + T) {
-        const unsigned r = tid - HS;
-        if (r < ri) bulk_g2s(s_qn + r * T, Qin + (size_t)(ty0 + (int)r) * (size_t)p.W + (size_t)tx0, bytes_i, &s_bar);
-    } else if (tid == TBLOCK - 1) {
-        bulk_g2s(s_cls, tp.tcls + (size_t)tile * tp.cls_stride, tp.cls_stride, &s_bar);
-    }
-
-    const unsigned roff = tp.reg_off[tile], fcap = tp.front_cap[tile], bcap = tp.reg_off[tile + 1u] - roff - fcap;
-    const unsigned n_front = min(tp.seg_cnt[par][tile], fcap);
-    const unsigned n_in = n_front + min(tp.arr_cnt[par][tile], bcap);           // front part, then back part
-    const unsigned n_all = n_in + min(tp.tctl[(unsigned)(g % 3ull)], p.N);      // then the global spill list, filtered by tile
-    const float eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx];
-
-    // record j of this tile's input, or false if list entry j belongs to another tile
-    auto fetch = [&](unsigned j, int4& r) -> bool {
-        if (j < n_in) { r = in[roff + (j < n_front ? j : fcap + (j - n_front))]; return true; }
-        r = ovf_in[j - n_in];
-        return tile_of(tp, r.x, r.y) == tile;
-    };
-
-    // ---- pass A (while the copies fly): occupants per cell -----------------------------------------------
-    for (unsigned j = tid; j < n_all; j += TBLOCK) {
-        int4 r;
-        if (!fetch(j, r)) continue;
-        const unsigned lx = (unsigned)(r.x - tx0), ly = (unsigned)(r.y - ty0);
-        if (lx >= T || ly >= T) { s_bad = 1u; continue; }
-        atomicAdd(&s_cnt[(ly << tsh) + lx], 1u);
+        s_goals = 0; s_timeouts = 0; s_conf = 0; s_nbig = 0; s_nbigent = 0; s_bad = 0; s_abort = 0;
+        mbar_init(&s_full[0], 1u); mbar_init(&s_full[1], 1u); mbar_init(&s_done[0], CT); mbar_init(&s_done[1], CT);
+        if (blockIdx.x == 0) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
     }
     __syncthreads();
 
-    // ---- cells with several occupants: space for their entries (one atomic per warp), and their list ----
-    for (unsigned base = 0; base < T2; base += 4u * TBLOCK) {
-        const unsigned c0 = base + 4u * tid;
-        uint4 c = make_uint4(0u, 0u, 0u, 0u);
-        if (c0 < T2) c = *reinterpret_cast<const uint4*>(s_cnt + c0);
-        const unsigned m0 = c.x > 1u ? c.x : 0u, m1 = c.y > 1u ? c.y : 0u, m2 = c.z > 1u ? c.z : 0u, m3 = c.w > 1u ? c.w : 0u;
-        const unsigned m = m0 + m1 + m2 + m3, nm = (m0 != 0u) + (m1 != 0u) + (m2 != 0u) + (m3 != 0u);
-        unsigned im = m, il = nm;                                      // inclusive prefixes over the warp: entries, listed cells
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned t1 = __shfl_up_sync(FULL, im, o), t2 = __shfl_up_sync(FULL, il, o);
-            if (lane >= (unsigned)o) { im += t1; il += t2; }
+    if (tid >= CT) {
+        // =========================== producer: one thread moves all the data ===========================
+        if (tid != CT) return;
+        const unsigned n_spill = min(tp.tctl[(unsigned)(g % 3ull)], p.N);
+        auto load_tile = [&](unsigned k) {                    // header + bulk copies of the block's k-th tile into stage k & 1
+            const unsigned b = k & 1u, tile = blockIdx.x + k * gridDim.x;
+            unsigned char* st = smem + b * stage_bytes;
+            float4* s_q = reinterpret_cast<float4*>(st);
+            int4* s_rec = reinterpret_cast<int4*>(st + HS2 * 16u);
+            int4* s_recb = s_rec + RC;
+            unsigned char* s_cls = reinterpret_cast<unsigned char*>(s_recb + RCB);
+            const int tx0 = (int)((tile % tp.tiles_x) << TSH), ty0 = (int)((tile / tp.tiles_x) << TSH);
+            const unsigned roff = tp.reg_off[tile], fcap = tp.front_cap[tile], bcap = tp.reg_off[tile + 1u] - roff - fcap;
+            const unsigned n_front = min(tp.seg_cnt[par][tile], fcap), n_back = min(tp.arr_cnt[par][tile], bcap);
+            const unsigned nf_s = min(n_front, RC), nb_s = min(n_back, RCB);
+            TileHdr& h = s_hdr[b];
+            h.tile = tile; h.roff = roff; h.fcap = fcap; h.n_front = n_front; h.n_in = n_front + n_back; h.n_all = n_front + n_back + n_spill;
+            h.nf_s = nf_s; h.nb_s = nb_s; h.tx0 = tx0; h.ty0 = ty0;
+            const int xs = max(tx0 - 1, 0), xe = min(tx0 + (int)T, p.W - 1);
+            const int gy_lo = max(ty0 - 1, 0), gy_hi = min(ty0 + (int)T, p.H - 1);
+            const unsigned bytes_h = (unsigned)(xe - xs + 1) * 16u;
+            mbar_arrive_expect_tx(&s_full[b], (unsigned)(gy_hi - gy_lo + 1) * bytes_h + tp.cls_stride + (nf_s + nb_s) * 16u);
+            if (nf_s) bulk_g2s(s_rec, in + roff, nf_s * 16u, &s_full[b]);
+            if (nb_s) bulk_g2s(s_recb, in + roff + fcap, nb_s * 16u, &s_full[b]);
+            bulk_g2s(s_cls, tp.tcls + (size_t)tile * tp.cls_stride, tp.cls_stride, &s_full[b]);
+            for (int gy = gy_lo; gy <= gy_hi; ++gy)
+                bulk_g2s(s_q + (unsigned)(gy - (ty0 - 1)) * HS + (unsigned)(xs - (tx0 - 1)), Qin + (size_t)gy * (size_t)p.W + (size_t)xs, bytes_h, &s_full[b]);
+        };
+        if (ntl > 0u) load_tile(0u);
+        if (ntl > 1u) load_tile(1u);
+        for (unsigned k = 0; k < ntl; ++k) {
+            const unsigned b = k & 1u;
+            if (!mbar_wait(&s_done[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); break; }
+            if (*(volatile unsigned*)&s_abort) break;
+            // rows of Q_{t+1} out (the consumers fenced their writes towards the async proxy before arriving)
+            const unsigned tile = blockIdx.x + k * gridDim.x;
+            const int tx0 = (int)((tile % tp.tiles_x) << TSH), ty0 = (int)((tile / tp.tiles_x) << TSH);
+            const unsigned wi = (unsigned)min((int)T, p.W - tx0), ri = (unsigned)min((int)T, p.H - ty0);
+            const float4* s_q = reinterpret_cast<const float4*>(smem + b * stage_bytes);
+            for (unsigned r = 0; r < ri; ++r)
+                bulk_s2g(Qout + (size_t)(ty0 + (int)r) * (size_t)p.W + (size_t)tx0, s_q + (r + 1u) * HS + 1u, wi * 16u);
+            bulk_commit_wait_read();                            // the stage may be overwritten once its rows have been read
+            if (k + 2u < ntl) load_tile(k + 2u);
         }
-        const unsigned totm = __shfl_sync(FULL, im, 31), totl = __shfl_sync(FULL, il, 31);
-        unsigned wb_e = 0, wb_l = 0;
-        if (lane == 0 && totl) { wb_e = atomicAdd(&s_nent, totm); wb_l = atomicAdd(&s_nmulti, totl); }
-        wb_e = __shfl_sync(FULL, wb_e, 0) + im - m; wb_l = __shfl_sync(FULL, wb_l, 0) + il - nm;
-        if (c0 < T2 && m) {
-            const unsigned ex = wb_e;
-            *reinterpret_cast<uint4*>(s_cur + c0) = make_uint4(ex, ex + m0, ex + m0 + m1, ex + m0 + m1 + m2);
-            unsigned li = wb_l;
-            if (m0) s_list[li++] = (unsigned short)c0;
-            if (m1) s_list[li++] = (unsigned short)(c0 + 1u);
-            if (m2) s_list[li++] = (unsigned short)(c0 + 2u);
-            if (m3) s_list[li++] = (unsigned short)(c0 + 3u);
-        }
+        return;
     }
-    __syncthreads();
-    const unsigned nent = s_nent, nmulti = s_nmulti;
-    if (nent > tp.ch) {                                           // too many for shared memory: a slice of the global scratch (block-uniform branch)
-        if (tid == 0) {
-            const unsigned b = atomicAdd(&tp.tctl[3u + par], nent);
-            if (b + nent <= p.N) s_base = b; else { s_base = 0xFFFFFFFEu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
-        }
-        __syncthreads();
-    }
-    const bool in_smem = s_base == 0xFFFFFFFFu, usable = s_base != 0xFFFFFFFEu;
-    uint2* sorted = in_smem ? s_sorted : tp.scratch + (usable ? s_base : 0u);
 
-    // the copies must have landed before this thread reads the tile
-    {
-        bool landed = false;
-        for (unsigned it = 0; it < WAIT_LIMIT; ++it) if (mbar_try_wait(&s_bar, 0u)) { landed = true; break; }
-        if (!landed) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_bad = 2u; }
-    }
-
-    // ---- pass B: the step itself ----------------------------------------------------------------------
+    // ================================= consumers ======================================================
+    StepCtx c;
+    c.eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx]; c.g = g;
+    c.out = tp.rec[par ^ 1u]; c.ovf_out = tp.ovf[par ^ 1u]; c.arr_next = tp.arr_cnt[par ^ 1u];
+    c.ovf_cnt_next = tp.tctl + (unsigned)((g + 1ull) % 3ull);
+    c.s_stay = &s_stay; c.s_goals = &s_goals; c.s_timeouts = &s_timeouts;
     unsigned conf = 0;
-    for (unsigned j = tid; j < n_all; j += TBLOCK) {
-        int4 rec;
-        if (!fetch(j, rec)) continue;
-        const int x = rec.x, y = rec.y, t = rec.z; const unsigned e = (unsigned)rec.w;
-        const unsigned lx = (unsigned)(x - tx0), ly = (unsigned)(y - ty0);
-        if (lx >= T || ly >= T) continue;
-        const unsigned ic = (ly << tsh) + lx, h = (ly + 1u) * HS + lx + 1u;
-        const float4 row = s_q[h];
-        const U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
-        const int a = (u01(w.x) < eps) ? (int)(w.y & 3u) : argmax4(row);
-        const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
-        int nx = x + dx, ny = y + dy;
-        const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
-        const unsigned ht = (unsigned)((int)h + dy * (int)HS + dx);       // inside the halo whenever the move is in bounds
-        const bool moved = inb && !(s_cls[inb ? ht : h] & CW_OBST);
-        const unsigned h2 = moved ? ht : h;
-        nx = moved ? nx : x; ny = moved ? ny : y;
-        const bool done = (s_cls[h2] & CW_GOAL) != 0;
-        const float r = done ? 1.0f : -0.01f;
-        float m = 0.0f;
-        if (!done) { m = max4(s_q[h2]); if (p.legacy_clamp && m < 0.0f) m = 0.0f; }
-        const float d = __fmaf_rn(p.gamma, m, r);                         // TD target from Q_t; the error is taken in fold()
-        if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = r; p.tr_d[e] = done ? 1 : 0; }
-        if (s_cnt[ic] == 1u) {                                            // alone on the cell: its row is final right away
-            float4 nr = row; fold(nr, a, p.lr, d); s_qn[ic] = nr;
-        } else {
-            conf += 1u;
-            if (usable) {
-                const unsigned pos = atomicAdd(&s_cur[ic], 1u);
-                sorted[pos] = make_uint2((e << 2) | (unsigned)a, __float_as_uint(d));
-                if (in_smem) s_ecell[pos] = (unsigned short)ic;
-            }
-        }
-        // episode bookkeeping and the record of the next step
-        const bool timeout = !done && p.max_steps > 0 && t + 1 >= p.max_steps;
-        int nt = t + 1;
-        if (done || timeout) {
-            const unsigned sn = sample_start(p, p.env_offset + e, g + 1ull, TAG_START);
-            nx = (int)(sn % (unsigned)p.W); ny = (int)(sn / (unsigned)p.W); nt = 0;
-            atomicAdd(done ? &s_goals : &s_timeouts, 1u);
-        }
-        const int4 nrec = make_int4(nx, ny, nt, (int)e);
-        const unsigned dt = tile_of(tp, nx, ny);
-        bool placed = false;
-        if (dt == tile) {
-            cg::coalesced_group cgp = cg::coalesced_threads();
-            unsigned pos = 0;
-            if (cgp.thread_rank() == 0) pos = atomicAdd(&s_stay, cgp.size());
-            pos = cgp.shfl(pos, 0) + cgp.thread_rank();
-            if (pos < fcap) { out[roff + pos] = nrec; placed = true; }
-        }
-        if (!placed) {
-            const unsigned doff = tp.reg_off[dt], dfc = tp.front_cap[dt], dbc = tp.reg_off[dt + 1u] - doff - dfc;
-            const unsigned pos = atomicAdd(&arr_next[dt], 1u);
-            if (pos < dbc) out[doff + dfc + pos] = nrec;
-            else {
-                const unsigned q = atomicAdd(ovf_cnt_next, 1u);
-                if (q < p.N) ovf_out[q] = nrec; else atomicOr(&p.ctl->error, ERR_BAD_STATE);
-            }
-        }
-    }
-    __syncthreads();
+    for (unsigned k = 0; k < ntl; ++k) {
+        const unsigned b = k & 1u;
+        unsigned char* st = smem + b * stage_bytes;
+        float4* s_q = reinterpret_cast<float4*>(st);
+        const int4* s_rec = reinterpret_cast<const int4*>(st + HS2 * 16u);
+        const int4* s_recb = s_rec + RC;
+        c.s_q = s_q; c.s_cls = reinterpret_cast<const unsigned char*>(s_recb + RCB);
 
-    // ---- order the entries of each shared cell by environment id ------------------------------------------
-    if (in_smem) {
-        // every entry counts the entries of its cell with a smaller id (ids are unique): that is its place
-        uint2 ent[EPT]; unsigned dst[EPT];
+        if (tid == 0) { s_stay = 0; s_nocc = 0; s_nent = 0; s_nb = 0; s_base = 0xFFFFFFFFu; }
+        if (!mbar_wait(&s_full[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
+        const TileHdr h = s_hdr[b];
+        const unsigned tile = h.tile, roff = h.roff, fcap = h.fcap, n_front = h.n_front, n_in = h.n_in, n_all = h.n_all, nf_s = h.nf_s, nb_s = h.nb_s;
+        c.tx0 = h.tx0; c.ty0 = h.ty0; c.tile = tile; c.roff = roff; c.fcap = fcap;
+        const bool chained = n_all <= NL;                          // block-uniform
+        if (chained) { for (unsigned q = 4u * tid; q < T2; q += 4u * CT) *reinterpret_cast<uint4*>(s_head + q) = make_uint4(0u, 0u, 0u, 0u); }
+        else         { for (unsigned q = 4u * tid; q < T2; q += 4u * CT) *reinterpret_cast<uint4*>(s_cnt + q) = make_uint4(0u, 0u, 0u, 0u); }
+        cons_sync();
+        if (s_abort) break;                                    // never seen; the producer gives up at its next wait
+
+        // record j of this tile's input (front part, back part, then the spill list filtered by tile)
+        auto fetch = [&](unsigned j, int4& r) -> bool {
+            if (j < n_front) { r = j < nf_s ? s_rec[j] : in[roff + j]; return true; }
+            if (j < n_in) { const unsigned q = j - n_front; r = q < nb_s ? s_recb[q] : in[roff + fcap + q]; return true; }
+            r = ovf_in[j - n_in];
+            return tile_of(tp, r.x, r.y) == tile;
+        };
+        auto cell_hh = [&](unsigned ic) -> unsigned { return ((ic >> TSH) + 1u) * HS + (ic & (T - 1u)) + 1u; };
+
+        if (chained) {
+            // ---- the step: every record chains itself to the previous arrival at its cell ----------------
 #pragma unroll
-        for (unsigned k = 0; k < EPT; ++k) {
-            const unsigned pos = tid + k * TBLOCK;
-            dst[k] = 0xFFFFFFFFu; ent[k] = make_uint2(0u, 0u);
-            if (pos < nent) {
-                ent[k] = s_sorted[pos];
-                const unsigned ic = s_ecell[pos], cnt = s_cnt[ic], start = s_cur[ic] - cnt;
-                unsigned rank = 0;
-                for (unsigned q = start; q < start + cnt; ++q) rank += s_sorted[q].x < ent[k].x ? 1u : 0u;
-                dst[k] = start + rank;
+            for (unsigned q = 0; q < NL / CT; ++q) {
+                const unsigned j = tid + q * CT;
+                int4 rec; unsigned ic = 0, key = 0, val = 0;
+                bool ok = j < n_all && fetch(j, rec);
+                if (ok && !step_env<TRACE, TSH>(p, c, rec, ic, key, val)) { s_bad = 1u; ok = false; }
+                if (ok) {
+                    s_key[j] = key; s_val[j] = val; s_cell[j] = (unsigned short)ic;
+                    s_next[j] = (unsigned short)atomicExch(&s_head[ic], j + 1u);
+                } else if (j < NL) s_cell[j] = 0xFFFFu;
             }
-        }
-        __syncthreads();
+            cons_sync();
+            // ---- alone on the cell: apply.  Otherwise: how many share the cell, how many of them have a smaller id ----
+            unsigned rank[NL / CT];
 #pragma unroll
-        for (unsigned k = 0; k < EPT; ++k) if (dst[k] != 0xFFFFFFFFu) s_sorted[dst[k]] = ent[k];
-        __syncthreads();
-        for (unsigned k = tid; k < nmulti; k += TBLOCK) {
-            const unsigned ic = s_list[k], cnt = s_cnt[ic];
-            float4 row = s_q[((ic >> tsh) + 1u) * HS + (ic & (T - 1u)) + 1u];
-            fold_entries(row, s_sorted + (s_cur[ic] - cnt), cnt, p.lr);
-            s_qn[ic] = row;
-            if (cnt > SMALL_MAX) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, cnt); }
-        }
-    } else if (usable) {
-        // a tile too crowded for shared memory: small cells are ordered by their own thread, large ones by the whole block
-        for (unsigned k = tid; k < nmulti; k += TBLOCK) {
-            const unsigned ic = s_list[k], cnt = s_cnt[ic];
-            if (cnt <= SMALL_MAX) {
-                uint2* e = sorted + (s_cur[ic] - cnt);
-                for (unsigned i = 1; i < cnt; ++i) {
-                    const uint2 v = e[i]; unsigned q = i;
-                    while (q > 0 && e[q - 1u].x > v.x) { e[q] = e[q - 1u]; --q; }
-                    e[q] = v;
+            for (unsigned q = 0; q < NL / CT; ++q) {
+                const unsigned j = tid + q * CT;
+                rank[q] = 0xFFFFFFFFu;
+                const unsigned ic = j < n_all ? s_cell[j] : 0xFFFFu;
+                if (ic == 0xFFFFu) continue;
+                const unsigned head = s_head[ic], key = s_key[j];
+                if (head == j + 1u && s_next[j] == 0u) {
+                    const unsigned hh = cell_hh(ic);
+                    float4 row = s_q[hh]; fold(row, (int)(key & 3u), p.lr, __uint_as_float(s_val[j])); s_q[hh] = row;
+                } else {
+                    unsigned cnt = 0, r = 0;
+                    for (unsigned z = head; z != 0u && cnt < NL; z = s_next[z - 1u]) { ++cnt; r += s_key[z - 1u] < key ? 1u : 0u; }
+                    rank[q] = r; conf += 1u;
+                    if (head == j + 1u) {                          // one member per cell reserves the cell's run of entries
+                        const unsigned base = atomicAdd(&s_nent, cnt);
+                        s_cb[ic] = base | (cnt << 16);
+                        s_mlist[atomicAdd(&s_nocc, 1u)] = (unsigned short)ic;
+                    }
                 }
-                float4 row = s_q[((ic >> tsh) + 1u) * HS + (ic & (T - 1u)) + 1u];
-                fold_entries(row, e, cnt, p.lr);
-                s_qn[ic] = row;
-            } else {
-                const unsigned kb = atomicAdd(&s_nbig, 1u);
-                if (kb < BIG_LIST) s_big[kb] = ic;
-                atomicAdd(&s_nbigent, cnt);
+            }
+            cons_sync();
+#pragma unroll
+            for (unsigned q = 0; q < NL / CT; ++q) {
+                const unsigned j = tid + q * CT;
+                if (rank[q] != 0xFFFFFFFFu) s_sorted2[(s_cb[s_cell[j]] & 0xFFFFu) + rank[q]] = make_uint2(s_key[j], s_val[j]);
+            }
+            cons_sync();
+            for (unsigned q = tid; q < s_nocc; q += CT) {
+                const unsigned ic = s_mlist[q], cb = s_cb[ic], cnt = cb >> 16, hh = cell_hh(ic);
+                float4 row = s_q[hh];
+                fold_entries(row, s_sorted2 + (cb & 0xFFFFu), cnt, p.lr);
+                s_q[hh] = row;
+                if (cnt > SMALL_MAX) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, cnt); }
+            }
+        } else {
+            // ---- crowded tile, pass A: occupants per cell ------------------------------------------------------
+            for (unsigned j = tid; j < n_all; j += CT) {
+                int4 r;
+                if (!fetch(j, r)) continue;
+                const unsigned lx = (unsigned)(r.x - c.tx0), ly = (unsigned)(r.y - c.ty0);
+                if (lx >= T || ly >= T) { s_bad = 1u; continue; }
+                atomicAdd(&s_cnt[(ly << TSH) + lx], 1u);
+            }
+            cons_sync();
+            // ---- occupied cells: space for their entries (one atomic per warp), and their list -------------------
+            for (unsigned base = 0; base < T2; base += 4u * CT) {
+                const unsigned c0 = base + 4u * tid;
+                uint4 cc = make_uint4(0u, 0u, 0u, 0u);
+                if (c0 < T2) cc = *reinterpret_cast<const uint4*>(s_cnt + c0);
+                const unsigned m = cc.x + cc.y + cc.z + cc.w, nm = (cc.x != 0u) + (cc.y != 0u) + (cc.z != 0u) + (cc.w != 0u);
+                unsigned im = m, il = nm;                              // inclusive prefixes over the warp: entries, listed cells
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned t1 = __shfl_up_sync(FULL, im, o), t2 = __shfl_up_sync(FULL, il, o);
+                    if (lane >= (unsigned)o) { im += t1; il += t2; }
+                }
+                const unsigned totm = __shfl_sync(FULL, im, 31), totl = __shfl_sync(FULL, il, 31);
+                unsigned wb_e = 0, wb_l = 0;
+                if (lane == 0 && totl) { wb_e = atomicAdd(&s_nent, totm); wb_l = atomicAdd(&s_nocc, totl); }
+                wb_e = __shfl_sync(FULL, wb_e, 0) + im - m; wb_l = __shfl_sync(FULL, wb_l, 0) + il - nm;
+                if (c0 < T2 && m) {
+                    *reinterpret_cast<uint4*>(s_cur + c0) = make_uint4(wb_e, wb_e + cc.x, wb_e + cc.x + cc.y, wb_e + cc.x + cc.y + cc.z);
+                    unsigned li = wb_l;
+                    if (cc.x) s_list[li++] = (unsigned short)c0;
+                    if (cc.y) s_list[li++] = (unsigned short)(c0 + 1u);
+                    if (cc.z) s_list[li++] = (unsigned short)(c0 + 2u);
+                    if (cc.w) s_list[li++] = (unsigned short)(c0 + 3u);
+                }
+            }
+            cons_sync();
+            const unsigned nent = s_nent, nocc = s_nocc;
+            if (nent > CH) {                                      // too many for shared memory: a slice of the global scratch (block-uniform branch)
+                if (tid == 0) {
+                    const unsigned q = atomicAdd(&tp.tctl[3u + par], nent);
+                    if (q + nent <= p.N) s_base = q; else { s_base = 0xFFFFFFFEu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
+                }
+                cons_sync();
+            }
+            const bool in_smem = s_base == 0xFFFFFFFFu, usable = s_base != 0xFFFFFFFEu;
+            uint2* sorted = in_smem ? s_sorted : tp.scratch + (usable ? s_base : 0u);
+            // ---- pass B: the step itself ----------------------------------------------------------------------
+            for (unsigned j = tid; j < n_all; j += CT) {
+                int4 rec; unsigned ic, key, val;
+                if (!fetch(j, rec)) continue;
+                if (!step_env<TRACE, TSH>(p, c, rec, ic, key, val)) continue;
+                if (s_cnt[ic] > 1u) conf += 1u;
+                if (usable) {
+                    const unsigned pos = atomicAdd(&s_cur[ic], 1u);
+                    sorted[pos] = make_uint2(key, val);
+                    if (in_smem) s_ecell[pos] = (unsigned short)ic;
+                }
+            }
+            cons_sync();
+            // ---- order the entries of each cell by environment id, then apply them: Q_t -> Q_{t+1} in place ------
+            if (in_smem) {
+                // every entry counts the entries of its cell with a smaller id (ids are unique): that is its place
+                uint2 ent[EPT]; unsigned dst[EPT];
+#pragma unroll
+                for (unsigned q = 0; q < EPT; ++q) {
+                    const unsigned pos = tid + q * CT;
+                    dst[q] = 0xFFFFFFFFu; ent[q] = make_uint2(0u, 0u);
+                    if (pos < nent) {
+                        ent[q] = s_sorted[pos];
+                        const unsigned ic = s_ecell[pos], cnt = s_cnt[ic];
+                        if (cnt > 1u) {
+                            const unsigned start = s_cur[ic] - cnt;
+                            unsigned r = 0;
+                            for (unsigned z = start; z < start + cnt; ++z) r += s_sorted[z].x < ent[q].x ? 1u : 0u;
+                            dst[q] = start + r;
+                        }
+                    }
+                }
+                cons_sync();
+#pragma unroll
+                for (unsigned q = 0; q < EPT; ++q) if (dst[q] != 0xFFFFFFFFu) s_sorted[dst[q]] = ent[q];
+                cons_sync();
+                for (unsigned q = tid; q < nocc; q += CT) {
+                    const unsigned ic = s_list[q], cnt = s_cnt[ic], hh = cell_hh(ic);
+                    float4 row = s_q[hh];
+                    fold_entries(row, s_sorted + (s_cur[ic] - cnt), cnt, p.lr);
+                    s_q[hh] = row;
+                    if (cnt > SMALL_MAX) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, cnt); }
+                }
+            } else if (usable) {
+                // entries in global scratch: small cells are ordered by their own thread, large ones by all consumers
+                for (unsigned q = tid; q < nocc; q += CT) {
+                    const unsigned ic = s_list[q], cnt = s_cnt[ic];
+                    if (cnt <= SMALL_MAX) {
+                        uint2* e = sorted + (s_cur[ic] - cnt);
+                        for (unsigned i = 1; i < cnt; ++i) {
+                            const uint2 v = e[i]; unsigned z = i;
+                            while (z > 0 && e[z - 1u].x > v.x) { e[z] = e[z - 1u]; --z; }
+                            e[z] = v;
+                        }
+                        const unsigned hh = cell_hh(ic);
+                        float4 row = s_q[hh];
+                        fold_entries(row, e, cnt, p.lr);
+                        s_q[hh] = row;
+                    } else {
+                        const unsigned kb = atomicAdd(&s_nb, 1u);
+                        if (kb < BIG_LIST) s_big[kb] = ic;
+                        atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, cnt);
+                    }
+                }
+                cons_sync();
+                const unsigned nb = s_nb;
+                if (nb && nb <= BIG_LIST) {
+                    for (unsigned q = 0; q < nb; ++q) { const unsigned ic = s_big[q], cnt = s_cnt[ic]; cons_sort_u2(sorted + (s_cur[ic] - cnt), cnt); }
+                    for (unsigned q = tid; q < nb; q += CT) {
+                        const unsigned ic = s_big[q], cnt = s_cnt[ic], hh = cell_hh(ic);
+                        float4 row = s_q[hh];
+                        fold_entries(row, sorted + (s_cur[ic] - cnt), cnt, p.lr);
+                        s_q[hh] = row;
+                    }
+                } else if (nb) {
+                    for (unsigned q = 0; q < nocc; ++q) { const unsigned ic = s_list[q], cnt = s_cnt[ic]; if (cnt > SMALL_MAX) cons_sort_u2(sorted + (s_cur[ic] - cnt), cnt); }
+                    for (unsigned q = tid; q < nocc; q += CT) {
+                        const unsigned ic = s_list[q], cnt = s_cnt[ic];
+                        if (cnt <= SMALL_MAX) continue;
+                        const unsigned hh = cell_hh(ic);
+                        float4 row = s_q[hh];
+                        fold_entries(row, sorted + (s_cur[ic] - cnt), cnt, p.lr);
+                        s_q[hh] = row;
+                    }
+                }
             }
         }
-        __syncthreads();
-        const unsigned nbig = s_nbig;
-        if (nbig && nbig <= BIG_LIST) {
-            for (unsigned k = 0; k < nbig; ++k) { const unsigned ic = s_big[k], cnt = s_cnt[ic]; block_sort_u2(sorted + (s_cur[ic] - cnt), cnt); }
-            for (unsigned k = tid; k < nbig; k += TBLOCK) {
-                const unsigned ic = s_big[k], cnt = s_cnt[ic];
-                float4 row = s_q[((ic >> tsh) + 1u) * HS + (ic & (T - 1u)) + 1u];
-                fold_entries(row, sorted + (s_cur[ic] - cnt), cnt, p.lr);
-                s_qn[ic] = row;
-            }
-        } else if (nbig) {
-            for (unsigned k = 0; k < nmulti; ++k) { const unsigned ic = s_list[k], cnt = s_cnt[ic]; if (cnt > SMALL_MAX) block_sort_u2(sorted + (s_cur[ic] - cnt), cnt); }
-            for (unsigned k = tid; k < nmulti; k += TBLOCK) {
-                const unsigned ic = s_list[k], cnt = s_cnt[ic];
-                if (cnt <= SMALL_MAX) continue;
-                float4 row = s_q[((ic >> tsh) + 1u) * HS + (ic & (T - 1u)) + 1u];
-                fold_entries(row, sorted + (s_cur[ic] - cnt), cnt, p.lr);
-                s_qn[ic] = row;
-            }
+        // hand the stage to the producer: rows written through the generic proxy, read by the bulk copy
+        fence_async_smem();
+        mbar_arrive(&s_done[b]);
+        cons_sync();                                                      // s_stay is final; nobody is still in this tile's work space
+        if (tid == 0) {
+            tp.seg_cnt[par ^ 1u][tile] = min(s_stay, fcap);
+            tp.arr_cnt[par][tile] = 0u;                                   // consumed; it is the append counter again in the next step
         }
     }
-
-    // ---- tile of Q_{t+1} out: one bulk copy per row ----------------------------------------------------
-    fence_async_smem();                                                   // the rows were written through the generic proxy
     for (int o = 16; o; o >>= 1) conf += __shfl_xor_sync(FULL, conf, o);
     if (lane == 0u && conf) atomicAdd(&s_conf, conf);
-    __syncthreads();
-    if (tid < ri && s_bad != 2u) {
-        bulk_s2g(Qout + (size_t)(ty0 + (int)tid) * (size_t)p.W + (size_t)tx0, s_qn + tid * T, bytes_i);
-        bulk_commit_wait_read();
-    }
-    if (tid == TBLOCK - 1) {
-        tp.seg_cnt[par ^ 1u][tile] = min(s_stay, fcap);
-        tp.arr_cnt[par][tile] = 0u;                                       // consumed; it is the append counter again in the next step
+    cons_sync();
+    if (tid == 0) {
         if (s_conf) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_conf);
         if (s_goals) atomicAdd(&p.ctl->goals, (unsigned long long)s_goals);
         if (s_timeouts) atomicAdd(&p.ctl->timeouts, (unsigned long long)s_timeouts);
         if (s_goals + s_timeouts) atomicAdd(&p.ctl->episodes, (unsigned long long)(s_goals + s_timeouts));
         if (s_nbig) { atomicAdd(&p.ctl->long_chains, (unsigned long long)s_nbig); atomicAdd(&p.ctl->general, (unsigned long long)s_nbigent); }
-        if (s_bad == 1u) atomicOr(&p.ctl->error, ERR_BAD_STATE);
+        if (s_bad) atomicOr(&p.ctl->error, ERR_BAD_STATE);
     }
 }
 
@@ -514,15 +684,38 @@ __global__ void k_q_average_dense(float4* table, const float4* gathered, unsigne
 // ------------------------------------------------------------------------------------------------
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 
+static size_t work_bytes(size_t T2) {
+    const size_t chained = 2 * T2 * 4 + 2 * (size_t)NL * 4 + (size_t)NL * 8 + 2 * (size_t)NL * 2 + (size_t)NL;
+    const size_t counting = (size_t)CH * 8 + 2 * T2 * 4 + T2 * 2 + (size_t)CH * 2;
+    return ((chained > counting ? chained : counting) + 15) / 16 * 16;
+}
 size_t tile_step_smem(const Params& p) {
     const size_t T = p.tp.T, HS = T + 2;
-    return HS * HS * 16 + T * T * 16 + (size_t)p.tp.ch * 8 + 2 * T * T * 4 + T * T * 2 + (size_t)p.tp.ch * 2 + ((HS * HS + 15) / 16) * 16;
+    const size_t stage = HS * HS * 16 + (size_t)RC * 16 + (size_t)RCB * 16 + p.tp.cls_stride;
+    return 2 * stage + work_bytes(T * T);
 }
-int tile_engine_configure(const Params& p) {
+template <unsigned TSH>
+static cudaError_t configure_one(int bytes, int* per_sm) {
+    cudaError_t e = cudaFuncSetAttribute(k_tile_step<false, TSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_tile_step<true, TSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH>, (int)TBLOCK, (size_t)bytes);
+    return e;
+}
+int tile_engine_configure(Params& p, int device) {
     const int bytes = (int)tile_step_smem(p);
-    cudaError_t e = cudaFuncSetAttribute(k_tile_step<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_tile_step<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    return (int)e;
+    int sms = 0, per_sm = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return (int)e;
+    switch (p.tp.tshift) {
+        case 3: e = configure_one<3>(bytes, &per_sm); break;
+        case 4: e = configure_one<4>(bytes, &per_sm); break;
+        case 5: e = configure_one<5>(bytes, &per_sm); break;
+        default: return (int)cudaErrorInvalidValue;
+    }
+    if (e != cudaSuccess) return (int)e;
+    if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
+    p.tp.grid = (unsigned)(sms * per_sm);
+    return 0;
 }
 void launch_tile_bucket(const Params& p, cudaStream_t st) {
     cudaMemsetAsync(p.tp.seg_cnt[p.step & 1ull], 0, (size_t)p.tp.ntiles * sizeof(unsigned), st);
@@ -535,11 +728,21 @@ void launch_tile_export(const Params& p, cudaStream_t st) {
     k_te_export<<<p.tp.ntiles, BLOCK, 0, st>>>(p);
     k_te_export_ovf<<<64, BLOCK, 0, st>>>(p);
 }
+static unsigned tile_step_grid(const Params& p) { return p.tp.ntiles < p.tp.grid ? p.tp.ntiles : p.tp.grid; }
+template <unsigned TSH>
+static void launch_step_one(const Params& p, bool trace, unsigned grid, size_t smem, cudaStream_t st) {
+    if (trace) k_tile_step<true, TSH><<<grid, TBLOCK, smem, st>>>(p);
+    else       k_tile_step<false, TSH><<<grid, TBLOCK, smem, st>>>(p);
+}
 void launch_tile_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c) {
     const size_t smem = tile_step_smem(p);
+    const unsigned grid = tile_step_grid(p);
     if (ev_a) cudaEventRecord(ev_a, st);
-    if (trace) k_tile_step<true><<<p.tp.ntiles, TBLOCK, smem, st>>>(p);
-    else       k_tile_step<false><<<p.tp.ntiles, TBLOCK, smem, st>>>(p);
+    switch (p.tp.tshift) {
+        case 3: launch_step_one<3>(p, trace, grid, smem, st); break;
+        case 4: launch_step_one<4>(p, trace, grid, smem, st); break;
+        default: launch_step_one<5>(p, trace, grid, smem, st); break;
+    }
     if (ev_b) cudaEventRecord(ev_b, st);
     if (p.eps_from_ctl) k_tile_eps_episode<<<1, 1, 0, st>>>(p);
     if (ev_c) cudaEventRecord(ev_c, st);
