@@ -128,8 +128,29 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     for (unsigned it = 0; it < WAIT_LIMIT; ++it) if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// The same for a thread that expects to wait long (the producer, for the consumers to finish a tile): every
+// poll may suspend the thread for a few microseconds, so the wait does not take issue slots from the warps that work.
+__device__ __forceinline__ bool mbar_wait_long(unsigned long long* bar, unsigned parity) {
+    for (unsigned it = 0; it < (1u << 20); ++it) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(4000u) : "memory");
+        if (ok) return true;
+        __nanosleep(200);
+    }
+    return false;
+}
 
 // ------------------------------------------------------------------------------------------------
+// Why no ordering is needed.  The oracle applies the updates of one (cell, action) one after the other in
+// ascending environment id, each as  q <- fma(lr, target - q, q).  Inside one fused step the target of an
+// update is a function of (cell, action) alone: the action fixes the next cell (the grid is static), the next
+// cell fixes reward and done, and the bootstrap value is the max over Q_t of that next cell.  So all updates of
+// one (cell, action) apply the SAME map, and applying it n times gives the same bits in any order; updates of
+// different actions touch different components.  The step therefore only has to count, per cell and action,
+// how many environments chose it -- a histogram in shared memory -- and then apply each map that many times.
+// (update_batch takes arbitrary caller transitions, so it keeps its ordered fold.)
+//
 // The step kernel is persistent: a block walks over tiles blockIdx, blockIdx + gridDim, ...  It has eight
 // CONSUMER warps, which do all the arithmetic on shared memory, and one PRODUCER warp (one active thread),
 // which only moves data: while the consumers work on tile k in one stage of shared memory, the producer has
@@ -140,24 +161,16 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 //             s_rec  RC    int4     the first records of the front part of the tile's region
 //             s_recb RCB   int4     the first records of the back part
 //             s_cls  HS*HS u8       cell classes of the tile and its halo
-// Consumer work space, shared by both stages.  A tile with at most NL records (the normal case) chains the
-// records of a cell through shared memory:
-//             s_head T*T   u32      last record that arrived at the cell (slot + 1; 0 = none)
-//             s_cb   T*T   u32      shared cells: first entry in s_sorted | occupants << 16
-//             s_key / s_val / s_next / s_cell  NL   per record slot: id << 2 | action, target, previous arrival at
-//                                   the same cell, cell
-//             s_sorted NL  uint2    entries of shared cells in (cell, id) order
-//             s_mlist NL/2 u16      shared cells
-// A more crowded tile groups its entries with a counting sort instead (the same bytes seen as
-// s_sorted[CH], s_cnt[T*T], s_cur[T*T], s_list[T*T], s_ecell[CH]), spilling to global scratch beyond CH entries.
+// Consumer work space, shared by both stages:
+//             s_n    T*T   u64      per cell: how many environments chose action a, 16 bits per action
+//             s_list T*T   u16      occupied cells
+// A tile with more than 65,535 records counts in 32-bit counters in global scratch instead.
 // full[stage] : the producer's copies have landed (transaction barrier);  done[stage] : every consumer thread
 // has finished the tile in that stage.
 constexpr unsigned CT = 256;         // consumer threads
 constexpr unsigned TBLOCK = CT + 32; // + the producer warp
-constexpr unsigned NL = 2 * CT;      // records of a tile handled by the chained path: at most two per consumer thread
-constexpr unsigned CH = 512;         // entries the counting-sort path orders in shared memory
-constexpr unsigned EPT = CH / CT;    // ... per consumer thread, in registers
 constexpr unsigned RC = 352, RCB = 96;   // records staged in shared memory (front part, back part); the rest is read from global memory
+constexpr unsigned NMAX16 = 65535u;  // records of a tile the 16-bit counters can hold
 
 struct TileHdr {                     // what the producer tells the consumers about the tile in a stage
     unsigned tile, roff, fcap, n_front, n_in, n_all, nf_s, nb_s;
@@ -165,24 +178,6 @@ struct TileHdr {                     // what the producer tells the consumers ab
 };
 
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-
-// consumer-only version of block_sort_u2 (the producer warp does not take part in barriers)
-__device__ void cons_sort_u2(uint2* a, unsigned n) {
-    for (unsigned k = 2; (k >> 1) < n; k <<= 1) {
-        for (unsigned i = threadIdx.x; i < n; i += CT) {
-            const unsigned l = i ^ (k - 1u);
-            if (l > i && l < n) { uint2 u = a[i], v = a[l]; if (u.x > v.x) { a[i] = v; a[l] = u; } }
-        }
-        cons_sync();
-        for (unsigned j = k >> 2; j > 0; j >>= 1) {
-            for (unsigned i = threadIdx.x; i < n; i += CT) {
-                const unsigned l = i ^ j;
-                if (l > i && l < n) { uint2 u = a[i], v = a[l]; if (u.x > v.x) { a[i] = v; a[l] = u; } }
-            }
-            cons_sync();
-        }
-    }
-}
 
 // Everything the per-environment step needs about the tile being processed.
 struct StepCtx {
@@ -193,11 +188,11 @@ struct StepCtx {
     unsigned* s_stay; unsigned* s_goals; unsigned* s_timeouts;
 };
 
-// One environment, one step: epsilon-greedy, move, TD target from Q_t; writes the record of the next step to the
-// region of the tile it will stand on.  Returns the cell (tile-local), the fold entry key (id << 2 | action) and
-// the target bits.  false: the record does not lie in this tile (never seen; flagged by the caller).
+// One environment, one step: epsilon-greedy action, move, episode bookkeeping; writes the record of the next
+// step to the region of the tile it will stand on.  Returns the cell (tile-local) and the action.
+// false: the record does not lie in this tile (never seen; flagged by the caller).
 template <bool TRACE, unsigned TSH>
-__device__ __forceinline__ bool step_env(const Params& p, const StepCtx& c, const int4 rec, unsigned& ic, unsigned& key, unsigned& val) {
+__device__ __forceinline__ bool step_env(const Params& p, const StepCtx& c, const int4 rec, unsigned& ic, unsigned& act) {
     constexpr unsigned T = 1u << TSH, HS = T + 2u;
     const TileP& tp = p.tp;
     const int x = rec.x, y = rec.y, t = rec.z; const unsigned e = (unsigned)rec.w;
@@ -205,23 +200,17 @@ __device__ __forceinline__ bool step_env(const Params& p, const StepCtx& c, cons
     if (lx >= T || ly >= T) return false;
     ic = (ly << TSH) + lx;
     const unsigned hh = (ly + 1u) * HS + lx + 1u;
-    const float4 row = c.s_q[hh];
     const U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)c.g, (unsigned)(c.g >> 32), p.k0, p.k1 ^ TAG_POLICY);
-    const int a = (u01(w.x) < c.eps) ? (int)(w.y & 3u) : argmax4(row);
+    const int a = (u01(w.x) < c.eps) ? (int)(w.y & 3u) : argmax4(c.s_q[hh]);
+    act = (unsigned)a;
     const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
     int nx = x + dx, ny = y + dy;
     const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
     const unsigned ht = (unsigned)((int)hh + dy * (int)HS + dx);          // inside the halo whenever the move is in bounds
     const bool moved = inb && !(c.s_cls[inb ? ht : hh] & CW_OBST);
-    const unsigned h2 = moved ? ht : hh;
     nx = moved ? nx : x; ny = moved ? ny : y;
-    const bool done = (c.s_cls[h2] & CW_GOAL) != 0;
-    const float r = done ? 1.0f : -0.01f;
-    float m = 0.0f;
-    if (!done) { m = max4(c.s_q[h2]); if (p.legacy_clamp && m < 0.0f) m = 0.0f; }
-    const float d = __fmaf_rn(p.gamma, m, r);                             // TD target from Q_t; the error is taken in fold()
-    if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = r; p.tr_d[e] = done ? 1 : 0; }
-    key = (e << 2) | (unsigned)a; val = __float_as_uint(d);
+    const bool done = (c.s_cls[moved ? ht : hh] & CW_GOAL) != 0;
+    if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = done ? 1.0f : -0.01f; p.tr_d[e] = done ? 1 : 0; }
     // episode bookkeeping and the record of the next step
     const bool timeout = !done && p.max_steps > 0 && t + 1 >= p.max_steps;
     int nt = t + 1;
@@ -252,34 +241,50 @@ __device__ __forceinline__ bool step_env(const Params& p, const StepCtx& c, cons
     return true;
 }
 
+// Q_{t+1} row of one cell from Q_t (still intact in s_q) and the number of environments that chose each action
+// (`w`: 16 bits per action, or `n32` when the tile counts in 32 bits).  Only the actions that were chosen are visited.
+template <unsigned TSH>
+__device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c, unsigned ic, unsigned long long w, const unsigned* n32) {
+    constexpr unsigned T = 1u << TSH, HS = T + 2u;
+    const unsigned lx = ic & (T - 1u), ly = ic >> TSH, hh = (ly + 1u) * HS + lx + 1u;
+    const int x = c.tx0 + (int)lx, y = c.ty0 + (int)ly;
+    float4 row = c.s_q[hh];
+    unsigned mask = n32 ? ((n32[0] != 0u) | ((n32[1] != 0u) << 1) | ((n32[2] != 0u) << 2) | ((n32[3] != 0u) << 3))
+                        : (((w & 0xFFFFull) != 0ull) | (((w >> 16) & 0xFFFFull) != 0ull) << 1 | (((w >> 32) & 0xFFFFull) != 0ull) << 2 | ((w >> 48) != 0ull) << 3);
+    while (mask) {
+        const int a = __ffs((int)mask) - 1; mask &= mask - 1u;
+        const unsigned n = n32 ? n32[a] : (unsigned)(w >> (16 * a)) & 0xFFFFu;
+        const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
+        const int nx = x + dx, ny = y + dy;
+        const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
+        const unsigned ht = (unsigned)((int)hh + dy * (int)HS + dx);
+        const bool moved = inb && !(c.s_cls[inb ? ht : hh] & CW_OBST);
+        const unsigned h2 = moved ? ht : hh;
+        const bool done = (c.s_cls[h2] & CW_GOAL) != 0;
+        float m = 0.0f;
+        if (!done) { m = max4(c.s_q[h2]); if (p.legacy_clamp && m < 0.0f) m = 0.0f; }
+        const float d = __fmaf_rn(p.gamma, m, done ? 1.0f : -0.01f);     // the TD target of (cell, a), from Q_t
+        float v = pick(row, a);
+        for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(d, v), v);       // one application per environment
+        row.x = a == 0 ? v : row.x; row.y = a == 1 ? v : row.y; row.z = a == 2 ? v : row.z; row.w = a == 3 ? v : row.w;
+    }
+    return row;
+}
+
 template <bool TRACE, unsigned TSH>
 __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
     constexpr unsigned T = 1u << TSH, HS = T + 2u, T2 = T * T, HS2 = HS * HS;
+    constexpr unsigned CPT = (T2 + CT - 1u) / CT;              // cells per consumer thread when every cell is occupied
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long s_full[2], s_done[2];
     __shared__ TileHdr s_hdr[2];
-    __shared__ unsigned s_stay, s_nocc, s_nent, s_base, s_abort, s_nb;
+    __shared__ unsigned s_stay, s_nocc, s_base, s_abort;
     __shared__ unsigned s_goals, s_timeouts, s_conf, s_nbig, s_nbigent, s_bad;     // accumulated over the block's tiles
-    __shared__ unsigned s_big[BIG_LIST];
 
     const TileP& tp = p.tp;
     const unsigned stage_bytes = HS2 * 16u + RC * 16u + RCB * 16u + tp.cls_stride;
-    unsigned char* work = smem + 2u * stage_bytes;
-    // chained path
-    unsigned* s_head = reinterpret_cast<unsigned*>(work);
-    unsigned* s_cb = s_head + T2;
-    unsigned* s_key = s_cb + T2;
-    unsigned* s_val = s_key + NL;
-    uint2* s_sorted2 = reinterpret_cast<uint2*>(s_val + NL);
-    unsigned short* s_next = reinterpret_cast<unsigned short*>(s_sorted2 + NL);
-    unsigned short* s_cell = s_next + NL;
-    unsigned short* s_mlist = s_cell + NL;
-    // counting-sort path (same bytes)
-    uint2* s_sorted = reinterpret_cast<uint2*>(work);
-    unsigned* s_cnt = reinterpret_cast<unsigned*>(s_sorted + CH);
-    unsigned* s_cur = s_cnt + T2;
-    unsigned short* s_list = reinterpret_cast<unsigned short*>(s_cur + T2);
-    unsigned short* s_ecell = s_list + T2;
+    unsigned long long* s_n = reinterpret_cast<unsigned long long*>(smem + 2u * stage_bytes);
+    unsigned short* s_list = reinterpret_cast<unsigned short*>(s_n + T2);
 
     const unsigned tid = threadIdx.x, lane = tid & 31u;
     const unsigned long long g = p.step;
@@ -298,10 +303,22 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
     __syncthreads();
 
     if (tid >= CT) {
-        // =========================== producer: one thread moves all the data ===========================
-        if (tid != CT) return;
+        // =========================== producer warp: moves all the data ===================================
+        // Lane r issues the bulk copies of rows r and r + 32, so a tile's copies are issued in a few instructions
+        // per lane; the region header of the tile to load next is fetched BEFORE waiting for the consumers, so its
+        // round trip to global memory is off the path.
         const unsigned n_spill = min(tp.tctl[(unsigned)(g % 3ull)], p.N);
-        auto load_tile = [&](unsigned k) {                    // header + bulk copies of the block's k-th tile into stage k & 1
+        struct Raw { unsigned roff, fcap, rend, seg, arr; };
+        auto fetch_hdr = [&](unsigned k) -> Raw {
+            Raw r{0u, 0u, 0u, 0u, 0u};
+            if (k < ntl) {
+                const unsigned tile = blockIdx.x + k * gridDim.x;
+                r.roff = tp.reg_off[tile]; r.fcap = tp.front_cap[tile]; r.rend = tp.reg_off[tile + 1u];
+                r.seg = tp.seg_cnt[par][tile]; r.arr = tp.arr_cnt[par][tile];
+            }
+            return r;
+        };
+        auto load_tile = [&](unsigned k, const Raw& raw) {    // header + bulk copies of the block's k-th tile into stage k & 1
             const unsigned b = k & 1u, tile = blockIdx.x + k * gridDim.x;
             unsigned char* st = smem + b * stage_bytes;
             float4* s_q = reinterpret_cast<float4*>(st);
@@ -309,37 +326,41 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
             int4* s_recb = s_rec + RC;
             unsigned char* s_cls = reinterpret_cast<unsigned char*>(s_recb + RCB);
             const int tx0 = (int)((tile % tp.tiles_x) << TSH), ty0 = (int)((tile / tp.tiles_x) << TSH);
-            const unsigned roff = tp.reg_off[tile], fcap = tp.front_cap[tile], bcap = tp.reg_off[tile + 1u] - roff - fcap;
-            const unsigned n_front = min(tp.seg_cnt[par][tile], fcap), n_back = min(tp.arr_cnt[par][tile], bcap);
+            const unsigned roff = raw.roff, fcap = raw.fcap, bcap = raw.rend - roff - fcap;
+            const unsigned n_front = min(raw.seg, fcap), n_back = min(raw.arr, bcap);
             const unsigned nf_s = min(n_front, RC), nb_s = min(n_back, RCB);
-            TileHdr& h = s_hdr[b];
-            h.tile = tile; h.roff = roff; h.fcap = fcap; h.n_front = n_front; h.n_in = n_front + n_back; h.n_all = n_front + n_back + n_spill;
-            h.nf_s = nf_s; h.nb_s = nb_s; h.tx0 = tx0; h.ty0 = ty0;
             const int xs = max(tx0 - 1, 0), xe = min(tx0 + (int)T, p.W - 1);
             const int gy_lo = max(ty0 - 1, 0), gy_hi = min(ty0 + (int)T, p.H - 1);
             const unsigned bytes_h = (unsigned)(xe - xs + 1) * 16u;
-            mbar_arrive_expect_tx(&s_full[b], (unsigned)(gy_hi - gy_lo + 1) * bytes_h + tp.cls_stride + (nf_s + nb_s) * 16u);
-            if (nf_s) bulk_g2s(s_rec, in + roff, nf_s * 16u, &s_full[b]);
-            if (nb_s) bulk_g2s(s_recb, in + roff + fcap, nb_s * 16u, &s_full[b]);
-            bulk_g2s(s_cls, tp.tcls + (size_t)tile * tp.cls_stride, tp.cls_stride, &s_full[b]);
-            for (int gy = gy_lo; gy <= gy_hi; ++gy)
+            if (lane == 0) {
+                TileHdr& h = s_hdr[b];
+                h.tile = tile; h.roff = roff; h.fcap = fcap; h.n_front = n_front; h.n_in = n_front + n_back; h.n_all = n_front + n_back + n_spill;
+                h.nf_s = nf_s; h.nb_s = nb_s; h.tx0 = tx0; h.ty0 = ty0;
+                mbar_arrive_expect_tx(&s_full[b], (unsigned)(gy_hi - gy_lo + 1) * bytes_h + tp.cls_stride + (nf_s + nb_s) * 16u);
+                if (nf_s) bulk_g2s(s_rec, in + roff, nf_s * 16u, &s_full[b]);
+            }
+            if (lane == 1 && nb_s) bulk_g2s(s_recb, in + roff + fcap, nb_s * 16u, &s_full[b]);
+            if (lane == 2) bulk_g2s(s_cls, tp.tcls + (size_t)tile * tp.cls_stride, tp.cls_stride, &s_full[b]);
+            for (int gy = gy_lo + (int)lane; gy <= gy_hi; gy += 32)
                 bulk_g2s(s_q + (unsigned)(gy - (ty0 - 1)) * HS + (unsigned)(xs - (tx0 - 1)), Qin + (size_t)gy * (size_t)p.W + (size_t)xs, bytes_h, &s_full[b]);
         };
-        if (ntl > 0u) load_tile(0u);
-        if (ntl > 1u) load_tile(1u);
+        if (ntl > 0u) load_tile(0u, fetch_hdr(0u));
+        if (ntl > 1u) load_tile(1u, fetch_hdr(1u));
         for (unsigned k = 0; k < ntl; ++k) {
             const unsigned b = k & 1u;
-            if (!mbar_wait(&s_done[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); break; }
+            const Raw nxt = fetch_hdr(k + 2u);                 // in flight while this warp waits
+            if (!mbar_wait_long(&s_done[b], (k >> 1) & 1u)) { if (lane == 0) atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); break; }
             if (*(volatile unsigned*)&s_abort) break;
             // rows of Q_{t+1} out (the consumers fenced their writes towards the async proxy before arriving)
             const unsigned tile = blockIdx.x + k * gridDim.x;
             const int tx0 = (int)((tile % tp.tiles_x) << TSH), ty0 = (int)((tile / tp.tiles_x) << TSH);
             const unsigned wi = (unsigned)min((int)T, p.W - tx0), ri = (unsigned)min((int)T, p.H - ty0);
             const float4* s_q = reinterpret_cast<const float4*>(smem + b * stage_bytes);
-            for (unsigned r = 0; r < ri; ++r)
+            for (unsigned r = lane; r < ri; r += 32u)
                 bulk_s2g(Qout + (size_t)(ty0 + (int)r) * (size_t)p.W + (size_t)tx0, s_q + (r + 1u) * HS + 1u, wi * 16u);
             bulk_commit_wait_read();                            // the stage may be overwritten once its rows have been read
-            if (k + 2u < ntl) load_tile(k + 2u);
+            __syncwarp();
+            if (k + 2u < ntl) load_tile(k + 2u, nxt);
         }
         return;
     }
@@ -359,16 +380,25 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
         const int4* s_recb = s_rec + RC;
         c.s_q = s_q; c.s_cls = reinterpret_cast<const unsigned char*>(s_recb + RCB);
 
-        if (tid == 0) { s_stay = 0; s_nocc = 0; s_nent = 0; s_nb = 0; s_base = 0xFFFFFFFFu; }
+        if (tid == 0) { s_stay = 0; s_nocc = 0; s_base = 0xFFFFFFFFu; }
+        for (unsigned q = 2u * tid; q < T2; q += 2u * CT) *reinterpret_cast<uint4*>(s_n + q) = make_uint4(0u, 0u, 0u, 0u);
         if (!mbar_wait(&s_full[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
         const TileHdr h = s_hdr[b];
         const unsigned tile = h.tile, roff = h.roff, fcap = h.fcap, n_front = h.n_front, n_in = h.n_in, n_all = h.n_all, nf_s = h.nf_s, nb_s = h.nb_s;
         c.tx0 = h.tx0; c.ty0 = h.ty0; c.tile = tile; c.roff = roff; c.fcap = fcap;
-        const bool chained = n_all <= NL;                          // block-uniform
-        if (chained) { for (unsigned q = 4u * tid; q < T2; q += 4u * CT) *reinterpret_cast<uint4*>(s_head + q) = make_uint4(0u, 0u, 0u, 0u); }
-        else         { for (unsigned q = 4u * tid; q < T2; q += 4u * CT) *reinterpret_cast<uint4*>(s_cnt + q) = make_uint4(0u, 0u, 0u, 0u); }
+        const bool crowded = n_all > NMAX16;                        // block-uniform
+        if (crowded && tid == 0) {                                   // 4 x 32-bit counters per cell in global scratch
+            const unsigned need = T2 * 2u, q = atomicAdd(&tp.tctl[3u + par], need);
+            if (q + need <= p.N) s_base = q; else { s_base = 0xFFFFFFFEu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
+        }
         cons_sync();
         if (s_abort) break;                                    // never seen; the producer gives up at its next wait
+        unsigned* gcnt = nullptr;
+        if (crowded) {
+            if (s_base != 0xFFFFFFFEu) gcnt = reinterpret_cast<unsigned*>(tp.scratch + s_base);
+            if (gcnt) for (unsigned q = tid; q < T2 * 4u; q += CT) gcnt[q] = 0u;
+            cons_sync();
+        }
 
         // record j of this tile's input (front part, back part, then the spill list filtered by tile)
         auto fetch = [&](unsigned j, int4& r) -> bool {
@@ -377,199 +407,55 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
             r = ovf_in[j - n_in];
             return tile_of(tp, r.x, r.y) == tile;
         };
-        auto cell_hh = [&](unsigned ic) -> unsigned { return ((ic >> TSH) + 1u) * HS + (ic & (T - 1u)) + 1u; };
 
-        if (chained) {
-            // ---- the step: every record chains itself to the previous arrival at its cell ----------------
-#pragma unroll
-            for (unsigned q = 0; q < NL / CT; ++q) {
-                const unsigned j = tid + q * CT;
-                int4 rec; unsigned ic = 0, key = 0, val = 0;
-                bool ok = j < n_all && fetch(j, rec);
-                if (ok && !step_env<TRACE, TSH>(p, c, rec, ic, key, val)) { s_bad = 1u; ok = false; }
-                if (ok) {
-                    s_key[j] = key; s_val[j] = val; s_cell[j] = (unsigned short)ic;
-                    s_next[j] = (unsigned short)atomicExch(&s_head[ic], j + 1u);
-                } else if (j < NL) s_cell[j] = 0xFFFFu;
-            }
-            cons_sync();
-            // ---- alone on the cell: apply.  Otherwise: how many share the cell, how many of them have a smaller id ----
-            unsigned rank[NL / CT];
-#pragma unroll
-            for (unsigned q = 0; q < NL / CT; ++q) {
-                const unsigned j = tid + q * CT;
-                rank[q] = 0xFFFFFFFFu;
-                const unsigned ic = j < n_all ? s_cell[j] : 0xFFFFu;
-                if (ic == 0xFFFFu) continue;
-                const unsigned head = s_head[ic], key = s_key[j];
-                if (head == j + 1u && s_next[j] == 0u) {
-                    const unsigned hh = cell_hh(ic);
-                    float4 row = s_q[hh]; fold(row, (int)(key & 3u), p.lr, __uint_as_float(s_val[j])); s_q[hh] = row;
-                } else {
-                    unsigned cnt = 0, r = 0;
-                    for (unsigned z = head; z != 0u && cnt < NL; z = s_next[z - 1u]) { ++cnt; r += s_key[z - 1u] < key ? 1u : 0u; }
-                    rank[q] = r; conf += 1u;
-                    if (head == j + 1u) {                          // one member per cell reserves the cell's run of entries
-                        const unsigned base = atomicAdd(&s_nent, cnt);
-                        s_cb[ic] = base | (cnt << 16);
-                        s_mlist[atomicAdd(&s_nocc, 1u)] = (unsigned short)ic;
-                    }
-                }
-            }
-            cons_sync();
-#pragma unroll
-            for (unsigned q = 0; q < NL / CT; ++q) {
-                const unsigned j = tid + q * CT;
-                if (rank[q] != 0xFFFFFFFFu) s_sorted2[(s_cb[s_cell[j]] & 0xFFFFu) + rank[q]] = make_uint2(s_key[j], s_val[j]);
-            }
-            cons_sync();
-            for (unsigned q = tid; q < s_nocc; q += CT) {
-                const unsigned ic = s_mlist[q], cb = s_cb[ic], cnt = cb >> 16, hh = cell_hh(ic);
-                float4 row = s_q[hh];
-                fold_entries(row, s_sorted2 + (cb & 0xFFFFu), cnt, p.lr);
-                s_q[hh] = row;
-                if (cnt > SMALL_MAX) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, cnt); }
-            }
-        } else {
-            // ---- crowded tile, pass A: occupants per cell ------------------------------------------------------
-            for (unsigned j = tid; j < n_all; j += CT) {
-                int4 r;
-                if (!fetch(j, r)) continue;
-                const unsigned lx = (unsigned)(r.x - c.tx0), ly = (unsigned)(r.y - c.ty0);
-                if (lx >= T || ly >= T) { s_bad = 1u; continue; }
-                atomicAdd(&s_cnt[(ly << TSH) + lx], 1u);
-            }
-            cons_sync();
-            // ---- occupied cells: space for their entries (one atomic per warp), and their list -------------------
-            for (unsigned base = 0; base < T2; base += 4u * CT) {
-                const unsigned c0 = base + 4u * tid;
-                uint4 cc = make_uint4(0u, 0u, 0u, 0u);
-                if (c0 < T2) cc = *reinterpret_cast<const uint4*>(s_cnt + c0);
-                const unsigned m = cc.x + cc.y + cc.z + cc.w, nm = (cc.x != 0u) + (cc.y != 0u) + (cc.z != 0u) + (cc.w != 0u);
-                unsigned im = m, il = nm;                              // inclusive prefixes over the warp: entries, listed cells
-                for (int o = 1; o < 32; o <<= 1) {
-                    const unsigned t1 = __shfl_up_sync(FULL, im, o), t2 = __shfl_up_sync(FULL, il, o);
-                    if (lane >= (unsigned)o) { im += t1; il += t2; }
-                }
-                const unsigned totm = __shfl_sync(FULL, im, 31), totl = __shfl_sync(FULL, il, 31);
-                unsigned wb_e = 0, wb_l = 0;
-                if (lane == 0 && totl) { wb_e = atomicAdd(&s_nent, totm); wb_l = atomicAdd(&s_nocc, totl); }
-                wb_e = __shfl_sync(FULL, wb_e, 0) + im - m; wb_l = __shfl_sync(FULL, wb_l, 0) + il - nm;
-                if (c0 < T2 && m) {
-                    *reinterpret_cast<uint4*>(s_cur + c0) = make_uint4(wb_e, wb_e + cc.x, wb_e + cc.x + cc.y, wb_e + cc.x + cc.y + cc.z);
-                    unsigned li = wb_l;
-                    if (cc.x) s_list[li++] = (unsigned short)c0;
-                    if (cc.y) s_list[li++] = (unsigned short)(c0 + 1u);
-                    if (cc.z) s_list[li++] = (unsigned short)(c0 + 2u);
-                    if (cc.w) s_list[li++] = (unsigned short)(c0 + 3u);
-                }
-            }
-            cons_sync();
-            const unsigned nent = s_nent, nocc = s_nocc;
-            if (nent > CH) {                                      // too many for shared memory: a slice of the global scratch (block-uniform branch)
-                if (tid == 0) {
-                    const unsigned q = atomicAdd(&tp.tctl[3u + par], nent);
-                    if (q + nent <= p.N) s_base = q; else { s_base = 0xFFFFFFFEu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
-                }
-                cons_sync();
-            }
-            const bool in_smem = s_base == 0xFFFFFFFFu, usable = s_base != 0xFFFFFFFEu;
-            uint2* sorted = in_smem ? s_sorted : tp.scratch + (usable ? s_base : 0u);
-            // ---- pass B: the step itself ----------------------------------------------------------------------
-            for (unsigned j = tid; j < n_all; j += CT) {
-                int4 rec; unsigned ic, key, val;
-                if (!fetch(j, rec)) continue;
-                if (!step_env<TRACE, TSH>(p, c, rec, ic, key, val)) continue;
-                if (s_cnt[ic] > 1u) conf += 1u;
-                if (usable) {
-                    const unsigned pos = atomicAdd(&s_cur[ic], 1u);
-                    sorted[pos] = make_uint2(key, val);
-                    if (in_smem) s_ecell[pos] = (unsigned short)ic;
-                }
-            }
-            cons_sync();
-            // ---- order the entries of each cell by environment id, then apply them: Q_t -> Q_{t+1} in place ------
-            if (in_smem) {
-                // every entry counts the entries of its cell with a smaller id (ids are unique): that is its place
-                uint2 ent[EPT]; unsigned dst[EPT];
-#pragma unroll
-                for (unsigned q = 0; q < EPT; ++q) {
-                    const unsigned pos = tid + q * CT;
-                    dst[q] = 0xFFFFFFFFu; ent[q] = make_uint2(0u, 0u);
-                    if (pos < nent) {
-                        ent[q] = s_sorted[pos];
-                        const unsigned ic = s_ecell[pos], cnt = s_cnt[ic];
-                        if (cnt > 1u) {
-                            const unsigned start = s_cur[ic] - cnt;
-                            unsigned r = 0;
-                            for (unsigned z = start; z < start + cnt; ++z) r += s_sorted[z].x < ent[q].x ? 1u : 0u;
-                            dst[q] = start + r;
-                        }
-                    }
-                }
-                cons_sync();
-#pragma unroll
-                for (unsigned q = 0; q < EPT; ++q) if (dst[q] != 0xFFFFFFFFu) s_sorted[dst[q]] = ent[q];
-                cons_sync();
-                for (unsigned q = tid; q < nocc; q += CT) {
-                    const unsigned ic = s_list[q], cnt = s_cnt[ic], hh = cell_hh(ic);
-                    float4 row = s_q[hh];
-                    fold_entries(row, s_sorted + (s_cur[ic] - cnt), cnt, p.lr);
-                    s_q[hh] = row;
-                    if (cnt > SMALL_MAX) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, cnt); }
-                }
-            } else if (usable) {
-                // entries in global scratch: small cells are ordered by their own thread, large ones by all consumers
-                for (unsigned q = tid; q < nocc; q += CT) {
-                    const unsigned ic = s_list[q], cnt = s_cnt[ic];
-                    if (cnt <= SMALL_MAX) {
-                        uint2* e = sorted + (s_cur[ic] - cnt);
-                        for (unsigned i = 1; i < cnt; ++i) {
-                            const uint2 v = e[i]; unsigned z = i;
-                            while (z > 0 && e[z - 1u].x > v.x) { e[z] = e[z - 1u]; --z; }
-                            e[z] = v;
-                        }
-                        const unsigned hh = cell_hh(ic);
-                        float4 row = s_q[hh];
-                        fold_entries(row, e, cnt, p.lr);
-                        s_q[hh] = row;
-                    } else {
-                        const unsigned kb = atomicAdd(&s_nb, 1u);
-                        if (kb < BIG_LIST) s_big[kb] = ic;
-                        atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, cnt);
-                    }
-                }
-                cons_sync();
-                const unsigned nb = s_nb;
-                if (nb && nb <= BIG_LIST) {
-                    for (unsigned q = 0; q < nb; ++q) { const unsigned ic = s_big[q], cnt = s_cnt[ic]; cons_sort_u2(sorted + (s_cur[ic] - cnt), cnt); }
-                    for (unsigned q = tid; q < nb; q += CT) {
-                        const unsigned ic = s_big[q], cnt = s_cnt[ic], hh = cell_hh(ic);
-                        float4 row = s_q[hh];
-                        fold_entries(row, sorted + (s_cur[ic] - cnt), cnt, p.lr);
-                        s_q[hh] = row;
-                    }
-                } else if (nb) {
-                    for (unsigned q = 0; q < nocc; ++q) { const unsigned ic = s_list[q], cnt = s_cnt[ic]; if (cnt > SMALL_MAX) cons_sort_u2(sorted + (s_cur[ic] - cnt), cnt); }
-                    for (unsigned q = tid; q < nocc; q += CT) {
-                        const unsigned ic = s_list[q], cnt = s_cnt[ic];
-                        if (cnt <= SMALL_MAX) continue;
-                        const unsigned hh = cell_hh(ic);
-                        float4 row = s_q[hh];
-                        fold_entries(row, sorted + (s_cur[ic] - cnt), cnt, p.lr);
-                        s_q[hh] = row;
-                    }
-                }
-            }
+        // ---- the step: every environment acts, moves and counts itself in its cell's histogram ----------
+        for (unsigned j = tid; j < n_all; j += CT) {
+            int4 rec; unsigned ic, a;
+            if (!fetch(j, rec)) continue;
+            if (!step_env<TRACE, TSH>(p, c, rec, ic, a)) { s_bad = 1u; continue; }
+            if (!crowded) {
+                const unsigned long long old = atomicAdd(&s_n[ic], 1ull << (16u * a));
+                if (old == 0ull) s_list[atomicAdd(&s_nocc, 1u)] = (unsigned short)ic;      // first one on the cell lists it
+            } else if (gcnt) atomicAdd(&gcnt[ic * 4u + a], 1u);
         }
-        // hand the stage to the producer: rows written through the generic proxy, read by the bulk copy
-        fence_async_smem();
-        mbar_arrive(&s_done[b]);
-        cons_sync();                                                      // s_stay is final; nobody is still in this tile's work space
+        cons_sync();
         if (tid == 0) {
             tp.seg_cnt[par ^ 1u][tile] = min(s_stay, fcap);
             tp.arr_cnt[par][tile] = 0u;                                   // consumed; it is the append counter again in the next step
         }
+
+        // ---- Q_{t+1} of the occupied cells: computed from Q_t into registers, written after everybody has read ---
+        float4 nrow[CPT]; unsigned nh[CPT];
+        const unsigned nocc = crowded ? T2 : s_nocc;
+#pragma unroll
+        for (unsigned q = 0; q < CPT; ++q) {
+            const unsigned idx = tid + q * CT;
+            nh[q] = 0xFFFFFFFFu;
+            if (idx >= nocc) continue;
+            unsigned ic, tot; unsigned long long w = 0ull; unsigned n32[4];
+            if (!crowded) {
+                ic = s_list[idx];
+                w = s_n[ic];
+                tot = ((unsigned)w & 0xFFFFu) + ((unsigned)(w >> 16) & 0xFFFFu) + ((unsigned)(w >> 32) & 0xFFFFu) + (unsigned)(w >> 48);
+            } else {
+                ic = idx;
+                if (!gcnt) continue;
+                const uint4 v = *reinterpret_cast<const uint4*>(gcnt + 4u * ic);
+                n32[0] = v.x; n32[1] = v.y; n32[2] = v.z; n32[3] = v.w;
+                tot = v.x + v.y + v.z + v.w;
+            }
+            if (!tot) continue;
+            if (tot > 1u) conf += tot;
+            if (tot > SMALL_MAX) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, tot); }
+            nrow[q] = updated_row<TSH>(p, c, ic, w, crowded ? n32 : nullptr);
+            nh[q] = ((ic >> TSH) + 1u) * HS + (ic & (T - 1u)) + 1u;
+        }
+        cons_sync();
+#pragma unroll
+        for (unsigned q = 0; q < CPT; ++q) if (nh[q] != 0xFFFFFFFFu) s_q[nh[q]] = nrow[q];
+        // hand the stage to the producer: rows written through the generic proxy, read by the bulk copy
+        fence_async_smem();
+        mbar_arrive(&s_done[b]);
     }
     for (int o = 16; o; o >>= 1) conf += __shfl_xor_sync(FULL, conf, o);
     if (lane == 0u && conf) atomicAdd(&s_conf, conf);
@@ -684,11 +570,7 @@ __global__ void k_q_average_dense(float4* table, const float4* gathered, unsigne
 // ------------------------------------------------------------------------------------------------
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 
-static size_t work_bytes(size_t T2) {
-    const size_t chained = 2 * T2 * 4 + 2 * (size_t)NL * 4 + (size_t)NL * 8 + 2 * (size_t)NL * 2 + (size_t)NL;
-    const size_t counting = (size_t)CH * 8 + 2 * T2 * 4 + T2 * 2 + (size_t)CH * 2;
-    return ((chained > counting ? chained : counting) + 15) / 16 * 16;
-}
+static size_t work_bytes(size_t T2) { return (T2 * 8 + T2 * 2 + 15) / 16 * 16; }
 size_t tile_step_smem(const Params& p) {
     const size_t T = p.tp.T, HS = T + 2;
     const size_t stage = HS * HS * 16 + (size_t)RC * 16 + (size_t)RCB * 16 + p.tp.cls_stride;

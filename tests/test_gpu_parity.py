@@ -167,6 +167,14 @@ def test_lockstep_dense_collisions(pkg, orc):
         assert s.long_chains > 0 or n < 512
 
 
+def test_lockstep_one_tile_beyond_16_bit_counts(pkg, orc):
+    """More environments in one tile than the 16-bit per-action counters of the step kernel hold: the tile counts
+    in 32-bit counters in global memory instead."""
+    cfg = pkg.make_config(3, 2, 70000, start_mode=pkg.START_RANDOM, eps_kind=pkg.EPS_FIXED, eps0=0.3, max_steps=5, lr=0.2)
+    gpu, cpu = pair(pkg, orc, cfg, threads=4)
+    lockstep(gpu, cpu, 8, what="70000 on 3x2")
+
+
 def test_lockstep_legacy_clamp_and_walls(pkg, orc):
     cfg = pkg.preset("C4", num_envs=20000)
     cfg.width = cfg.height = 96
