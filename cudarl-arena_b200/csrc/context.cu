@@ -354,6 +354,8 @@ int alloc_tiles(cudarl_ctx* c) {
     tp.tiles_x = (unsigned)((p.W + (int)tp.T - 1) >> tsh); tp.tiles_y = (unsigned)((p.H + (int)tp.T - 1) >> tsh);
     tp.ntiles = tp.tiles_x * tp.tiles_y;
     tp.ch = 512;
+    tp.ct = (N / ((size_t)tp.tiles_x * tp.tiles_y) <= 72) ? 96u : 256u;
+    if (const char* ev = getenv("CUDARL_TILE_CT")) { int v = atoi(ev); if (v == 96 || v == 256) tp.ct = (unsigned)v; }
     for (int k = 0; k < 2; ++k) {
         CK(cudaMalloc(&c->dQd[k], S * sizeof(float4)));
         CK(cudaMalloc(&c->drec[k], (N + N / 2 + 96 * (size_t)tp.ntiles + 64) * sizeof(int4)));

@@ -53,6 +53,7 @@ struct TileP {
     unsigned tshift, T;        // tile edge = 1 << tshift cells
     unsigned tiles_x, tiles_y, ntiles;
     unsigned ch;               // entries a block can sort in shared memory; fuller tiles use `scratch`
+    unsigned ct;               // consumer threads per block of the step kernel: 256, or 96 for small tiles
     unsigned grid;             // blocks of the persistent step kernel (SMs x resident blocks per SM)
     float4* Qd[2];             // dense table, one float4 (4 action values) per cell; [step & 1] is current
     int4* rec[2];              // records {x, y, t, id}; [step & 1] is current

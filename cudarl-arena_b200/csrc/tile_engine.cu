@@ -164,12 +164,15 @@ __device__ __forceinline__ bool mbar_wait_long(unsigned long long* bar, unsigned
 // Consumer work space, shared by both stages:
 //             s_n    T*T   u64      per cell: how many environments chose action a, 16 bits per action
 //             s_list T*T   u16      occupied cells
+//             s_flag T*T/32 u32     one bit per cell: already listed
 // A tile with more than 65,535 records counts in 32-bit counters in global scratch instead.
 // full[stage] : the producer's copies have landed (transaction barrier);  done[stage] : every consumer thread
 // has finished the tile in that stage.
-constexpr unsigned CT = 256;         // consumer threads
-constexpr unsigned TBLOCK = CT + 32; // + the producer warp
-constexpr unsigned RC = 352, RCB = 96;   // records staged in shared memory (front part, back part); the rest is read from global memory
+// CT consumer threads (+ 32 of the producer warp) per block: 256 for tiles that hold a few hundred environments, 96 for
+// small tiles (fewer threads per block = more blocks, i.e. more tiles in flight, per SM).
+// Records staged in shared memory (front part, back part of the region); the rest is read from global memory.
+__host__ __device__ constexpr unsigned rc_front(unsigned ct) { return ct + ct / 4u + 32u; }
+__host__ __device__ constexpr unsigned rc_back(unsigned ct) { return ct / 4u + 32u; }
 constexpr unsigned NMAX16 = 65535u;  // records of a tile the 16-bit counters can hold
 
 struct TileHdr {                     // what the producer tells the consumers about the tile in a stage
@@ -177,7 +180,7 @@ struct TileHdr {                     // what the producer tells the consumers ab
     int tx0, ty0;
 };
 
-__device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+template <unsigned CT> __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" :: "n"(CT) : "memory"); }
 
 // Everything the per-environment step needs about the tile being processed.
 struct StepCtx {
@@ -271,9 +274,10 @@ __device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c,
     return row;
 }
 
-template <bool TRACE, unsigned TSH>
-__global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
+template <bool TRACE, unsigned TSH, unsigned CT>
+__global__ void __launch_bounds__(CT + 32u, CT == 256u ? 3 : 6) k_tile_step(Params p) {
     constexpr unsigned T = 1u << TSH, HS = T + 2u, T2 = T * T, HS2 = HS * HS;
+    constexpr unsigned RC = rc_front(CT), RCB = rc_back(CT);
     constexpr unsigned CPT = (T2 + CT - 1u) / CT;              // cells per consumer thread when every cell is occupied
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long s_full[2], s_done[2];
@@ -285,6 +289,7 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
     const unsigned stage_bytes = HS2 * 16u + RC * 16u + RCB * 16u + tp.cls_stride;
     unsigned long long* s_n = reinterpret_cast<unsigned long long*>(smem + 2u * stage_bytes);
     unsigned short* s_list = reinterpret_cast<unsigned short*>(s_n + T2);
+    unsigned* s_flag = reinterpret_cast<unsigned*>(s_list + T2);       // one bit per cell: listed
 
     const unsigned tid = threadIdx.x, lane = tid & 31u;
     const unsigned long long g = p.step;
@@ -349,7 +354,9 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
         for (unsigned k = 0; k < ntl; ++k) {
             const unsigned b = k & 1u;
             const Raw nxt = fetch_hdr(k + 2u);                 // in flight while this warp waits
-            if (!mbar_wait_long(&s_done[b], (k >> 1) & 1u)) { if (lane == 0) atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); break; }
+            // one lane polls; the others park at the warp barrier instead of spinning
+            if (lane == 0 && !mbar_wait_long(&s_done[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
+            __syncwarp();
             if (*(volatile unsigned*)&s_abort) break;
             // rows of Q_{t+1} out (the consumers fenced their writes towards the async proxy before arriving)
             const unsigned tile = blockIdx.x + k * gridDim.x;
@@ -382,22 +389,25 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
 
         if (tid == 0) { s_stay = 0; s_nocc = 0; s_base = 0xFFFFFFFFu; }
         for (unsigned q = 2u * tid; q < T2; q += 2u * CT) *reinterpret_cast<uint4*>(s_n + q) = make_uint4(0u, 0u, 0u, 0u);
-        if (!mbar_wait(&s_full[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
+        for (unsigned q = tid; q < (T2 + 31u) / 32u; q += CT) s_flag[q] = 0u;
+        // one thread waits for the copies; the barrier below passes the news (and the data) on to the others
+        if (tid == 0 && !mbar_wait(&s_full[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
+        cons_sync<CT>();
+        if (s_abort) break;                                    // never seen; the producer gives up at its next wait
         const TileHdr h = s_hdr[b];
         const unsigned tile = h.tile, roff = h.roff, fcap = h.fcap, n_front = h.n_front, n_in = h.n_in, n_all = h.n_all, nf_s = h.nf_s, nb_s = h.nb_s;
         c.tx0 = h.tx0; c.ty0 = h.ty0; c.tile = tile; c.roff = roff; c.fcap = fcap;
         const bool crowded = n_all > NMAX16;                        // block-uniform
-        if (crowded && tid == 0) {                                   // 4 x 32-bit counters per cell in global scratch
-            const unsigned need = T2 * 2u, q = atomicAdd(&tp.tctl[3u + par], need);
-            if (q + need <= p.N) s_base = q; else { s_base = 0xFFFFFFFEu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
-        }
-        cons_sync();
-        if (s_abort) break;                                    // never seen; the producer gives up at its next wait
         unsigned* gcnt = nullptr;
-        if (crowded) {
+        if (crowded) {                                               // 4 x 32-bit counters per cell in global scratch
+            if (tid == 0) {
+                const unsigned need = T2 * 2u, q = atomicAdd(&tp.tctl[3u + par], need);
+                if (q + need <= p.N) s_base = q; else { s_base = 0xFFFFFFFEu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
+            }
+            cons_sync<CT>();
             if (s_base != 0xFFFFFFFEu) gcnt = reinterpret_cast<unsigned*>(tp.scratch + s_base);
             if (gcnt) for (unsigned q = tid; q < T2 * 4u; q += CT) gcnt[q] = 0u;
-            cons_sync();
+            cons_sync<CT>();
         }
 
         // record j of this tile's input (front part, back part, then the spill list filtered by tile)
@@ -414,11 +424,15 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
             if (!fetch(j, rec)) continue;
             if (!step_env<TRACE, TSH>(p, c, rec, ic, a)) { s_bad = 1u; continue; }
             if (!crowded) {
-                const unsigned long long old = atomicAdd(&s_n[ic], 1ull << (16u * a));
-                if (old == 0ull) s_list[atomicAdd(&s_nocc, 1u)] = (unsigned short)ic;      // first one on the cell lists it
+                // 32-bit shared-memory atomics are native; the 64-bit word of a cell is counted in its two halves
+                const unsigned old = atomicAdd(reinterpret_cast<unsigned*>(s_n) + 2u * ic + (a >> 1), 1u << (16u * (a & 1u)));
+                if (old == 0u) {                                                           // first on this half: maybe first on the cell
+                    const unsigned bit = 1u << (ic & 31u);
+                    if (!(atomicOr(&s_flag[ic >> 5], bit) & bit)) s_list[atomicAdd(&s_nocc, 1u)] = (unsigned short)ic;
+                }
             } else if (gcnt) atomicAdd(&gcnt[ic * 4u + a], 1u);
         }
-        cons_sync();
+        cons_sync<CT>();
         if (tid == 0) {
             tp.seg_cnt[par ^ 1u][tile] = min(s_stay, fcap);
             tp.arr_cnt[par][tile] = 0u;                                   // consumed; it is the append counter again in the next step
@@ -450,7 +464,7 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
             nrow[q] = updated_row<TSH>(p, c, ic, w, crowded ? n32 : nullptr);
             nh[q] = ((ic >> TSH) + 1u) * HS + (ic & (T - 1u)) + 1u;
         }
-        cons_sync();
+        cons_sync<CT>();
 #pragma unroll
         for (unsigned q = 0; q < CPT; ++q) if (nh[q] != 0xFFFFFFFFu) s_q[nh[q]] = nrow[q];
         // hand the stage to the producer: rows written through the generic proxy, read by the bulk copy
@@ -459,7 +473,7 @@ __global__ void __launch_bounds__(TBLOCK, 3) k_tile_step(Params p) {
     }
     for (int o = 16; o; o >>= 1) conf += __shfl_xor_sync(FULL, conf, o);
     if (lane == 0u && conf) atomicAdd(&s_conf, conf);
-    cons_sync();
+    cons_sync<CT>();
     if (tid == 0) {
         if (s_conf) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_conf);
         if (s_goals) atomicAdd(&p.ctl->goals, (unsigned long long)s_goals);
@@ -570,30 +584,36 @@ __global__ void k_q_average_dense(float4* table, const float4* gathered, unsigne
 // ------------------------------------------------------------------------------------------------
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 
-static size_t work_bytes(size_t T2) { return (T2 * 8 + T2 * 2 + 15) / 16 * 16; }
+static size_t work_bytes(size_t T2) { return (T2 * 8 + T2 * 2 + (T2 + 31) / 32 * 4 + 15) / 16 * 16; }
 size_t tile_step_smem(const Params& p) {
     const size_t T = p.tp.T, HS = T + 2;
-    const size_t stage = HS * HS * 16 + (size_t)RC * 16 + (size_t)RCB * 16 + p.tp.cls_stride;
+    const size_t stage = HS * HS * 16 + (size_t)rc_front(p.tp.ct) * 16 + (size_t)rc_back(p.tp.ct) * 16 + p.tp.cls_stride;
     return 2 * stage + work_bytes(T * T);
 }
-template <unsigned TSH>
+template <unsigned TSH, unsigned CT>
 static cudaError_t configure_one(int bytes, int* per_sm) {
-    cudaError_t e = cudaFuncSetAttribute(k_tile_step<false, TSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_tile_step<true, TSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH>, (int)TBLOCK, (size_t)bytes);
+    cudaError_t e = cudaFuncSetAttribute(k_tile_step<false, TSH, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_tile_step<true, TSH, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH, CT>, (int)(CT + 32u), (size_t)bytes);
     return e;
+}
+template <unsigned CT>
+static cudaError_t configure_ct(unsigned tshift, int bytes, int* per_sm) {
+    switch (tshift) {
+        case 3: return configure_one<3, CT>(bytes, per_sm);
+        case 4: return configure_one<4, CT>(bytes, per_sm);
+        case 5: return configure_one<5, CT>(bytes, per_sm);
+        default: return cudaErrorInvalidValue;
+    }
 }
 int tile_engine_configure(Params& p, int device) {
     const int bytes = (int)tile_step_smem(p);
     int sms = 0, per_sm = 0;
     cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     if (e != cudaSuccess) return (int)e;
-    switch (p.tp.tshift) {
-        case 3: e = configure_one<3>(bytes, &per_sm); break;
-        case 4: e = configure_one<4>(bytes, &per_sm); break;
-        case 5: e = configure_one<5>(bytes, &per_sm); break;
-        default: return (int)cudaErrorInvalidValue;
-    }
+    if (p.tp.ct == 96u) e = configure_ct<96>(p.tp.tshift, bytes, &per_sm);
+    else if (p.tp.ct == 256u) e = configure_ct<256>(p.tp.tshift, bytes, &per_sm);
+    else return (int)cudaErrorInvalidValue;
     if (e != cudaSuccess) return (int)e;
     if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
     p.tp.grid = (unsigned)(sms * per_sm);
@@ -611,20 +631,25 @@ void launch_tile_export(const Params& p, cudaStream_t st) {
     k_te_export_ovf<<<64, BLOCK, 0, st>>>(p);
 }
 static unsigned tile_step_grid(const Params& p) { return p.tp.ntiles < p.tp.grid ? p.tp.ntiles : p.tp.grid; }
-template <unsigned TSH>
+template <unsigned TSH, unsigned CT>
 static void launch_step_one(const Params& p, bool trace, unsigned grid, size_t smem, cudaStream_t st) {
-    if (trace) k_tile_step<true, TSH><<<grid, TBLOCK, smem, st>>>(p);
-    else       k_tile_step<false, TSH><<<grid, TBLOCK, smem, st>>>(p);
+    if (trace) k_tile_step<true, TSH, CT><<<grid, CT + 32u, smem, st>>>(p);
+    else       k_tile_step<false, TSH, CT><<<grid, CT + 32u, smem, st>>>(p);
+}
+template <unsigned CT>
+static void launch_step_ct(const Params& p, bool trace, unsigned grid, size_t smem, cudaStream_t st) {
+    switch (p.tp.tshift) {
+        case 3: launch_step_one<3, CT>(p, trace, grid, smem, st); break;
+        case 4: launch_step_one<4, CT>(p, trace, grid, smem, st); break;
+        default: launch_step_one<5, CT>(p, trace, grid, smem, st); break;
+    }
 }
 void launch_tile_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c) {
     const size_t smem = tile_step_smem(p);
     const unsigned grid = tile_step_grid(p);
     if (ev_a) cudaEventRecord(ev_a, st);
-    switch (p.tp.tshift) {
-        case 3: launch_step_one<3>(p, trace, grid, smem, st); break;
-        case 4: launch_step_one<4>(p, trace, grid, smem, st); break;
-        default: launch_step_one<5>(p, trace, grid, smem, st); break;
-    }
+    if (p.tp.ct == 96u) launch_step_ct<96>(p, trace, grid, smem, st);
+    else                launch_step_ct<256>(p, trace, grid, smem, st);
     if (ev_b) cudaEventRecord(ev_b, st);
     if (p.eps_from_ctl) k_tile_eps_episode<<<1, 1, 0, st>>>(p);
     if (ev_c) cudaEventRecord(ev_c, st);
