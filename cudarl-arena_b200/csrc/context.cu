@@ -74,26 +74,22 @@ struct cudarl_ctx {
     std::string err;
     std::vector<uint8_t> cells;           // host copy of the cell classes
     // device buffers
-    void *dQ = nullptr, *dci = nullptr, *dreward = nullptr, *ddone = nullptr;
-    void *dstate[2] = {nullptr, nullptr};   // int4 {x,y,t,id} per slot: two copies (sort target / export scratch)
+    void *dci = nullptr, *dreward = nullptr, *ddone = nullptr;
+    void *dstate[2] = {nullptr, nullptr};   // int4 {x,y,t,id} per environment, and a scratch copy of the same size
     void *dimport = nullptr;              // staging for caller state arrays (3 x N int32)
-    void *dsortcnt = nullptr, *dsortblk = nullptr, *dactive = nullptr;
+    void *dactive = nullptr;
     // tile engine (the layout the train step runs on)
     void *dQd[2] = {nullptr, nullptr}, *drec[2] = {nullptr, nullptr}, *dovf[2] = {nullptr, nullptr};
     void *dtmeta = nullptr, *dtscratch = nullptr, *dtcls = nullptr;   // per-tile offsets / capacities / counters; fold entries of crowded tiles
-    bool tile_mode = false;               // true: records live in tile regions and the table in Qd[h_step & 1]
-    bool legacy_engine = false;
+    bool tile_mode = false;               // true: the records live in tile regions (train steps), false: in environment order
+    bool cls_dirty = true;                // the per-tile class bytes must be rebuilt from the cell words
     int64_t bucket_every = 32, since_bucket = 0;
-    int cur = 0;                          // which copy of the state is live
-    bool slots_identity = true;           // id[k] == k
-    int64_t sort_every = 8, since_sort = 0;
     void *dent = nullptr, *dctl = nullptr, *deps = nullptr;
     void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
-    void *ddense = nullptr;               // S float4: table in the caller's layout
-    void *dgather = nullptr, *dsend = nullptr;   // replica averaging: all-gather landing zone and send chunk
+    void *dgather = nullptr;              // replica averaging: all-gather landing zone
     void* dub[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; size_t ub_cap = 0;   // update_batch staging
     void* dact = nullptr;                 // actions staging for the host form of step_actions
-    size_t ent_cap = 0, eps_cap = 0, l2_window_bytes = 0;
+    size_t ent_cap = 0, eps_cap = 0;
     float* h_eps = nullptr; size_t h_eps_cap = 0; cudaEvent_t ev_eps = nullptr; bool eps_inflight = false;
     float eps_fixed_cached = -1.0f; bool eps_fixed_valid = false;
     // host mirror of schedule state
@@ -102,7 +98,7 @@ struct cudarl_ctx {
     float eps_used = 0.0f;
     double eps_running = 1.0;
     int64_t eval_calls = 0;
-    bool occ_valid = false, trace = false;
+    bool trace = false;
     // communicator
     ncclComm_t comm = nullptr; int rank = 0, nranks = 1;
     // timing
@@ -184,10 +180,8 @@ int build_cells(cudarl_ctx* c, std::vector<uint8_t>& cells, uint32_t& start_cell
     return 0;
 }
 
-void bind_state(cudarl_ctx* c) {
-    Params& p = c->p; const int a = c->cur, b = 1 - c->cur;
-    p.st = (int4*)c->dstate[a]; p.st2 = (int4*)c->dstate[b];
-}
+// the current table: the dense copy of the parity of the step counter
+void bind_q(cudarl_ctx* c) { c->p.Q = c->p.tp.Qd[c->h_step & 1]; }
 
 int upload_cells(cudarl_ctx* c) {
     const size_t S = c->p.S, pad = (S + 7) / 8 * 8;
@@ -195,26 +189,6 @@ int upload_cells(cudarl_ctx* c) {
     for (size_t s = 0; s < S; ++s) b[s] = c->cells[s] == 1 ? CW_OBST : (c->cells[s] == 2 ? CW_GOAL : 0);
     CK(cudaMemcpyAsync(c->dci, b.data(), pad * 2, cudaMemcpyHostToDevice, c->st));
     CK(cudaStreamSynchronize(c->st));
-    c->occ_valid = false;
-    return 0;
-}
-
-// Re-order the slots by cell (counting sort into the other copy of the state, then swap).
-int sort_slots(cudarl_ctx* c) {
-    if (c->p.N < 2048) return 0;                   // nothing to gain for a handful of environments
-    launch_sort_by_cell(c->p, c->st);                // scatter into the spare copy, rank back into the live one
-    CK(cudaGetLastError());
-    c->slots_identity = false; c->since_sort = 0;
-    return 0;
-}
-
-// Bring the state back to environment order (slot k = environment k), e.g. before the caller overwrites it.
-int normalize_slots(cudarl_ctx* c) {
-    if (c->slots_identity) return 0;
-    launch_normalize(c->p, c->st);
-    c->cur = 1 - c->cur; bind_state(c);
-    CK(cudaGetLastError());
-    c->slots_identity = true;
     return 0;
 }
 
@@ -234,51 +208,18 @@ int ensure_entry_capacity(cudarl_ctx* c, size_t cap) {
     return 0;
 }
 
-// The per-cell info bytes and the mailbox are the two structures every step hits with random
-// accesses and atomics; they share one allocation so that one L2 access-policy window can keep
-// both resident while the state arrays and Q rows stream through.
+// The per-cell class words, and the chain heads / work lists of update_batch.
 int alloc_hot(cudarl_ctx* c) {
     const size_t S = c->p.S, N = c->p.N ? c->p.N : 1;
     const size_t ci_bytes = (2 * S + 255) / 256 * 256;      // one 16-bit word per cell
-    // one slot per two environments: chains stay short, and every MiB taken from the L2 window is a MiB more for table rows
     size_t slots = pow2ceil(N) / 2; if (slots < (1u << 16)) slots = 1u << 16; if (slots > (1u << 24)) slots = 1u << 24;
-    unsigned lg = 0; while ((1ull << lg) < slots) ++lg;
     const size_t total = ci_bytes + slots * sizeof(unsigned);
     CK(cudaMalloc(&c->dci, total));
     CK(cudaMemsetAsync(c->dci, 0, total, c->st));
     c->p.cw = (unsigned short*)c->dci;
-    c->p.mailbox = (unsigned*)((char*)c->dci + ci_bytes); c->p.mb_slots = (unsigned)slots; (void)lg;
+    c->p.mailbox = (unsigned*)((char*)c->dci + ci_bytes); c->p.mb_slots = (unsigned)slots;
     CK(cudaMalloc(&c->dactive, 3 * slots * sizeof(unsigned)));
     c->p.active = (unsigned*)c->dactive; c->p.longq = (unsigned*)c->dactive + slots; c->p.longq2 = (unsigned*)c->dactive + 2 * slots;
-    // L2 persistence (per context, released with it): best effort, a refusal is not an error.
-    int dev = c->cfg.device, max_persist = 0, max_window = 0;
-    cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev);
-    cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev);
-    c->l2_window_bytes = 0;
-    if (max_persist > 0 && max_window > 0 && !getenv("CUDARL_NO_L2_WINDOW")) {
-        size_t want = total; if (want > (size_t)max_window) want = (size_t)max_window;
-        size_t carve = want; if (carve > (size_t)max_persist) carve = (size_t)max_persist;
-        if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, carve) == cudaSuccess) {
-            cudaStreamAttrValue av; std::memset(&av, 0, sizeof(av));
-            av.accessPolicyWindow.base_ptr = c->dci;
-            av.accessPolicyWindow.num_bytes = want;
-            av.accessPolicyWindow.hitRatio = (float)((double)carve / (double)want);
-            av.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
-            av.accessPolicyWindow.missProp = cudaAccessPropertyNormal;
-            if (cudaStreamSetAttribute(c->st, cudaStreamAttributeAccessPolicyWindow, &av) == cudaSuccess) c->l2_window_bytes = want;
-        }
-        cudaGetLastError();
-    }
-    return 0;
-}
-
-int ensure_occupancy(cudarl_ctx* c) {
-    if (c->occ_valid) return 0;
-    { int rs = sort_slots(c); if (rs) return rs; }
-    c->p.step = (unsigned long long)c->h_step;
-    launch_rebuild_occupancy(c->p, c->st);
-    CK(cudaGetLastError());
-    c->occ_valid = true;
     return 0;
 }
 
@@ -291,12 +232,6 @@ int ensure_step_buffers(cudarl_ctx* c) {
     CK(cudaMemsetAsync(c->dreward, 0, N * sizeof(float), c->st));
     CK(cudaMemsetAsync(c->ddone, 0, N, c->st));
     c->p.reward = (float*)c->dreward; c->p.done = (unsigned char*)c->ddone;
-    return 0;
-}
-
-int ensure_dense(cudarl_ctx* c) {
-    if (c->ddense) return 0;
-    CK(cudaMalloc(&c->ddense, (size_t)c->p.S * sizeof(float4)));
     return 0;
 }
 
@@ -339,23 +274,20 @@ int drain_kernel_events(cudarl_ctx* c) {
 
 
 // ---- tile engine: buffers, entering and leaving the tile layout ------------------------------------
-// Tile edge: the largest of 32 / 16 / 8 cells that still gives every SM several tiles and keeps the
-// average tile population within what a block sorts in shared memory.
+// Tile edge: the largest of 32 / 16 / 8 cells that still gives every SM more than one tile (measured on
+// B200: fewer, fuller tiles win as long as all SMs have work).
 int alloc_tiles(cudarl_ctx* c) {
     Params& p = c->p; TileP& tp = p.tp;
     const size_t S = p.S, N = p.N ? p.N : 1;
     unsigned tsh = 3;
     for (unsigned cand = 5; cand >= 3; --cand) {
         const size_t nt = (((size_t)p.W + (1u << cand) - 1) >> cand) * (((size_t)p.H + (1u << cand) - 1) >> cand);
-        if (nt >= 592 && N / nt <= 768) { tsh = cand; break; }
+        if (nt >= 222) { tsh = cand; break; }
     }
     if (const char* ev = getenv("CUDARL_TILE_SHIFT")) { int v = atoi(ev); if (v >= 3 && v <= 5) tsh = (unsigned)v; }
     tp.tshift = tsh; tp.T = 1u << tsh;
     tp.tiles_x = (unsigned)((p.W + (int)tp.T - 1) >> tsh); tp.tiles_y = (unsigned)((p.H + (int)tp.T - 1) >> tsh);
     tp.ntiles = tp.tiles_x * tp.tiles_y;
-    tp.ch = 512;
-    tp.ct = (N / ((size_t)tp.tiles_x * tp.tiles_y) <= 72) ? 96u : 256u;
-    if (const char* ev = getenv("CUDARL_TILE_CT")) { int v = atoi(ev); if (v == 96 || v == 256) tp.ct = (unsigned)v; }
     for (int k = 0; k < 2; ++k) {
         CK(cudaMalloc(&c->dQd[k], S * sizeof(float4)));
         CK(cudaMalloc(&c->drec[k], (N + N / 2 + 96 * (size_t)tp.ntiles + 64) * sizeof(int4)));
@@ -372,95 +304,79 @@ int alloc_tiles(cudarl_ctx* c) {
     tp.cls_stride = (unsigned)((((size_t)tp.T + 2) * (tp.T + 2) + 15) / 16 * 16);
     CK(cudaMalloc(&c->dtcls, nt * tp.cls_stride));
     tp.tcls = (unsigned char*)c->dtcls;
-    CK(cudaMalloc(&c->dtscratch, N * sizeof(uint2)));
+    CK(cudaMalloc(&c->dtscratch, (N > 65536 ? N : 65536) * sizeof(uint2)));
     tp.scratch = (uint2*)c->dtscratch;
     if (tile_engine_configure(p, c->cfg.device) != 0) { cudaGetLastError(); return fail(c, -5, "tile step: shared memory request refused"); }
     return 0;
 }
 
-// canonical layout (records in slot order, 32-byte table rows with a parity bit) -> tile layout
+// records in environment order -> tile regions (the table is the same dense array in both layouts)
 int enter_tiles(cudarl_ctx* c) {
     if (c->tile_mode) return 0;
     c->p.step = (unsigned long long)c->h_step;
-    launch_q_gather(c->p, c->p.tp.Qd[c->h_step & 1], c->st);
-    launch_tile_classes(c->p, c->st);
+    if (c->cls_dirty) { launch_tile_classes(c->p, c->st); c->cls_dirty = false; }
     launch_tile_bucket(c->p, c->st);
     CK(cudaGetLastError());
     c->tile_mode = true; c->since_bucket = 0;
     return 0;
 }
-// tile layout -> canonical layout, records back in environment order
+// tile regions -> records back in environment order
 int leave_tiles(cudarl_ctx* c) {
+    bind_q(c);
     if (!c->tile_mode) return 0;
     c->p.step = (unsigned long long)c->h_step;
     launch_tile_export(c->p, c->st);
-    launch_q_scatter(c->p, c->p.tp.Qd[c->h_step & 1], 1.0f, c->st);
     CK(cudaGetLastError());
-    c->tile_mode = false; c->slots_identity = true; c->occ_valid = false;
+    c->tile_mode = false;
     return 0;
 }
-// re-size the tile regions from the current populations (records only; the table stays where it is)
+// re-size the tile regions from the current populations
 int rebucket_tiles(cudarl_ctx* c) {
     c->p.step = (unsigned long long)c->h_step;
     launch_tile_export(c->p, c->st);
     launch_tile_bucket(c->p, c->st);
     CK(cudaGetLastError());
-    c->slots_identity = true; c->since_bucket = 0;
+    c->since_bucket = 0;
     return 0;
 }
 
 // Q <- (Q_0 + Q_1 + ... + Q_{R-1}) * (1/R), summed in rank order on every GPU.  The rows travel with an
-// NCCL all-gather in chunks (NVLink / NVSwitch); the reduction itself is our kernel, so the result is the
-// same bits on every rank and the same bits as the CPU oracle for any R (an all-reduce would leave the
-// summation order to the library).
+// NCCL all-gather in chunks (NVLink / NVSwitch), straight out of the dense table; the reduction itself is
+// our kernel, so the result is the same bits on every rank and the same bits as the CPU oracle for any R
+// (an all-reduce would leave the summation order to the library).
 int average_now(cudarl_ctx* c) {
     if (!c->comm || c->nranks <= 1) return 0;
     const size_t S = c->p.S, R = (size_t)c->nranks;
     const size_t chunk = S < (1u << 20) ? S : (1u << 20);            // cells per round: 16 MiB per rank
-    if (!c->dgather) {
-        CK(cudaMalloc(&c->dgather, R * chunk * sizeof(float4)));
-        CK(cudaMalloc(&c->dsend, chunk * sizeof(float4)));
-    }
-    if (c->tile_mode) {                       // the dense table is contiguous: rows go out as they lie
-        float4* table = c->p.tp.Qd[c->h_step & 1];
-        for (size_t c0 = 0; c0 < S; c0 += chunk) {
-            const size_t n = S - c0 < chunk ? S - c0 : chunk;
-            NK(g_nccl.AllGather(table + c0, c->dgather, n * 4, ncclFloat, c->comm, c->st));
-            launch_q_average_dense(c->p, table, (const float4*)c->dgather, (unsigned)R, (unsigned)c0, (unsigned)n, 1.0f / (float)R, c->st);
-        }
-        CK(cudaGetLastError());
-        return 0;
-    }
+    if (!c->dgather) CK(cudaMalloc(&c->dgather, R * chunk * sizeof(float4)));
+    float4* table = c->p.tp.Qd[c->h_step & 1];
     for (size_t c0 = 0; c0 < S; c0 += chunk) {
         const size_t n = S - c0 < chunk ? S - c0 : chunk;
-        launch_q_gather_range(c->p, (float4*)c->dsend, (unsigned)c0, (unsigned)n, c->st);
-        NK(g_nccl.AllGather(c->dsend, c->dgather, n * 4, ncclFloat, c->comm, c->st));
-        launch_q_average(c->p, (const float4*)c->dgather, (unsigned)R, (unsigned)c0, (unsigned)n, 1.0f / (float)R, c->st);
+        NK(g_nccl.AllGather(table + c0, c->dgather, n * 4, ncclFloat, c->comm, c->st));
+        launch_q_average_dense(c->p, table, (const float4*)c->dgather, (unsigned)R, (unsigned)c0, (unsigned)n, 1.0f / (float)R, c->st);
     }
     CK(cudaGetLastError());
     return 0;
 }
 
 int run_steps(cudarl_ctx* c, int64_t n) {
-    if (!c->legacy_engine) { int re = enter_tiles(c); if (re) return re; }
-    else { int ro = ensure_occupancy(c); if (ro) return ro; }
+    { int re = enter_tiles(c); if (re) return re; }
     for (int64_t k = 0; k < n; ++k) {
         cudaEvent_t a = nullptr, b = nullptr, d = nullptr;
         if (c->ktiming) {
             if (c->kev_used + 3 > c->kev.size()) { int rc = drain_kernel_events(c); if (rc) return rc; }
             a = c->kev[c->kev_used]; b = c->kev[c->kev_used + 1]; d = c->kev[c->kev_used + 2]; c->kev_used += 3;
         }
-        if (c->legacy_engine) { if (c->sort_every > 0 && c->since_sort >= c->sort_every) { int rs = sort_slots(c); if (rs) return rs; } }
-        else if (c->bucket_every > 0 && c->since_bucket >= c->bucket_every) { int rs = rebucket_tiles(c); if (rs) return rs; }
+        if (c->bucket_every > 0 && c->since_bucket >= c->bucket_every) { int rs = rebucket_tiles(c); if (rs) return rs; }
         c->p.step = (unsigned long long)c->h_step;
         c->p.eps_idx = c->eps_mode == 1 ? (unsigned)k : 0u;
         c->p.eps_from_ctl = c->eps_mode == 2 ? 1 : 0;
         if (c->eps_mode != 2 && c->h_eps) c->eps_used = c->h_eps[c->p.eps_idx];
-        if (c->legacy_engine) launch_train_step(c->p, c->trace, c->st, a, b, d);
-        else launch_tile_step(c->p, c->trace, c->st, a, b, d);
-        c->h_step += 1; c->since_sort += 1; c->since_bucket += 1;
+        launch_tile_step(c->p, c->trace, c->st, a, b, d);
+        c->h_step += 1; c->since_bucket += 1;
         if (c->cfg.sync_every > 0 && c->comm && (c->h_step % c->cfg.sync_every) == 0) { int rc = average_now(c); if (rc) return rc; }
     }
+    bind_q(c);
     CK(cudaGetLastError());
     return 0;
 }
@@ -468,8 +384,8 @@ int run_steps(cudarl_ctx* c, int64_t n) {
 void free_all(cudarl_ctx* c) {
     if (c->st) cudaStreamSynchronize(c->st);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
-    void* bufs[] = {c->dQ, c->dci, c->dstate[0], c->dstate[1], c->dimport, c->dsortcnt, c->dsortblk, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
-                    c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->ddense, c->dgather, c->dsend, c->dact,
+    void* bufs[] = {c->dci, c->dstate[0], c->dstate[1], c->dimport, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
+                    c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->dgather, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6],
                     c->dQd[0], c->dQd[1], c->drec[0], c->drec[1], c->dovf[0], c->dovf[1], c->dtmeta, c->dtscratch, c->dtcls};
     for (void* b : bufs) if (b) cudaFree(b);
@@ -521,7 +437,6 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
         p.W = f->width; p.H = f->height; p.S = (unsigned)(f->width * f->height); p.N = (unsigned)f->num_envs;
         p.env_offset = (unsigned)f->env_offset; p.k0 = (uint32_t)f->seed; p.k1 = (uint32_t)(f->seed >> 32);
         p.max_steps = f->max_steps; p.start_mode = f->start_mode; p.lr = f->lr; p.gamma = f->gamma; p.legacy_clamp = f->legacy_clamp;
-        p.nblocks_main = (p.N + BLOCK - 1) / BLOCK;
         uint32_t sc = 0, fb = 0;
         rc = build_cells(c, c->cells, sc, fb); if (rc) break;
         p.start_cell = sc; p.fallback_start = fb;
@@ -529,20 +444,16 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             CK(cudaStreamCreateWithFlags(&c->st, cudaStreamNonBlocking));
             CK(cudaEventCreateWithFlags(&c->ev_eps, cudaEventDisableTiming));
             CK(cudaEventCreate(&c->ev0)); CK(cudaEventCreate(&c->ev1));
-            const size_t S = p.S, N = p.N ? p.N : 1;
-            CK(cudaMalloc(&c->dQ, S * 2 * sizeof(float4)));
+            const size_t N = p.N ? p.N : 1;
             { int r0 = alloc_hot(c); if (r0) return r0; }
             for (int cp = 0; cp < 2; ++cp) { CK(cudaMalloc(&c->dstate[cp], N * 16)); CK(cudaMemsetAsync(c->dstate[cp], 0, N * 16, c->st)); }
-            p.sort_shift = 0; while (((S - 1) >> p.sort_shift) + 1 > (1u << 21) || (((S - 1) >> p.sort_shift) + 1 > 2 * N && ((S - 1) >> p.sort_shift) + 1 > (1u << 12))) ++p.sort_shift;
-            p.nkeys = (unsigned)(((S - 1) >> p.sort_shift) + 1);
-            CK(cudaMalloc(&c->dsortcnt, (((size_t)p.nkeys + 4095) / 4096 * 4096 + 4) * sizeof(unsigned)));   // padded to whole scan chunks
-            CK(cudaMalloc(&c->dsortblk, ((size_t)p.nkeys / 4096 + 2) * sizeof(unsigned)));
             CK(cudaMalloc(&c->dctl, sizeof(Ctl)));
             CK(cudaMemsetAsync(c->dctl, 0, sizeof(Ctl), c->st));
-            p.Q = (float4*)c->dQ; bind_state(c); p.sort_cnt = (unsigned*)c->dsortcnt; p.sort_blk = (unsigned*)c->dsortblk;
+            p.st = (int4*)c->dstate[0]; p.st2 = (int4*)c->dstate[1];
             p.ctl = (Ctl*)c->dctl;
             int r2 = ensure_entry_capacity(c, N); if (r2) return r2;
             r2 = alloc_tiles(c); if (r2) return r2;
+            bind_q(c);
             r2 = upload_cells(c); if (r2) return r2;
             launch_q_init(p, f->q_init_kind, f->q_init_scale, c->st);
             float e0 = (float)f->eps0; r2 = upload_eps(c, &e0, 1); if (r2) return r2;
@@ -553,11 +464,8 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             CK(cudaStreamSynchronize(c->st));
             return 0;
         };
-        c->sort_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 8);
-        if (const char* ev = getenv("CUDARL_SORT_EVERY")) c->sort_every = atoll(ev);
         c->bucket_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 32);
         if (const char* ev = getenv("CUDARL_BUCKET_EVERY")) c->bucket_every = atoll(ev);
-        if (const char* ev = getenv("CUDARL_ENGINE")) c->legacy_engine = std::strcmp(ev, "legacy") == 0;
         rc = body();
     } while (0);
     if (rc) { g_err = c->err; free_all(c); delete c; return rc; }
@@ -584,7 +492,6 @@ int cudarl_reset_all(cudarl_ctx* c) {
     c->p.step = (unsigned long long)c->h_step;
     launch_reset_all(c->p, c->st);
     CK(cudaGetLastError());
-    c->occ_valid = false;
     return 0;
 }
 
@@ -595,7 +502,6 @@ int cudarl_step_actions_device(cudarl_ctx* c, const int32_t* d_actions, float* d
     int rc = ensure_step_buffers(c); if (rc) return rc;
     launch_step_actions(c->p, d_actions, d_rewards, d_dones, c->st);
     CK(cudaGetLastError());
-    c->occ_valid = false;
     return 0;
 }
 
@@ -611,7 +517,6 @@ int cudarl_step_actions(cudarl_ctx* c, const int32_t* actions, float* rewards, u
     if (rewards) CK(cudaMemcpyAsync(rewards, c->dreward, N * sizeof(float), cudaMemcpyDeviceToHost, c->st));
     if (dones) CK(cudaMemcpyAsync(dones, c->ddone, N, cudaMemcpyDeviceToHost, c->st));
     CK(cudaStreamSynchronize(c->st));
-    c->occ_valid = false;
     return 0;
 }
 
@@ -767,7 +672,6 @@ int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const in
     if (y) for (size_t i = 0; i < N; ++i) if (y[i] < 0 || y[i] >= c->p.H) return fail(c, -3, "Invalid state");
     CK(cudaSetDevice(c->cfg.device));
     { int rl = leave_tiles(c); if (rl) return rl; }
-    { int rn = normalize_slots(c); if (rn) return rn; }
     if (!c->dimport) CK(cudaMalloc(&c->dimport, (N ? N : 1) * 12));
     int* dx = (int*)c->dimport; int* dy = dx + N; int* dt = dy + N;
     if (x) CK(cudaMemcpyAsync(dx, x, N * 4, cudaMemcpyHostToDevice, c->st));
@@ -776,7 +680,6 @@ int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const in
     launch_import_state(c->p, x ? dx : nullptr, y ? dy : nullptr, t ? dt : nullptr, c->st);
     CK(cudaGetLastError());
     CK(cudaStreamSynchronize(c->st));
-    c->occ_valid = false;
     return 0;
 }
 
@@ -784,10 +687,7 @@ int cudarl_get_q(cudarl_ctx* c, float* q) {
     if (!c || !q) return fail(c, -1, "null argument");
     CK(cudaSetDevice(c->cfg.device));
     { int rl = leave_tiles(c); if (rl) return rl; }
-    int rc = ensure_dense(c); if (rc) return rc;
-    launch_q_gather(c->p, (float4*)c->ddense, c->st);
-    CK(cudaGetLastError());
-    CK(cudaMemcpyAsync(q, c->ddense, (size_t)c->p.S * sizeof(float4), cudaMemcpyDeviceToHost, c->st));
+    CK(cudaMemcpyAsync(q, c->p.Q, (size_t)c->p.S * sizeof(float4), cudaMemcpyDeviceToHost, c->st));   // the table already is in the caller's layout
     CK(cudaStreamSynchronize(c->st));
     return 0;
 }
@@ -795,10 +695,7 @@ int cudarl_set_q(cudarl_ctx* c, const float* q) {
     if (!c || !q) return fail(c, -1, "null argument");
     CK(cudaSetDevice(c->cfg.device));
     { int rl = leave_tiles(c); if (rl) return rl; }
-    int rc = ensure_dense(c); if (rc) return rc;
-    CK(cudaMemcpyAsync(c->ddense, q, (size_t)c->p.S * sizeof(float4), cudaMemcpyHostToDevice, c->st));
-    launch_q_scatter(c->p, (const float4*)c->ddense, 1.0f, c->st);
-    CK(cudaGetLastError());
+    CK(cudaMemcpyAsync(c->p.Q, q, (size_t)c->p.S * sizeof(float4), cudaMemcpyHostToDevice, c->st));
     CK(cudaStreamSynchronize(c->st));
     return 0;
 }
@@ -819,7 +716,7 @@ static int set_cell(cudarl_ctx* c, int32_t x, int32_t y, unsigned cls, bool sing
         for (auto& v : c->cells) if (v == 2) v = 0;
         launch_cell_set(c->p, 0, 0, 1, c->st);
     }
-    c->cells[cell] = (uint8_t)cls;
+    c->cells[cell] = (uint8_t)cls; c->cls_dirty = true;
     launch_cell_set(c->p, cell, cls == 1 ? CW_OBST : (cls == 2 ? CW_GOAL : 0u), 0, c->st);
     CK(cudaGetLastError());
     uint32_t fb = 0xFFFFFFFFu;

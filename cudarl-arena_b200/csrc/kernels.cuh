@@ -6,16 +6,10 @@
 
 namespace cudarl {
 
-// ---- per-cell word (16 bits per grid cell, array padded to 16 bytes) ---------------------------
-// One 2-byte load of a cell answers "obstacle?", "goal?", "which half of the Q row is current?" and
-// "how many environments stand here in this step?" in a single L2 access.
+// ---- per-cell word (16 bits per grid cell, array padded to 16 bytes): the cell's class ------------
 enum : unsigned {
-    CW_OBST = 1u,      // static: cell blocks movement            (src/kernels.cu:29-36 of the reference)
-    CW_GOAL = 2u,      // static: cell ends the episode, reward 1  (src/environment.cu:43-46)
-    CW_PAR  = 4u,      // which 16-byte half of the 32-byte Q row holds Q_t for this cell
-    CW_CNT_SHIFT0 = 3u,   // bits 3-8 : occupant count of even steps, saturating at 63
-    CW_CNT_SHIFT1 = 9u,   // bits 9-14: occupant count of odd steps; while one plane is read, the other is filled
-    CW_CNT_MAX = 63u,
+    CW_OBST = 1u,      // cell blocks movement                     (src/kernels.cu:29-36 of the reference)
+    CW_GOAL = 2u,      // cell ends the episode, reward 1          (src/environment.cu:43-46)
 };
 
 // A chain link names a run of consecutive collision entries: low 26 bits = position of the first entry + 1
@@ -52,8 +46,6 @@ enum : unsigned { ERR_SCRATCH_OVERFLOW = 1u, ERR_BAD_STATE = 2u, ERR_BAD_TRANSIT
 struct TileP {
     unsigned tshift, T;        // tile edge = 1 << tshift cells
     unsigned tiles_x, tiles_y, ntiles;
-    unsigned ch;               // entries a block can sort in shared memory; fuller tiles use `scratch`
-    unsigned ct;               // consumer threads per block of the step kernel: 256, or 96 for small tiles
     unsigned grid;             // blocks of the persistent step kernel (SMs x resident blocks per SM)
     float4* Qd[2];             // dense table, one float4 (4 action values) per cell; [step & 1] is current
     int4* rec[2];              // records {x, y, t, id}; [step & 1] is current
@@ -65,7 +57,7 @@ struct TileP {
     unsigned* tctl;            // [0..2] overflow counts (read step%3, append (step+1)%3, clear (step+2)%3); [3..4] scratch cursors by parity
     unsigned char* tcls;       // ntiles x cls_stride: class bytes of each tile with its halo, row-major (T+2)^2, padded to 16
     unsigned cls_stride;
-    uint2* scratch;            // N fold entries {id << 2 | action, td target bits} for tiles beyond `ch`
+    uint2* scratch;            // N x 8 bytes: 32-bit (cell, action) counters of tiles with more than 65,535 records
 };
 
 // ---- everything a kernel needs, passed by value ------------------------------------------------
@@ -81,17 +73,16 @@ struct Params {
     unsigned fallback_start;
     float lr, gamma;
     int legacy_clamp;
-    float4* Q;             // 2*S float4: row s = {half0, half1}, 32-byte aligned
+    float4* Q;             // the current table: S float4, row s = the 4 action values of cell s (= tp.Qd[step & 1])
     unsigned short* cw;    // S cell words (padded to 16 bytes)
-    // environment state in SLOT order: one int4 {x, y, t, id} per slot (all int32, one coalesced 16-byte
-    // vector per thread).  Slots are re-ordered by cell every few steps so that neighbouring threads touch
-    // neighbouring rows; the record moves as one vector.
+    // environment state outside train steps: one int4 {x, y, t, id} per environment (all int32, one
+    // coalesced 16-byte vector per thread), record k = environment k
     int4* st;
-    int4* st2;             // the other half of the double buffer (sort target / export scratch)
+    int4* st2;             // scratch of the same size (export of x[N] | y[N] | t[N])
     float* reward; unsigned char* done;        // per ENVIRONMENT (caller-driven stepping only)
     uint4* ent;            // collision entries
     unsigned ent_cap;      // slots in ent
-    unsigned* mailbox;     // chain heads (0 = empty), power-of-two size
+    unsigned* mailbox;     // update_batch: chain heads (0 = empty), power-of-two size
     unsigned mb_slots;     // mailbox slots (power of two, multiple of BLOCK)
     unsigned* active;      // list of the mailbox slots that hold a chain in this step (mb_slots entries)
     unsigned* longq;       // heads of the chains left to the warp-per-chain kernel (mb_slots entries)
@@ -100,11 +91,6 @@ struct Params {
     const float* eps_tab;
     int* tr_a; float* tr_r; unsigned char* tr_d;   // optional trace of the last step, per ENVIRONMENT
     unsigned long long* sc_key; float* sc_val; unsigned sc_cap;   // long-chain scratch (global)
-    unsigned* sort_cnt;    // S+1 counters for the counting sort by cell
-    unsigned* sort_blk;    // per-4096-cell partial sums
-    unsigned nkeys;        // sort keys = ((S - 1) >> sort_shift) + 1
-    unsigned sort_shift;
-    unsigned nblocks_main;
     // per-launch values set by the host
     unsigned long long step;   // global batched step index g (keys the policy stream, selects the counter plane)
     unsigned eps_idx;          // index of this step's epsilon in eps_tab
@@ -115,22 +101,14 @@ struct Params {
 constexpr int BLOCK = 256;
 
 // launch wrappers (kernels.cu); all asynchronous on `st`
-void launch_rebuild_occupancy(const Params& p, cudaStream_t st);
-void launch_sort_by_cell(const Params& p, cudaStream_t st);       // writes st2; caller swaps
 void launch_identity_ids(const Params& p, cudaStream_t st);
 void launch_export_state(const Params& p, cudaStream_t st);       // st2 viewed as x[N]|y[N]|t[N] in environment order
-void launch_normalize(const Params& p, cudaStream_t st);          // st2[id] = st[slot]; caller swaps
 void launch_import_state(const Params& p, const int* x, const int* y, const int* t, cudaStream_t st);
 void launch_reset_all(const Params& p, cudaStream_t st);
-void launch_train_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c);
 void launch_step_actions(const Params& p, const int* d_actions, float* d_rewards, unsigned char* d_dones, cudaStream_t st);
 void launch_eval(const Params& p, int max_steps, unsigned long long nonce, cudaStream_t st);
 void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* sy, const int* a, const float* r,
                          const int* nx, const int* ny, const unsigned char* dn, cudaStream_t st);
-void launch_q_gather(const Params& p, float4* dense, cudaStream_t st);
-void launch_q_scatter(const Params& p, const float4* dense, float scale, cudaStream_t st);
-void launch_q_gather_range(const Params& p, float4* dense, unsigned cell0, unsigned n, cudaStream_t st);
-void launch_q_average(const Params& p, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale, cudaStream_t st);
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st);
 // tile engine (tile_engine.cu)
 size_t tile_step_smem(const Params& p);

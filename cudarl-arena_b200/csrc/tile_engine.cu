@@ -1,26 +1,24 @@
-// tile_engine.cu -- the fused train step as a streaming pass over the grid, one thread block per tile.
+// tile_engine.cu -- the fused train step as a streaming pass over the grid, one tile at a time.
 //
 // With a quarter as many environments as cells, nearly every 128-byte line of the table is touched in
 // every step, so the step is organised around the TABLE, not around the environments:
 //
 //   * the grid is cut into T x T tiles; the environments are kept bucketed by tile (records {x,y,t,id});
-//   * one block loads its tile of Q_t plus a one-cell halo into shared memory with coalesced row loads
-//     (the halo serves the max over Q_t[s'] of moves that leave the tile), and the tile's cell classes;
+//   * a tile of Q_t plus a one-cell halo is brought into shared memory by bulk asynchronous copies, one
+//     per table row (the halo serves the max over Q_t[s'] of moves that leave the tile), together with the
+//     tile's cell classes and its records;
 //   * every environment of the tile is stepped against shared memory: epsilon-greedy from the Philox
-//     stream keyed by (seed, global env, step), move with obstacle / goal lookup, TD target from Q_t;
-//   * a counting sort by cell (shared-memory counters) groups the (id, action, target) entries of one
-//     cell; the cell's thread orders them by environment id and applies them one after the other, each
-//     seeing the value the previous one left -- no float atomics, the same bits as the sequential
-//     oracle however the entries arrived; cells with many occupants are sorted by the whole block;
-//   * the tile of Q_{t+1} is written to the OTHER dense table with coalesced stores (two dense tables
-//     alternate, so a block never sees a neighbour's writes of the same step);
+//     stream keyed by (seed, global env, step), move with obstacle / goal lookup, auto-reset;
+//   * the TD updates of a cell are applied from a histogram of (cell, action) counts: inside one step the
+//     target of an update depends on (cell, action) only, so n environments on one (cell, action) mean the
+//     same map applied n times -- the same bits as the oracle's sequential order, without sorting anything
+//     and without float atomics;
+//   * the tile of Q_{t+1} goes out to the OTHER dense table, one bulk copy per row (two dense tables
+//     alternate, so no block ever sees a neighbour's writes of the same step);
 //   * an environment that stays in the tile is appended to the front part of the tile's region of the
 //     other record array; one that leaves (a walk across the edge, a restart anywhere) is appended to
 //     the back part of its new tile's region with one atomic; a full back part spills to a global list
 //     that every block filters.  Regions are re-sized from the actual populations every few steps.
-//
-// A tile with more environments than fit the shared sort buffer runs the same code on a slice of a
-// global scratch array, so any distribution (all environments on one cell included) is handled.
 //
 // Reference semantics (paths relative to the CudaRL-Arena project root):
 //   step        src/environment.cu:17-48, obstacle test src/kernels.cu:29-44, goal src/kernels.cu:56-59
@@ -35,8 +33,7 @@ namespace cg = cooperative_groups;
 
 namespace cudarl {
 
-constexpr unsigned SMALL_MAX = 24;   // occupants of one cell that the cell's own thread orders by insertion
-constexpr unsigned BIG_LIST = 32;    // crowded cells a block lists; beyond that it scans all its cells
+constexpr unsigned CROWDED_CELL = 24;   // a cell with more environments than this counts as "crowded" in the run statistics
 
 __device__ __forceinline__ unsigned tile_of(const TileP& tp, int x, int y) {
     return ((unsigned)y >> tp.tshift) * tp.tiles_x + ((unsigned)x >> tp.tshift);
@@ -60,32 +57,6 @@ __device__ __forceinline__ unsigned block_scan_excl(unsigned v, unsigned* s_warp
     *total = s_warp[32];
     __syncthreads();
     return r;
-}
-
-__device__ __forceinline__ void cswap_u2(uint2& a, uint2& b) { if (a.x > b.x) { const uint2 t = a; a = b; b = t; } }
-
-// Block-wide ascending sort of a[0..n) by .x, any n: the bitonic network in its all-ascending form (the first
-// comparator of every merge mirrors the index), so the missing tail behaves like +infinity and is never touched.
-__device__ void block_sort_u2(uint2* a, unsigned n) {
-    for (unsigned k = 2; (k >> 1) < n; k <<= 1) {
-        for (unsigned i = threadIdx.x; i < n; i += blockDim.x) {
-            const unsigned l = i ^ (k - 1u);
-            if (l > i && l < n) { uint2 u = a[i], v = a[l]; if (u.x > v.x) { a[i] = v; a[l] = u; } }
-        }
-        __syncthreads();
-        for (unsigned j = k >> 2; j > 0; j >>= 1) {
-            for (unsigned i = threadIdx.x; i < n; i += blockDim.x) {
-                const unsigned l = i ^ j;
-                if (l > i && l < n) { uint2 u = a[i], v = a[l]; if (u.x > v.x) { a[i] = v; a[l] = u; } }
-            }
-            __syncthreads();
-        }
-    }
-}
-
-// Apply the entries e[0..n) (already in ascending environment id) to `row`.
-__device__ __forceinline__ void fold_entries(float4& row, const uint2* e, unsigned n, float lr) {
-    for (unsigned k = 0; k < n; ++k) { const uint2 v = e[k]; fold(row, (int)(v.x & 3u), lr, __uint_as_float(v.y)); }
 }
 
 // ---- asynchronous bulk copies (global <-> shared, no registers, no per-element instructions) -------------
@@ -168,8 +139,7 @@ __device__ __forceinline__ bool mbar_wait_long(unsigned long long* bar, unsigned
 // A tile with more than 65,535 records counts in 32-bit counters in global scratch instead.
 // full[stage] : the producer's copies have landed (transaction barrier);  done[stage] : every consumer thread
 // has finished the tile in that stage.
-// CT consumer threads (+ 32 of the producer warp) per block: 256 for tiles that hold a few hundred environments, 96 for
-// small tiles (fewer threads per block = more blocks, i.e. more tiles in flight, per SM).
+constexpr unsigned CONSUMERS = 256;      // consumer threads per block (+ 32 of the producer warp)
 // Records staged in shared memory (front part, back part of the region); the rest is read from global memory.
 __host__ __device__ constexpr unsigned rc_front(unsigned ct) { return ct + ct / 4u + 32u; }
 __host__ __device__ constexpr unsigned rc_back(unsigned ct) { return ct / 4u + 32u; }
@@ -275,7 +245,7 @@ __device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c,
 }
 
 template <bool TRACE, unsigned TSH, unsigned CT>
-__global__ void __launch_bounds__(CT + 32u, CT == 256u ? 3 : 6) k_tile_step(Params p) {
+__global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
     constexpr unsigned T = 1u << TSH, HS = T + 2u, T2 = T * T, HS2 = HS * HS;
     constexpr unsigned RC = rc_front(CT), RCB = rc_back(CT);
     constexpr unsigned CPT = (T2 + CT - 1u) / CT;              // cells per consumer thread when every cell is occupied
@@ -460,7 +430,7 @@ __global__ void __launch_bounds__(CT + 32u, CT == 256u ? 3 : 6) k_tile_step(Para
             }
             if (!tot) continue;
             if (tot > 1u) conf += tot;
-            if (tot > SMALL_MAX) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, tot); }
+            if (tot > CROWDED_CELL) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, tot); }
             nrow[q] = updated_row<TSH>(p, c, ic, w, crowded ? n32 : nullptr);
             nh[q] = ((ic >> TSH) + 1u) * HS + (ic & (T - 1u)) + 1u;
         }
@@ -587,33 +557,27 @@ static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 static size_t work_bytes(size_t T2) { return (T2 * 8 + T2 * 2 + (T2 + 31) / 32 * 4 + 15) / 16 * 16; }
 size_t tile_step_smem(const Params& p) {
     const size_t T = p.tp.T, HS = T + 2;
-    const size_t stage = HS * HS * 16 + (size_t)rc_front(p.tp.ct) * 16 + (size_t)rc_back(p.tp.ct) * 16 + p.tp.cls_stride;
+    const size_t stage = HS * HS * 16 + (size_t)rc_front(CONSUMERS) * 16 + (size_t)rc_back(CONSUMERS) * 16 + p.tp.cls_stride;
     return 2 * stage + work_bytes(T * T);
 }
-template <unsigned TSH, unsigned CT>
+template <unsigned TSH>
 static cudaError_t configure_one(int bytes, int* per_sm) {
-    cudaError_t e = cudaFuncSetAttribute(k_tile_step<false, TSH, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_tile_step<true, TSH, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH, CT>, (int)(CT + 32u), (size_t)bytes);
+    cudaError_t e = cudaFuncSetAttribute(k_tile_step<false, TSH, CONSUMERS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_tile_step<true, TSH, CONSUMERS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH, CONSUMERS>, (int)(CONSUMERS + 32u), (size_t)bytes);
     return e;
-}
-template <unsigned CT>
-static cudaError_t configure_ct(unsigned tshift, int bytes, int* per_sm) {
-    switch (tshift) {
-        case 3: return configure_one<3, CT>(bytes, per_sm);
-        case 4: return configure_one<4, CT>(bytes, per_sm);
-        case 5: return configure_one<5, CT>(bytes, per_sm);
-        default: return cudaErrorInvalidValue;
-    }
 }
 int tile_engine_configure(Params& p, int device) {
     const int bytes = (int)tile_step_smem(p);
     int sms = 0, per_sm = 0;
     cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     if (e != cudaSuccess) return (int)e;
-    if (p.tp.ct == 96u) e = configure_ct<96>(p.tp.tshift, bytes, &per_sm);
-    else if (p.tp.ct == 256u) e = configure_ct<256>(p.tp.tshift, bytes, &per_sm);
-    else return (int)cudaErrorInvalidValue;
+    switch (p.tp.tshift) {
+        case 3: e = configure_one<3>(bytes, &per_sm); break;
+        case 4: e = configure_one<4>(bytes, &per_sm); break;
+        case 5: e = configure_one<5>(bytes, &per_sm); break;
+        default: return (int)cudaErrorInvalidValue;
+    }
     if (e != cudaSuccess) return (int)e;
     if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
     p.tp.grid = (unsigned)(sms * per_sm);
@@ -631,25 +595,20 @@ void launch_tile_export(const Params& p, cudaStream_t st) {
     k_te_export_ovf<<<64, BLOCK, 0, st>>>(p);
 }
 static unsigned tile_step_grid(const Params& p) { return p.tp.ntiles < p.tp.grid ? p.tp.ntiles : p.tp.grid; }
-template <unsigned TSH, unsigned CT>
+template <unsigned TSH>
 static void launch_step_one(const Params& p, bool trace, unsigned grid, size_t smem, cudaStream_t st) {
-    if (trace) k_tile_step<true, TSH, CT><<<grid, CT + 32u, smem, st>>>(p);
-    else       k_tile_step<false, TSH, CT><<<grid, CT + 32u, smem, st>>>(p);
-}
-template <unsigned CT>
-static void launch_step_ct(const Params& p, bool trace, unsigned grid, size_t smem, cudaStream_t st) {
-    switch (p.tp.tshift) {
-        case 3: launch_step_one<3, CT>(p, trace, grid, smem, st); break;
-        case 4: launch_step_one<4, CT>(p, trace, grid, smem, st); break;
-        default: launch_step_one<5, CT>(p, trace, grid, smem, st); break;
-    }
+    if (trace) k_tile_step<true, TSH, CONSUMERS><<<grid, CONSUMERS + 32u, smem, st>>>(p);
+    else       k_tile_step<false, TSH, CONSUMERS><<<grid, CONSUMERS + 32u, smem, st>>>(p);
 }
 void launch_tile_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c) {
     const size_t smem = tile_step_smem(p);
     const unsigned grid = tile_step_grid(p);
     if (ev_a) cudaEventRecord(ev_a, st);
-    if (p.tp.ct == 96u) launch_step_ct<96>(p, trace, grid, smem, st);
-    else                launch_step_ct<256>(p, trace, grid, smem, st);
+    switch (p.tp.tshift) {
+        case 3: launch_step_one<3>(p, trace, grid, smem, st); break;
+        case 4: launch_step_one<4>(p, trace, grid, smem, st); break;
+        default: launch_step_one<5>(p, trace, grid, smem, st); break;
+    }
     if (ev_b) cudaEventRecord(ev_b, st);
     if (p.eps_from_ctl) k_tile_eps_episode<<<1, 1, 0, st>>>(p);
     if (ev_c) cudaEventRecord(ev_c, st);
