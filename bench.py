@@ -12,8 +12,9 @@ The line printed by rank 0 carries
   value      whole-job env-steps/s with everything resident in HBM (device events, max over ranks),
   e2e        the same through the host-facing call: every window uploads its epsilon schedule from host
              memory and reads the run statistics back,
-  roofline   algorithmic bytes (60 B per env-step) x envs per launch / mean duration of the main kernel,
-             against the measured HBM copy bandwidth of MEASURED_PEAKS.json,
+  roofline   algorithmic bytes (60 B per env-step) x envs per launch / mean duration of the step kernel
+             (k_tile_step, CUDA events around every launch), against the measured HBM copy bandwidth of
+             MEASURED_PEAKS.json,
   cpu_baseline  the CPU oracle (a C++ port of the same semantics) timed on this box's cores.
 
 `--impl reference` times that CPU port with all host threads instead (the reference project itself
@@ -32,6 +33,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 PKG_DIR = os.path.join(ROOT, "cudarl-arena_b200")
 ALGO_BYTES_TRAIN = 60      # 12 state in + 12 state out + 16 Q[s] row + 16 Q[s'] row + 4 Q[s,a] write
 FALLBACK_HBM_GBS = 6650.0
+TRAFFIC_C5 = 655.5e6      # dram__bytes_read.sum + dram__bytes_write.sum of one k_tile_step launch on C5 (profiles/k_tile_step_C5.md)
 
 
 def load_pkg():
@@ -204,7 +206,7 @@ def main():
     cfg.env_offset = rank * n_local
     window = args.window or (cfg.sync_every if cfg.sync_every > 0 else 256)
     env = pkg.VecGridWorld(cfg)
-    launches_per_step = 4      # k_train_main, k_fix, k_fix_long, k_fix_long2 (+ 6 re-ordering kernels every 8th step)
+    launches_per_step = 1      # k_tile_step (+ 5 kernels that re-size the tile regions every 128th step)
 
     if args.profile_steps:                      # small fixed run for profilers: no timing, no JSON
         env.train_steps(args.profile_steps)
@@ -216,7 +218,7 @@ def main():
         ids = [pkg.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         env.comm_init(ids[0], rank, world)
-        launches_per_step_window_extra = 32     # gather + average kernels around each all-gather round (16 rounds at C5)
+        launches_per_step_window_extra = (cfg.width * cfg.height + (1 << 20) - 1) >> 20     # one averaging kernel per all-gather round of 2^20 cells
     else:
         launches_per_step_window_extra = 0
 
@@ -276,17 +278,17 @@ def main():
         "metric": "env-steps/s (step+eps-greedy+TD update)", "value": value, "unit": "env-steps/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.config, cfg), "window": window, "l2": "inputs_exceed_l2" if cfg.width * cfg.height * 32 > 126e6 else "l2_resident",
+        "config": {"workload": workload_name(args.config, cfg), "window": window, "l2": "inputs_exceed_l2" if cfg.width * cfg.height * 32 > 126e6 else "l2_resident",   # two dense tables of 16 B per cell
                    "parallelism": "env-sharded x%d, Q replica per GPU, NCCL average every %d steps" % (world, cfg.sync_every)},
         "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": int(window * 4), "d2h_bytes_per_step": 128},
-        "gpu_launches": int(args.steps * (window * launches_per_step + (window // 8) * 6 + launches_per_step_window_extra)),
+        "gpu_launches": int(args.steps * (window * launches_per_step + (window // 128) * 5 + launches_per_step_window_extra)),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one k_train_main launch on this workload, from the ncu
-                     # capture summarised in profiles/k_train_main_C5.md (not measured by this run)
-                     "traffic": 574.1e6 if (args.config == "C5" and not args.envs) else None,
-                     "peak_kind": peak_kind, "kernel": "k_train_main", "algorithmic_bytes_per_env_step": ALGO_BYTES_TRAIN,
-                     "main_kernel_us": main_avg_s * 1e6, "fix_kernel_us": fix_avg_s * 1e6,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one k_tile_step launch on this workload, from the ncu
+                     # capture summarised in profiles/k_tile_step_C5.md (not measured by this run)
+                     "traffic": TRAFFIC_C5 if (args.config == "C5" and not args.envs) else None,
+                     "peak_kind": peak_kind, "kernel": "k_tile_step", "algorithmic_bytes_per_env_step": ALGO_BYTES_TRAIN,
+                     "main_kernel_us": main_avg_s * 1e6, "other_kernels_us": fix_avg_s * 1e6,
                      "whole_step_frac": ALGO_BYTES_TRAIN * n_local / (ms * 1e-3 / (args.steps * window)) / 1e9 / peak},
         "cpu_baseline": cpu,
         "run_stats": {"steps": stats.steps, "goals": stats.goals, "timeouts": stats.timeouts,

@@ -83,7 +83,7 @@ struct cudarl_ctx {
     void *dtmeta = nullptr, *dtscratch = nullptr, *dtcls = nullptr;   // per-tile offsets / capacities / counters; fold entries of crowded tiles
     bool tile_mode = false;               // true: the records live in tile regions (train steps), false: in environment order
     bool cls_dirty = true;                // the per-tile class bytes must be rebuilt from the cell words
-    int64_t bucket_every = 32, since_bucket = 0;
+    int64_t bucket_every = 128, since_bucket = 0;
     void *dent = nullptr, *dctl = nullptr, *deps = nullptr;
     void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
     void *dgather = nullptr;              // replica averaging: all-gather landing zone
@@ -464,7 +464,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             CK(cudaStreamSynchronize(c->st));
             return 0;
         };
-        c->bucket_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 32);
+        c->bucket_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 128);
         if (const char* ev = getenv("CUDARL_BUCKET_EVERY")) c->bucket_every = atoll(ev);
         rc = body();
     } while (0);

@@ -73,7 +73,7 @@ typedef struct cudarl_config {
     float    q_init_scale;
     int32_t  legacy_clamp;  /* 1: max_next = max(0, max_a' Q) as in src/kernels.cu:102-110 */
     int32_t  sync_every;    /* average the replicas every this many train steps; 0 = never */
-    int32_t  reserved[4];   /* reserved[0]: re-order the slots by cell every this many train steps (0 = default 8, <0 = never; the environment variable CUDARL_SORT_EVERY overrides it) */
+    int32_t  reserved[4];   /* reserved[0]: re-size the per-tile record regions every this many train steps (0 = default 128, <0 = only when training starts; results never depend on it) */
 } cudarl_config;
 
 typedef struct cudarl_stats {
@@ -83,8 +83,8 @@ typedef struct cudarl_stats {
     int64_t goals;       /* episodes that ended on a goal cell */
     int64_t timeouts;    /* episodes that ended on the step cap */
     int64_t conflicts;   /* environment-steps that shared their cell with another environment */
-    int64_t long_chains; /* collision chains that took the cooperative path */
-    int64_t chained;     /* environment-steps whose update went through the entry/chain path */
+    int64_t long_chains; /* (cell, step) pairs with more than 24 environments on the cell */
+    int64_t chained;     /* environment-steps spent on such crowded cells */
     double  reward_sum;  /* goals * 1.0 - 0.01 * (env_steps - goals), derived from the counters */
     float   epsilon;     /* epsilon used by the most recent train step */
     int32_t device_error;/* nonzero if a kernel recorded an internal limit or bounds violation */

@@ -159,12 +159,12 @@ def test_lockstep_c3_uniform_q_linear_eps(pkg, orc):
 
 
 def test_lockstep_dense_collisions(pkg, orc):
-    """Tiny grids packed with environments: every chain is long, shared-memory and global-scratch sort paths."""
+    """Tiny grids packed with environments: hundreds to thousands of updates of one (cell, action) per step."""
     for w, h, n, steps in [(3, 3, 512, 40), (5, 5, 4096, 25), (2, 2, 6000, 12), (2, 1, 300, 5)]:
         cfg = pkg.make_config(w, h, n, start_mode=pkg.START_RANDOM, eps_kind=pkg.EPS_FIXED, eps0=0.3, max_steps=7, lr=0.25)
         gpu, cpu = pair(pkg, orc, cfg)
         s = lockstep(gpu, cpu, steps, what="dense %dx%d" % (w, h))
-        assert s.long_chains > 0 or n < 512
+        assert s.long_chains > 0 or n < 512          # cells with more than 24 occupants are counted
 
 
 def test_lockstep_one_tile_beyond_16_bit_counts(pkg, orc):
@@ -203,7 +203,7 @@ def test_caller_epsilon_array(pkg, orc):
 
 
 def test_state_roundtrip_and_external_steps_then_training(pkg, orc):
-    """Caller-driven steps and set_state invalidate the occupancy bits; training must rebuild them."""
+    """Caller-driven steps and set_state happen in environment order; training must re-bucket the records."""
     cfg = pkg.preset("C2", num_envs=2048)
     gpu, cpu = pair(pkg, orc, cfg)
     rng = np.random.RandomState(5)
@@ -312,9 +312,9 @@ def test_full_size_c5_lockstep_and_properties(pkg, orc):
     assert np.isfinite(q).all() and q.max() <= 1.0 and q.min() >= -1.0
 
 
-def test_slot_reordering_never_changes_results(pkg, orc):
-    """The slots are re-ordered by cell every few steps purely for locality; any period (and none) must give the
-    same bits, and the state must come back in environment order."""
+def test_region_resizing_never_changes_results(pkg, orc):
+    """The per-tile record regions are re-sized from the populations every few steps; any period (and none) must
+    give the same bits, and the state must come back in environment order."""
     base = pkg.preset("C3", num_envs=20000)
     base.width = base.height = 96
     ref = orc.Oracle(base, threads=4)
