@@ -205,8 +205,9 @@ int cudarl_average_replicas(cudarl_ctx* ctx);
 /* Timing helpers for benchmarks: record events on the context's stream. */
 int cudarl_timer_start(cudarl_ctx* ctx);
 int cudarl_timer_stop_ms(cudarl_ctx* ctx, float* ms); /* synchronises */
-/* Milliseconds spent in the step kernels proper (main kernel) between start and stop are
- * collected when enabled; used for the roofline figure. */
+/* When enabled, every train step is bracketed by events: main_ms = time in the step kernel (k_tile_step),
+ * fix_ms = time in whatever follows it inside the step (the per-episode epsilon kernel, else nothing),
+ * launches = steps measured.  Used for the roofline figure. */
 int cudarl_kernel_timing(cudarl_ctx* ctx, int on);
 int cudarl_kernel_time_ms(cudarl_ctx* ctx, float* main_ms, float* fix_ms, int64_t* launches);
 
