@@ -99,19 +99,6 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     for (unsigned it = 0; it < WAIT_LIMIT; ++it) if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-// The same for a thread that expects to wait long (the producer, for the consumers to finish a tile): every
-// poll may suspend the thread for a few microseconds, so the wait does not take issue slots from the warps that work.
-__device__ __forceinline__ bool mbar_wait_long(unsigned long long* bar, unsigned parity) {
-    for (unsigned it = 0; it < (1u << 20); ++it) {
-        unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(4000u) : "memory");
-        if (ok) return true;
-        __nanosleep(200);
-    }
-    return false;
-}
-
 // ------------------------------------------------------------------------------------------------
 // Why no ordering is needed.  The oracle applies the updates of one (cell, action) one after the other in
 // ascending environment id, each as  q <- fma(lr, target - q, q).  Inside one fused step the target of an
@@ -139,6 +126,7 @@ __device__ __forceinline__ bool mbar_wait_long(unsigned long long* bar, unsigned
 // A tile with more than 65,535 records counts in 32-bit counters in global scratch instead.
 // full[stage] : the producer's copies have landed (transaction barrier);  done[stage] : every consumer thread
 // has finished the tile in that stage.
+constexpr unsigned NSTAGE = 2;           // shared-memory stages per block: tiles loaded ahead of the consumers
 constexpr unsigned CONSUMERS = 256;      // consumer threads per block (+ 32 of the producer warp)
 // Records staged in shared memory (front part, back part of the region); the rest is read from global memory.
 __host__ __device__ constexpr unsigned rc_front(unsigned ct) { return ct + ct / 4u + 32u; }
@@ -250,14 +238,14 @@ __global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
     constexpr unsigned RC = rc_front(CT), RCB = rc_back(CT);
     constexpr unsigned CPT = (T2 + CT - 1u) / CT;              // cells per consumer thread when every cell is occupied
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_full[2], s_done[2];
-    __shared__ TileHdr s_hdr[2];
+    __shared__ __align__(8) unsigned long long s_full[NSTAGE], s_done[NSTAGE];
+    __shared__ TileHdr s_hdr[NSTAGE];
     __shared__ unsigned s_stay, s_nocc, s_base, s_abort;
     __shared__ unsigned s_goals, s_timeouts, s_conf, s_nbig, s_nbigent, s_bad;     // accumulated over the block's tiles
 
     const TileP& tp = p.tp;
     const unsigned stage_bytes = HS2 * 16u + RC * 16u + RCB * 16u + tp.cls_stride;
-    unsigned long long* s_n = reinterpret_cast<unsigned long long*>(smem + 2u * stage_bytes);
+    unsigned long long* s_n = reinterpret_cast<unsigned long long*>(smem + NSTAGE * stage_bytes);
     unsigned short* s_list = reinterpret_cast<unsigned short*>(s_n + T2);
     unsigned* s_flag = reinterpret_cast<unsigned*>(s_list + T2);       // one bit per cell: listed
 
@@ -272,7 +260,7 @@ __global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
 
     if (tid == 0) {
         s_goals = 0; s_timeouts = 0; s_conf = 0; s_nbig = 0; s_nbigent = 0; s_bad = 0; s_abort = 0;
-        mbar_init(&s_full[0], 1u); mbar_init(&s_full[1], 1u); mbar_init(&s_done[0], CT); mbar_init(&s_done[1], CT);
+        for (unsigned q = 0; q < NSTAGE; ++q) { mbar_init(&s_full[q], 1u); mbar_init(&s_done[q], CT); }
         if (blockIdx.x == 0) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
     }
     __syncthreads();
@@ -293,8 +281,8 @@ __global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
             }
             return r;
         };
-        auto load_tile = [&](unsigned k, const Raw& raw) {    // header + bulk copies of the block's k-th tile into stage k & 1
-            const unsigned b = k & 1u, tile = blockIdx.x + k * gridDim.x;
+        auto load_tile = [&](unsigned k, const Raw& raw) {    // header + bulk copies of the block's k-th tile into stage k % NSTAGE
+            const unsigned b = k % NSTAGE, tile = blockIdx.x + k * gridDim.x;
             unsigned char* st = smem + b * stage_bytes;
             float4* s_q = reinterpret_cast<float4*>(st);
             int4* s_rec = reinterpret_cast<int4*>(st + HS2 * 16u);
@@ -319,13 +307,12 @@ __global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
             for (int gy = gy_lo + (int)lane; gy <= gy_hi; gy += 32)
                 bulk_g2s(s_q + (unsigned)(gy - (ty0 - 1)) * HS + (unsigned)(xs - (tx0 - 1)), Qin + (size_t)gy * (size_t)p.W + (size_t)xs, bytes_h, &s_full[b]);
         };
-        if (ntl > 0u) load_tile(0u, fetch_hdr(0u));
-        if (ntl > 1u) load_tile(1u, fetch_hdr(1u));
+        for (unsigned q = 0; q < NSTAGE; ++q) if (ntl > q) load_tile(q, fetch_hdr(q));
         for (unsigned k = 0; k < ntl; ++k) {
-            const unsigned b = k & 1u;
-            const Raw nxt = fetch_hdr(k + 2u);                 // in flight while this warp waits
+            const unsigned b = k % NSTAGE;
+            const Raw nxt = fetch_hdr(k + NSTAGE);             // in flight while this warp waits
             // one lane polls; the others park at the warp barrier instead of spinning
-            if (lane == 0 && !mbar_wait_long(&s_done[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
+            if (lane == 0 && !mbar_wait(&s_done[b], (k / NSTAGE) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
             __syncwarp();
             if (*(volatile unsigned*)&s_abort) break;
             // rows of Q_{t+1} out (the consumers fenced their writes towards the async proxy before arriving)
@@ -337,7 +324,7 @@ __global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
                 bulk_s2g(Qout + (size_t)(ty0 + (int)r) * (size_t)p.W + (size_t)tx0, s_q + (r + 1u) * HS + 1u, wi * 16u);
             bulk_commit_wait_read();                            // the stage may be overwritten once its rows have been read
             __syncwarp();
-            if (k + 2u < ntl) load_tile(k + 2u, nxt);
+            if (k + NSTAGE < ntl) load_tile(k + NSTAGE, nxt);
         }
         return;
     }
@@ -350,7 +337,7 @@ __global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
     c.s_stay = &s_stay; c.s_goals = &s_goals; c.s_timeouts = &s_timeouts;
     unsigned conf = 0;
     for (unsigned k = 0; k < ntl; ++k) {
-        const unsigned b = k & 1u;
+        const unsigned b = k % NSTAGE;
         unsigned char* st = smem + b * stage_bytes;
         float4* s_q = reinterpret_cast<float4*>(st);
         const int4* s_rec = reinterpret_cast<const int4*>(st + HS2 * 16u);
@@ -361,7 +348,7 @@ __global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
         for (unsigned q = 2u * tid; q < T2; q += 2u * CT) *reinterpret_cast<uint4*>(s_n + q) = make_uint4(0u, 0u, 0u, 0u);
         for (unsigned q = tid; q < (T2 + 31u) / 32u; q += CT) s_flag[q] = 0u;
         // one thread waits for the copies; the barrier below passes the news (and the data) on to the others
-        if (tid == 0 && !mbar_wait(&s_full[b], (k >> 1) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
+        if (tid == 0 && !mbar_wait(&s_full[b], (k / NSTAGE) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
         cons_sync<CT>();
         if (s_abort) break;                                    // never seen; the producer gives up at its next wait
         const TileHdr h = s_hdr[b];
@@ -558,7 +545,7 @@ static size_t work_bytes(size_t T2) { return (T2 * 8 + T2 * 2 + (T2 + 31) / 32 *
 size_t tile_step_smem(const Params& p) {
     const size_t T = p.tp.T, HS = T + 2;
     const size_t stage = HS * HS * 16 + (size_t)rc_front(CONSUMERS) * 16 + (size_t)rc_back(CONSUMERS) * 16 + p.tp.cls_stride;
-    return 2 * stage + work_bytes(T * T);
+    return NSTAGE * stage + work_bytes(T * T);
 }
 template <unsigned TSH>
 static cudaError_t configure_one(int bytes, int* per_sm) {
