@@ -110,8 +110,8 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 // (update_batch takes arbitrary caller transitions, so it keeps its ordered fold.)
 //
 // The step kernel is persistent: a block walks over tiles blockIdx, blockIdx + gridDim, ...  It has eight
-// CONSUMER warps, which do all the arithmetic on shared memory, and one PRODUCER warp (one active thread),
-// which only moves data: while the consumers work on tile k in one stage of shared memory, the producer has
+// CONSUMER warps, which do all the arithmetic on shared memory, and one PRODUCER warp (each lane issues the
+// copies of one or two table rows), which only moves data: while the consumers work on tile k in one stage of shared memory, the producer has
 // the bulk copies of tile k+1 in flight into the other stage and the rows of tile k-1 on their way out.
 //
 // Per stage:  s_q    HS*HS float4   Q_t of the tile and its halo; the consumers turn the interior into
