@@ -43,7 +43,8 @@ class Config(C.Structure):
         ("eps0", C.c_double), ("eps_decay", C.c_double), ("eps_end", C.c_double),
         ("eps_steps", C.c_int64),
         ("q_init_kind", C.c_int32), ("q_init_scale", C.c_float),
-        ("legacy_clamp", C.c_int32), ("sync_every", C.c_int32), ("reserved", C.c_int32 * 4),
+        ("legacy_clamp", C.c_int32), ("sync_every", C.c_int32),
+        ("rebucket_every", C.c_int32), ("tile_edge", C.c_int32), ("reserved", C.c_int32 * 2),
     ]
 
     def copy(self):
@@ -100,7 +101,8 @@ ABI = {
     "cudarl_timer_start": (C.c_int, [_P]),
     "cudarl_timer_stop_ms": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "cudarl_kernel_timing": (C.c_int, [_P, C.c_int]),
-    "cudarl_kernel_time_ms": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_int64)]),
+    "cudarl_kernel_time_ms": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int64)]),
+    "cudarl_debug_set_copy_wait_polls": (C.c_int, [_P, C.c_int32]),
     "cudarl_version": (C.c_char_p, []),
 }
 
@@ -340,9 +342,12 @@ class VecGridWorld:
         self._ck(self.lib.cudarl_kernel_timing(self.h, 1 if on else 0))
 
     def kernel_time_ms(self):
-        a, b, n = C.c_float(), C.c_float(), C.c_int64()
-        self._ck(self.lib.cudarl_kernel_time_ms(self.h, C.byref(a), C.byref(b), C.byref(n)))
-        return a.value, b.value, n.value
+        a, n = C.c_float(), C.c_int64()
+        self._ck(self.lib.cudarl_kernel_time_ms(self.h, C.byref(a), C.byref(n)))
+        return a.value, n.value
+
+    def debug_set_copy_wait_polls(self, polls):
+        self._ck(self.lib.cudarl_debug_set_copy_wait_polls(self.h, polls))
 
 
 def comm_unique_id():

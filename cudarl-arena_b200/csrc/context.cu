@@ -1,7 +1,8 @@
 // context.cu -- the C ABI of include/cudarl.h: one context per GPU owning the shard's device
 // buffers, one stream, and (optionally) an NCCL communicator for replica averaging.
-// Host logic only; every hot operation is a kernel of kernels.cu.  There is no CPU fallback:
-// a call either runs on the device or returns an error code.
+// Host logic only; every hot operation is a kernel of tile_engine.cu (the fused train step and its record
+// bucketing) or kernels.cu (everything else).  There is no CPU fallback: a call either runs on the device or
+// returns an error code.
 #include "../../include/cudarl.h"
 #include "kernels.cuh"
 #include <nccl.h>
@@ -43,6 +44,10 @@ struct NcclApi {
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     bool load(std::string& err) {
         if (h) return true;
@@ -53,8 +58,10 @@ struct NcclApi {
         CommDestroy = (decltype(CommDestroy))dlsym(h, "ncclCommDestroy");
         AllReduce = (decltype(AllReduce))dlsym(h, "ncclAllReduce");
         AllGather = (decltype(AllGather))dlsym(h, "ncclAllGather");
+        Send = (decltype(Send))dlsym(h, "ncclSend"); Recv = (decltype(Recv))dlsym(h, "ncclRecv");
+        GroupStart = (decltype(GroupStart))dlsym(h, "ncclGroupStart"); GroupEnd = (decltype(GroupEnd))dlsym(h, "ncclGroupEnd");
         GetErrorString = (decltype(GetErrorString))dlsym(h, "ncclGetErrorString");
-        if (!GetUniqueId || !CommInitRank || !CommDestroy || !AllReduce || !AllGather) { err = "NCCL symbols missing"; h = nullptr; return false; }
+        if (!GetUniqueId || !CommInitRank || !CommDestroy || !AllReduce || !AllGather || !Send || !Recv || !GroupStart || !GroupEnd) { err = "NCCL symbols missing"; h = nullptr; return false; }
         return true;
     }
 };
@@ -79,14 +86,15 @@ struct cudarl_ctx {
     void *dimport = nullptr;              // staging for caller state arrays (3 x N int32)
     void *dactive = nullptr;
     // tile engine (the layout the train step runs on)
-    void *dQd[2] = {nullptr, nullptr}, *drec[2] = {nullptr, nullptr}, *dovf[2] = {nullptr, nullptr};
-    void *dtmeta = nullptr, *dtscratch = nullptr, *dtcls = nullptr;   // per-tile offsets / capacities / counters; fold entries of crowded tiles
+    void *dQ = nullptr;                    // the table (padded so that it splits into equal slices for any number of ranks)
+    void *drec[2] = {nullptr, nullptr}, *darr[2] = {nullptr, nullptr}, *dovf[2] = {nullptr, nullptr}, *dbmax[2] = {nullptr, nullptr};
+    void *dtmeta = nullptr, *dtscratch = nullptr, *dtcls = nullptr;   // per-tile regions / counters; 32-bit counters of crowded tiles
     bool tile_mode = false;               // true: the records live in tile regions (train steps), false: in environment order
     bool cls_dirty = true;                // the per-tile class bytes must be rebuilt from the cell words
     int64_t bucket_every = 128, since_bucket = 0;
     void *dent = nullptr, *dctl = nullptr, *deps = nullptr;
     void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
-    void *dgather = nullptr;              // replica averaging: all-gather landing zone
+    void *dgather = nullptr;              // replica averaging: the other ranks' rows of this rank's slice
     void* dub[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; size_t ub_cap = 0;   // update_batch staging
     void* dact = nullptr;                 // actions staging for the host form of step_actions
     size_t ent_cap = 0, eps_cap = 0;
@@ -103,8 +111,10 @@ struct cudarl_ctx {
     ncclComm_t comm = nullptr; int rank = 0, nranks = 1;
     // timing
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    bool ktiming = false; std::vector<cudaEvent_t> kev; size_t kev_used = 0;
-    double main_ms = 0, fix_ms = 0; int64_t klaunches = 0;
+    // kernel timing: one event pair around every uninterrupted run of step-kernel launches
+    bool ktiming = false, kseg_open = false; std::vector<cudaEvent_t> kev; size_t kev_used = 0;
+    std::vector<int64_t> kseg_launches; int64_t kseg_count = 0;
+    double main_ms = 0; int64_t klaunches = 0;
 };
 
 namespace {
@@ -179,9 +189,6 @@ int build_cells(cudarl_ctx* c, std::vector<uint8_t>& cells, uint32_t& start_cell
     if (fallback == 0xFFFFFFFFu) fallback = start_cell;
     return 0;
 }
-
-// the current table: the dense copy of the parity of the step counter
-void bind_q(cudarl_ctx* c) { c->p.Q = c->p.tp.Qd[c->h_step & 1]; }
 
 int upload_cells(cudarl_ctx* c) {
     const size_t S = c->p.S, pad = (S + 7) / 8 * 8;
@@ -259,71 +266,120 @@ int upload_eps(cudarl_ctx* c, const float* eps, size_t n) {
     return 0;
 }
 
+// Close the open run of step-kernel launches (an event after its last launch).
+int close_kernel_segment(cudarl_ctx* c) {
+    if (!c->kseg_open) return 0;
+    CK(cudaEventRecord(c->kev[c->kev_used + 1], c->st));
+    c->kev_used += 2; c->kseg_launches.push_back(c->kseg_count);
+    c->kseg_open = false; c->kseg_count = 0;
+    return 0;
+}
 int drain_kernel_events(cudarl_ctx* c) {
+    { int rc = close_kernel_segment(c); if (rc) return rc; }
     if (!c->kev_used) return 0;
     CK(cudaStreamSynchronize(c->st));
-    for (size_t k = 0; k + 2 < c->kev_used + 1; k += 3) {
-        float a = 0, b = 0;
+    for (size_t k = 0; k + 1 < c->kev_used; k += 2) {
+        float a = 0;
         CK(cudaEventElapsedTime(&a, c->kev[k], c->kev[k + 1]));
-        CK(cudaEventElapsedTime(&b, c->kev[k + 1], c->kev[k + 2]));
-        c->main_ms += a; c->fix_ms += b; c->klaunches += 1;
+        c->main_ms += a; c->klaunches += c->kseg_launches[k / 2];
     }
-    c->kev_used = 0;
+    c->kev_used = 0; c->kseg_launches.clear();
     return 0;
 }
 
+// After a synchronisation: has any kernel recorded an internal failure (a copy that never landed, a full
+// scratch area, a record outside its tile)?  The word is sticky; the results of the context are not to be trusted.
+int check_device_error(cudarl_ctx* c) {
+    unsigned err = 0;
+    CK(cudaMemcpyAsync(&err, (const char*)c->dctl + offsetof(Ctl, error), sizeof(err), cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    if (err) return fail(c, CUDARL_ERR_DEVICE + (int)err, "device error bits " + std::to_string(err) +
+                         ((err & ERR_COPY_TIMEOUT) ? " (a tile copy did not land within its wait bound)" : "") +
+                         ((err & ERR_SCRATCH_OVERFLOW) ? " (scratch area full)" : "") + ((err & ERR_BAD_STATE) ? " (a record outside its tile or the grid)" : "") +
+                         ((err & ERR_CHAIN_CYCLE) ? " (update_batch chain longer than the batch)" : ""));
+    return 0;
+}
 
 // ---- tile engine: buffers, entering and leaving the tile layout ------------------------------------
-// Tile edge: the largest of 32 / 16 / 8 cells that still gives every SM more than one tile (measured on
-// B200: fewer, fuller tiles win as long as all SMs have work).
+// The table as a 2-D tensor of floats, 4W wide and H high, fetched in boxes of one tile (4T x T floats).
+int make_table_map(cudarl_ctx* c) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* f = nullptr; cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !f) return fail(c, -5, "cuTensorMapEncodeTiled is not available in this driver");
+        encode = (EncodeFn)f;
+    }
+    const Params& p = c->p;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.W * 4u, (cuuint64_t)p.H};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.W * 16u};                 // bytes between table rows: a multiple of 16
+    const cuuint32_t box[2] = {4u * p.tp.T, p.tp.T}, estr[2] = {1u, 1u};
+    const CUresult r = encode(&c->p.tp.tmq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p.Q, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, p.tp.T >= 16u ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(c, -5, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return 0;
+}
+
+// Tile edge: 16 cells where a 16 x 16 tile holds at most ~128 environments on average, else 8 (a warp steps a
+// tile's environments 32 at a time; measured on B200, about 64 per tile keeps the warps short and even).
 int alloc_tiles(cudarl_ctx* c) {
     Params& p = c->p; TileP& tp = p.tp;
     const size_t S = p.S, N = p.N ? p.N : 1;
-    unsigned tsh = 3;
-    for (unsigned cand = 5; cand >= 3; --cand) {
-        const size_t nt = (((size_t)p.W + (1u << cand) - 1) >> cand) * (((size_t)p.H + (1u << cand) - 1) >> cand);
-        if (nt >= 222) { tsh = cand; break; }
-    }
-    if (const char* ev = getenv("CUDARL_TILE_SHIFT")) { int v = atoi(ev); if (v >= 3 && v <= 5) tsh = (unsigned)v; }
+    CK(cudaMalloc(&c->dQ, (S + 64) * sizeof(float4)));
+    CK(cudaMemsetAsync(c->dQ, 0, (S + 64) * sizeof(float4), c->st));
+    p.Q = (float4*)c->dQ;
+    const size_t nt16 = (((size_t)p.W + 15) >> 4) * (((size_t)p.H + 15) >> 4);
+    unsigned tsh = (N / nt16 <= 128) ? 4u : 3u;
+    if (c->cfg.tile_edge == 8) tsh = 3u; else if (c->cfg.tile_edge == 16) tsh = 4u;
     tp.tshift = tsh; tp.T = 1u << tsh;
     tp.tiles_x = (unsigned)((p.W + (int)tp.T - 1) >> tsh); tp.tiles_y = (unsigned)((p.H + (int)tp.T - 1) >> tsh);
     tp.ntiles = tp.tiles_x * tp.tiles_y;
+    const size_t nt = tp.ntiles;
     for (int k = 0; k < 2; ++k) {
-        CK(cudaMalloc(&c->dQd[k], S * sizeof(float4)));
-        CK(cudaMalloc(&c->drec[k], (N + N / 2 + 96 * (size_t)tp.ntiles + 64) * sizeof(int4)));
+        CK(cudaMalloc(&c->drec[k], (N + N / 4 + 32 * nt + 64) * sizeof(int4)));
+        CK(cudaMalloc(&c->darr[k], nt * ARR_CAP * sizeof(int4)));
         CK(cudaMalloc(&c->dovf[k], N * sizeof(int4)));
-        tp.Qd[k] = (float4*)c->dQd[k]; tp.rec[k] = (int4*)c->drec[k]; tp.ovf[k] = (int4*)c->dovf[k];
+        CK(cudaMalloc(&c->dbmax[k], nt * 4 * tp.T * sizeof(float)));
+        CK(cudaMemsetAsync(c->dbmax[k], 0, nt * 4 * tp.T * sizeof(float), c->st));
+        tp.rec[k] = (int4*)c->drec[k]; tp.arr[k] = (int4*)c->darr[k]; tp.ovf[k] = (int4*)c->dovf[k]; tp.bmax[k] = (float*)c->dbmax[k];
     }
-    const size_t nt = tp.ntiles, meta = (nt + 1) + nt + 4 * nt + 8;
+    const size_t meta = 2 * (nt + 1) + 4 * nt + 8;
     CK(cudaMalloc(&c->dtmeta, meta * sizeof(unsigned)));
     CK(cudaMemsetAsync(c->dtmeta, 0, meta * sizeof(unsigned), c->st));
     unsigned* m = (unsigned*)c->dtmeta;
-    tp.reg_off = m; m += nt + 1; tp.front_cap = m; m += nt;
+    tp.reg = (uint2*)m; m += 2 * (nt + 1);
     tp.seg_cnt[0] = m; m += nt; tp.seg_cnt[1] = m; m += nt; tp.arr_cnt[0] = m; m += nt; tp.arr_cnt[1] = m; m += nt;
     tp.tctl = m;
-    tp.cls_stride = (unsigned)((((size_t)tp.T + 2) * (tp.T + 2) + 15) / 16 * 16);
+    tp.cls_stride = tile_cls_stride(tsh);
     CK(cudaMalloc(&c->dtcls, nt * tp.cls_stride));
     tp.tcls = (unsigned char*)c->dtcls;
     CK(cudaMalloc(&c->dtscratch, (N > 65536 ? N : 65536) * sizeof(uint2)));
     tp.scratch = (uint2*)c->dtscratch;
+    tp.wait_polls = 0;
+    { int rm = make_table_map(c); if (rm) return rm; }
     if (tile_engine_configure(p, c->cfg.device) != 0) { cudaGetLastError(); return fail(c, -5, "tile step: shared memory request refused"); }
     return 0;
 }
 
-// records in environment order -> tile regions (the table is the same dense array in both layouts)
+// records in environment order -> tile regions; border values from the table as it is now
 int enter_tiles(cudarl_ctx* c) {
     if (c->tile_mode) return 0;
     c->p.step = (unsigned long long)c->h_step;
     if (c->cls_dirty) { launch_tile_classes(c->p, c->st); c->cls_dirty = false; }
     launch_tile_bucket(c->p, c->st);
+    launch_tile_border(c->p, c->st);
     CK(cudaGetLastError());
     c->tile_mode = true; c->since_bucket = 0;
     return 0;
 }
 // tile regions -> records back in environment order
 int leave_tiles(cudarl_ctx* c) {
-    bind_q(c);
     if (!c->tile_mode) return 0;
+    { int rc = close_kernel_segment(c); if (rc) return rc; }
     c->p.step = (unsigned long long)c->h_step;
     launch_tile_export(c->p, c->st);
     CK(cudaGetLastError());
@@ -332,6 +388,7 @@ int leave_tiles(cudarl_ctx* c) {
 }
 // re-size the tile regions from the current populations
 int rebucket_tiles(cudarl_ctx* c) {
+    { int rc = close_kernel_segment(c); if (rc) return rc; }
     c->p.step = (unsigned long long)c->h_step;
     launch_tile_export(c->p, c->st);
     launch_tile_bucket(c->p, c->st);
@@ -340,21 +397,30 @@ int rebucket_tiles(cudarl_ctx* c) {
     return 0;
 }
 
-// Q <- (Q_0 + Q_1 + ... + Q_{R-1}) * (1/R), summed in rank order on every GPU.  The rows travel with an
-// NCCL all-gather in chunks (NVLink / NVSwitch), straight out of the dense table; the reduction itself is
-// our kernel, so the result is the same bits on every rank and the same bits as the CPU oracle for any R
-// (an all-reduce would leave the summation order to the library).
+// Q <- (Q_0 + Q_1 + ... + Q_{R-1}) * (1/R), summed in rank order on every GPU, shaped like an all-reduce: the table
+// is cut into R equal slices, rank j owns slice j.  (1) every rank sends its rows of slice j to rank j (grouped NCCL
+// send / receive over NVLink / NVSwitch); (2) rank j sums the R versions of its slice in rank order 0..R-1 in our own
+// kernel, scale fused, into its table; (3) an in-place all-gather hands the averaged slices round.  Each GPU receives
+// 2 (R-1)/R of the table per averaging, and because the summation order is ours, not the library's, every rank ends
+// up with the same bits as the CPU oracle for any R.
 int average_now(cudarl_ctx* c) {
     if (!c->comm || c->nranks <= 1) return 0;
-    const size_t S = c->p.S, R = (size_t)c->nranks;
-    const size_t chunk = S < (1u << 20) ? S : (1u << 20);            // cells per round: 16 MiB per rank
-    if (!c->dgather) CK(cudaMalloc(&c->dgather, R * chunk * sizeof(float4)));
-    float4* table = c->p.tp.Qd[c->h_step & 1];
-    for (size_t c0 = 0; c0 < S; c0 += chunk) {
-        const size_t n = S - c0 < chunk ? S - c0 : chunk;
-        NK(g_nccl.AllGather(table + c0, c->dgather, n * 4, ncclFloat, c->comm, c->st));
-        launch_q_average_dense(c->p, table, (const float4*)c->dgather, (unsigned)R, (unsigned)c0, (unsigned)n, 1.0f / (float)R, c->st);
+    { int rc = close_kernel_segment(c); if (rc) return rc; }
+    const size_t S = c->p.S, R = (size_t)c->nranks, self = (size_t)c->rank;
+    const size_t slice = (S + R - 1) / R;                      // cells; R * slice <= S + 64 = the padded table
+    if (R > 64) return fail(c, -1, "replica averaging supports at most 64 ranks");
+    if (!c->dgather) CK(cudaMalloc(&c->dgather, (R - 1) * slice * sizeof(float4)));
+    float4* table = c->p.Q; float4* others = (float4*)c->dgather;
+    NK(g_nccl.GroupStart());
+    for (size_t r = 0; r < R; ++r) {
+        if (r == self) continue;
+        NK(g_nccl.Send(table + r * slice, slice * 4, ncclFloat, (int)r, c->comm, c->st));
+        NK(g_nccl.Recv(others + (r - (r > self ? 1 : 0)) * slice, slice * 4, ncclFloat, (int)r, c->comm, c->st));
     }
+    NK(g_nccl.GroupEnd());
+    launch_q_average_slice(table, others, (unsigned)R, (unsigned)self, self * slice, slice, 1.0f / (float)R, c->st);
+    NK(g_nccl.AllGather(table + self * slice, table, slice * 4, ncclFloat, c->comm, c->st));
+    if (c->tile_mode) { c->p.step = (unsigned long long)c->h_step; launch_tile_border(c->p, c->st); }
     CK(cudaGetLastError());
     return 0;
 }
@@ -362,21 +428,21 @@ int average_now(cudarl_ctx* c) {
 int run_steps(cudarl_ctx* c, int64_t n) {
     { int re = enter_tiles(c); if (re) return re; }
     for (int64_t k = 0; k < n; ++k) {
-        cudaEvent_t a = nullptr, b = nullptr, d = nullptr;
-        if (c->ktiming) {
-            if (c->kev_used + 3 > c->kev.size()) { int rc = drain_kernel_events(c); if (rc) return rc; }
-            a = c->kev[c->kev_used]; b = c->kev[c->kev_used + 1]; d = c->kev[c->kev_used + 2]; c->kev_used += 3;
-        }
         if (c->bucket_every > 0 && c->since_bucket >= c->bucket_every) { int rs = rebucket_tiles(c); if (rs) return rs; }
+        if (c->ktiming && !c->kseg_open) {
+            if (c->kev_used + 2 > c->kev.size()) { int rc = drain_kernel_events(c); if (rc) return rc; }
+            CK(cudaEventRecord(c->kev[c->kev_used], c->st));
+            c->kseg_open = true; c->kseg_count = 0;
+        }
         c->p.step = (unsigned long long)c->h_step;
         c->p.eps_idx = c->eps_mode == 1 ? (unsigned)k : 0u;
         c->p.eps_from_ctl = c->eps_mode == 2 ? 1 : 0;
         if (c->eps_mode != 2 && c->h_eps) c->eps_used = c->h_eps[c->p.eps_idx];
-        launch_tile_step(c->p, c->trace, c->st, a, b, d);
-        c->h_step += 1; c->since_bucket += 1;
+        launch_tile_step(c->p, c->trace, c->st);
+        c->h_step += 1; c->since_bucket += 1; c->kseg_count += 1;
         if (c->cfg.sync_every > 0 && c->comm && (c->h_step % c->cfg.sync_every) == 0) { int rc = average_now(c); if (rc) return rc; }
     }
-    bind_q(c);
+    { int rc = close_kernel_segment(c); if (rc) return rc; }
     CK(cudaGetLastError());
     return 0;
 }
@@ -387,7 +453,8 @@ void free_all(cudarl_ctx* c) {
     void* bufs[] = {c->dci, c->dstate[0], c->dstate[1], c->dimport, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->dgather, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6],
-                    c->dQd[0], c->dQd[1], c->drec[0], c->drec[1], c->dovf[0], c->dovf[1], c->dtmeta, c->dtscratch, c->dtcls};
+                    c->dQ, c->drec[0], c->drec[1], c->darr[0], c->darr[1], c->dovf[0], c->dovf[1], c->dbmax[0], c->dbmax[1],
+                    c->dtmeta, c->dtscratch, c->dtcls};
     for (void* b : bufs) if (b) cudaFree(b);
     if (c->h_eps) cudaFreeHost(c->h_eps);
     for (auto e : c->kev) cudaEventDestroy(e);
@@ -426,6 +493,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
     if (f->env_offset < 0 || f->env_offset + f->num_envs >= (1ll << 32)) return fail(nullptr, -1, "env_offset out of range");
     if (f->max_steps < 0) return fail(nullptr, -1, "max_steps negative");
     if (f->eps_kind < 0 || f->eps_kind > 3) return fail(nullptr, -1, "bad eps_kind");
+    if (f->tile_edge != 0 && f->tile_edge != 8 && f->tile_edge != 16) return fail(nullptr, -1, "tile_edge must be 0 (automatic), 8 or 16");
     cudarl_ctx* c = new (std::nothrow) cudarl_ctx();
     if (!c) return fail(nullptr, -1, "out of host memory");
     c->cfg = *f;
@@ -453,7 +521,6 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             p.ctl = (Ctl*)c->dctl;
             int r2 = ensure_entry_capacity(c, N); if (r2) return r2;
             r2 = alloc_tiles(c); if (r2) return r2;
-            bind_q(c);
             r2 = upload_cells(c); if (r2) return r2;
             launch_q_init(p, f->q_init_kind, f->q_init_scale, c->st);
             float e0 = (float)f->eps0; r2 = upload_eps(c, &e0, 1); if (r2) return r2;
@@ -464,8 +531,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             CK(cudaStreamSynchronize(c->st));
             return 0;
         };
-        c->bucket_every = f->reserved[0] > 0 ? f->reserved[0] : (f->reserved[0] < 0 ? 0 : 128);
-        if (const char* ev = getenv("CUDARL_BUCKET_EVERY")) c->bucket_every = atoll(ev);
+        c->bucket_every = f->rebucket_every > 0 ? f->rebucket_every : (f->rebucket_every < 0 ? 0 : 128);
         rc = body();
     } while (0);
     if (rc) { g_err = c->err; free_all(c); delete c; return rc; }
@@ -483,7 +549,17 @@ void cudarl_destroy(cudarl_ctx* c) {
 
 int cudarl_get_config(const cudarl_ctx* c, cudarl_config* out) { if (!c || !out) return -1; *out = c->cfg; return 0; }
 
-int cudarl_synchronize(cudarl_ctx* c) { if (!c) return -1; CK(cudaStreamSynchronize(c->st)); return 0; }
+int cudarl_synchronize(cudarl_ctx* c) {
+    if (!c) return -1;
+    CK(cudaSetDevice(c->cfg.device));
+    CK(cudaStreamSynchronize(c->st));
+    return check_device_error(c);
+}
+int cudarl_debug_set_copy_wait_polls(cudarl_ctx* c, int32_t polls) {
+    if (!c || polls < 0) return fail(c, -1, "bad argument");
+    c->p.tp.wait_polls = (unsigned)polls;
+    return 0;
+}
 
 int cudarl_reset_all(cudarl_ctx* c) {
     if (!c) return -1;
@@ -661,8 +737,7 @@ int cudarl_get_state(cudarl_ctx* c, int32_t* x, int32_t* y, int32_t* t) {
     if (x) CK(cudaMemcpyAsync(x, base, b, cudaMemcpyDeviceToHost, c->st));
     if (y) CK(cudaMemcpyAsync(y, base + b, b, cudaMemcpyDeviceToHost, c->st));
     if (t) CK(cudaMemcpyAsync(t, base + 2 * b, b, cudaMemcpyDeviceToHost, c->st));
-    CK(cudaStreamSynchronize(c->st));
-    return 0;
+    return check_device_error(c);
 }
 
 int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const int32_t* t) {
@@ -688,8 +763,7 @@ int cudarl_get_q(cudarl_ctx* c, float* q) {
     CK(cudaSetDevice(c->cfg.device));
     { int rl = leave_tiles(c); if (rl) return rl; }
     CK(cudaMemcpyAsync(q, c->p.Q, (size_t)c->p.S * sizeof(float4), cudaMemcpyDeviceToHost, c->st));   // the table already is in the caller's layout
-    CK(cudaStreamSynchronize(c->st));
-    return 0;
+    return check_device_error(c);
 }
 int cudarl_set_q(cudarl_ctx* c, const float* q) {
     if (!c || !q) return fail(c, -1, "null argument");
@@ -745,6 +819,7 @@ int cudarl_get_stats(cudarl_ctx* c, cudarl_stats* out) {
     out->conflicts = (int64_t)h.conflicts; out->long_chains = (int64_t)h.long_chains; out->chained = (int64_t)h.general;
     out->reward_sum = (double)out->goals * 1.0 - 0.01 * (double)(out->env_steps - out->goals);
     out->epsilon = c->eps_mode == 2 ? h.eps_used : c->eps_used; out->device_error = (int32_t)h.error;
+    if (h.error) return fail(c, CUDARL_ERR_DEVICE + (int)h.error, "device error bits " + std::to_string(h.error) + " (statistics filled in; the results of this context are not to be trusted)");
     return 0;
 }
 
@@ -785,20 +860,19 @@ int cudarl_kernel_timing(cudarl_ctx* c, int on) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));
     if (on && c->kev.empty()) {
-        c->kev.resize(3 * 512);
+        c->kev.resize(2 * 256);
         for (auto& e : c->kev) CK(cudaEventCreate(&e));
     }
     if (!on) { int rc = drain_kernel_events(c); if (rc) return rc; }
-    else { c->main_ms = c->fix_ms = 0; c->klaunches = 0; c->kev_used = 0; }
+    else { c->main_ms = 0; c->klaunches = 0; c->kev_used = 0; c->kseg_open = false; c->kseg_launches.clear(); }
     c->ktiming = on != 0;
     return 0;
 }
-int cudarl_kernel_time_ms(cudarl_ctx* c, float* main_ms, float* fix_ms, int64_t* launches) {
+int cudarl_kernel_time_ms(cudarl_ctx* c, float* step_ms, int64_t* launches) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));
     int rc = drain_kernel_events(c); if (rc) return rc;
-    if (main_ms) *main_ms = (float)c->main_ms;
-    if (fix_ms) *fix_ms = (float)c->fix_ms;
+    if (step_ms) *step_ms = (float)c->main_ms;
     if (launches) *launches = c->klaunches;
     return 0;
 }

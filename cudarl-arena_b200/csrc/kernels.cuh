@@ -1,6 +1,7 @@
-// kernels.cuh -- device-side data layout and launch entry points shared by kernels.cu (the
+// kernels.cuh -- device-side data layout and launch entry points shared by kernels.cu, tile_engine.cu (the
 // sm_100a kernels) and context.cu (the C ABI).  Nothing here is visible outside the library.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -30,34 +31,39 @@ struct Ctl {
     unsigned int long_count[2];     // chains queued for the warp-per-chain kernel, per step parity
     unsigned int long2_count[2];    // chains too long for a warp, queued for the block-per-chain kernel
     unsigned int scratch_cursor;    // bump allocator of the long-chain scratch, reset every step
-    unsigned int blocks_done;       // last-block detection of the fix kernel
     unsigned int error;             // sticky internal error bits
     float eps_used;                 // epsilon of the most recent step (for the stats call)
 };
 
-enum : unsigned { ERR_SCRATCH_OVERFLOW = 1u, ERR_BAD_STATE = 2u, ERR_BAD_TRANSITION = 4u, ERR_CHAIN_CYCLE = 8u, ERR_CAS_LIMIT = 16u, ERR_COPY_TIMEOUT = 32u };
+enum : unsigned { ERR_SCRATCH_OVERFLOW = 1u, ERR_BAD_STATE = 2u, ERR_CHAIN_CYCLE = 8u, ERR_COPY_TIMEOUT = 32u };   // = CUDARL_DEVERR_* of cudarl.h
 
 // ---- tile engine (tile_engine.cu): the layout the train step runs on ---------------------------
-// The grid is cut into T x T tiles.  Every tile owns a REGION of the record array: a front part that
-// only the tile's own block writes (environments that stay) and a back part that other blocks append
-// to with an atomic cursor (environments that walk or restart into the tile).  Two copies of the
-// records, of the per-tile counters and of the dense table alternate by step parity, so a step reads
-// one set and writes the other.
+// The grid is cut into T x T tiles (T = 16 or 8); one WARP steps one tile at a time.  The table is a single
+// dense array updated in place: a tile's cells are read and written by the tile's own warp only, and what
+// a move across a tile edge needs from the neighbour -- max_a Q_t of the cell beyond the edge -- comes from a
+// small double-buffered border array that every tile refreshes at the end of its step.
+// Every tile owns a REGION of the record array that only the tile's own warp writes (environments that
+// stay) and a fixed arrival buffer that other warps append to with an atomic cursor (environments that
+// walk or restart into the tile).  Records, counters and border values alternate by step parity, so a step
+// reads one set and writes the other.
+constexpr unsigned ARR_CAP = 32u;  // arrival slots per tile and step; what does not fit goes to the spill list
 struct TileP {
     unsigned tshift, T;        // tile edge = 1 << tshift cells
     unsigned tiles_x, tiles_y, ntiles;
     unsigned grid;             // blocks of the persistent step kernel (SMs x resident blocks per SM)
-    float4* Qd[2];             // dense table, one float4 (4 action values) per cell; [step & 1] is current
-    int4* rec[2];              // records {x, y, t, id}; [step & 1] is current
-    unsigned* reg_off;         // ntiles + 1: start of each tile's region
-    unsigned* front_cap;       // ntiles: slots of the front part (the back part is the rest of the region)
-    unsigned* seg_cnt[2];      // ntiles: records in the front part
-    unsigned* arr_cnt[2];      // ntiles: records appended to the back part
-    int4* ovf[2];              // records that found their tile's back part full, any tile, N slots
-    unsigned* tctl;            // [0..2] overflow counts (read step%3, append (step+1)%3, clear (step+2)%3); [3..4] scratch cursors by parity
-    unsigned char* tcls;       // ntiles x cls_stride: class bytes of each tile with its halo, row-major (T+2)^2, padded to 16
+    unsigned wait_polls;       // 0: copy waits are bounded by time (seconds); > 0: by this many polls (tests only)
+    int4* rec[2];              // records {x, y, t, id} of the environments that stayed; [step & 1] is current
+    uint2* reg;                // ntiles + 1: {start of the tile's region, its capacity}
+    unsigned* seg_cnt[2];      // ntiles: records in the region
+    unsigned* arr_cnt[2];      // ntiles: records in the arrival buffer
+    int4* arr[2];              // ntiles x ARR_CAP arrival slots
+    int4* ovf[2];              // records that found their tile's arrival buffer full, any tile, N slots
+    unsigned* tctl;            // [0..2] spill counts (read step%3, append (step+1)%3, clear (step+2)%3); [3..4] scratch cursors by parity
+    unsigned char* tcls;       // ntiles x cls_stride: class bytes of each tile with a one-cell halo, row-major (T+2)^2, padded to 16
     unsigned cls_stride;
+    float* bmax[2];            // ntiles x 4T: max_a Q of the cells just outside the tile's north / south / west / east edge; [step & 1] is current
     uint2* scratch;            // N x 8 bytes: 32-bit (cell, action) counters of tiles with more than 65,535 records
+    CUtensorMap tmq;           // the table as a 2-D tensor of floats (4W x H), box 4T x T: one copy instruction per tile
 };
 
 // ---- everything a kernel needs, passed by value ------------------------------------------------
@@ -73,7 +79,7 @@ struct Params {
     unsigned fallback_start;
     float lr, gamma;
     int legacy_clamp;
-    float4* Q;             // the current table: S float4, row s = the 4 action values of cell s (= tp.Qd[step & 1])
+    float4* Q;             // the table: S float4, row s = the 4 action values of cell s; every kernel updates it in place
     unsigned short* cw;    // S cell words (padded to 16 bytes)
     // environment state outside train steps: one int4 {x, y, t, id} per environment (all int32, one
     // coalesced 16-byte vector per thread), record k = environment k
@@ -116,8 +122,12 @@ int  tile_engine_configure(Params& p, int device);                  // opt in to
 void launch_tile_bucket(const Params& p, cudaStream_t st);         // p.st (any slot order) -> tile regions of parity p.step & 1
 void launch_tile_classes(const Params& p, cudaStream_t st);       // cell words -> per-tile class bytes (after any change of the grid)
 void launch_tile_export(const Params& p, cudaStream_t st);         // tile regions -> p.st in environment order
-void launch_tile_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c);
-void launch_q_average_dense(const Params& p, float4* table, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale, cudaStream_t st);
+void launch_tile_step(const Params& p, bool trace, cudaStream_t st);
+unsigned tile_cls_stride(unsigned tshift);                         // bytes of one tile's class block
+void launch_tile_border(const Params& p, cudaStream_t st);         // border array of parity p.step & 1 from the table (after any change of the table outside train steps)
+// Replica averaging, the slice this rank owns: table[cell0 + i] = (sum over ranks 0..R-1 in that order) / R, where rank `self`'s
+// rows are the table's own and the other ranks' rows lie in `others` (R - 1 slices of n rows, ascending rank).
+void launch_q_average_slice(float4* table, const float4* others, unsigned R, unsigned self, size_t cell0, size_t n, float scale, cudaStream_t st);
 void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st);
 
 }  // namespace cudarl

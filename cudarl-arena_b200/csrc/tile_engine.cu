@@ -1,24 +1,29 @@
-// tile_engine.cu -- the fused train step as a streaming pass over the grid, one tile at a time.
+// tile_engine.cu -- the fused train step as a streaming pass over the grid, one WARP per tile.
 //
 // With a quarter as many environments as cells, nearly every 128-byte line of the table is touched in
 // every step, so the step is organised around the TABLE, not around the environments:
 //
-//   * the grid is cut into T x T tiles; the environments are kept bucketed by tile (records {x,y,t,id});
-//   * a tile of Q_t plus a one-cell halo is brought into shared memory by bulk asynchronous copies, one
-//     per table row (the halo serves the max over Q_t[s'] of moves that leave the tile), together with the
-//     tile's cell classes and its records;
+//   * the grid is cut into T x T tiles (16 x 16 cells, or 8 x 8 on densely populated grids); the environments
+//     are kept bucketed by tile (records {x,y,t,id});
+//   * a warp owns a tile for the whole step and needs no block-wide barrier: it fetches the tile of Q_t with
+//     ONE tensor copy (cp.async.bulk.tensor, a T x T box of float4 out of the row-major table), plus the
+//     tile's class bytes and its border values, completion on the warp's own mbarrier; while the copies are
+//     in flight it already holds the tile's first records in registers and the next tile's header;
 //   * every environment of the tile is stepped against shared memory: epsilon-greedy from the Philox
 //     stream keyed by (seed, global env, step), move with obstacle / goal lookup, auto-reset;
 //   * the TD updates of a cell are applied from a histogram of (cell, action) counts: inside one step the
 //     target of an update depends on (cell, action) only, so n environments on one (cell, action) mean the
 //     same map applied n times -- the same bits as the oracle's sequential order, without sorting anything
 //     and without float atomics;
-//   * the tile of Q_{t+1} goes out to the OTHER dense table, one bulk copy per row (two dense tables
-//     alternate, so no block ever sees a neighbour's writes of the same step);
-//   * an environment that stays in the tile is appended to the front part of the tile's region of the
-//     other record array; one that leaves (a walk across the edge, a restart anywhere) is appended to
-//     the back part of its new tile's region with one atomic; a full back part spills to a global list
-//     that every block filters.  Regions are re-sized from the actual populations every few steps.
+//   * the table is updated IN PLACE: only the rows of occupied cells are stored (16 bytes each, straight from
+//     registers), and no other warp reads this tile's cells in this step.  The one thing a neighbour needs
+//     from a tile -- max_a Q of the cell just beyond the shared edge, for the TD target of a move across the
+//     edge -- travels through a border array: at the end of its step a tile stores the max of every cell of
+//     its border ring (taken from Q_{t+1}) into its four neighbours' slots of the OTHER parity;
+//   * an environment that stays in the tile is appended to the tile's region of the other record array
+//     (positions from a warp ballot, no atomics); one that leaves (a walk across the edge, a restart anywhere)
+//     is appended to its new tile's arrival buffer with one atomic; a full arrival buffer spills to a global
+//     list that every warp filters.  Regions are re-sized from the actual populations every few steps.
 //
 // Reference semantics (paths relative to the CudaRL-Arena project root):
 //   step        src/environment.cu:17-48, obstacle test src/kernels.cu:29-44, goal src/kernels.cu:56-59
@@ -27,13 +32,13 @@
 //   episode     src/train.py:191-222
 #include "kernels.cuh"
 #include "rules.cuh"
-#include <cooperative_groups.h>
-
-namespace cg = cooperative_groups;
 
 namespace cudarl {
 
 constexpr unsigned CROWDED_CELL = 24;   // a cell with more environments than this counts as "crowded" in the run statistics
+constexpr unsigned NMAX16 = 65535u;     // records of a tile the 16-bit counters can hold
+constexpr unsigned WPB = 4;             // warps per block; every warp works on its own
+constexpr unsigned PRE = 3;             // records per lane fetched before the warp waits for its copies
 
 __device__ __forceinline__ unsigned tile_of(const TileP& tp, int x, int y) {
     return ((unsigned)y >> tp.tshift) * tp.tiles_x + ((unsigned)x >> tp.tshift);
@@ -59,9 +64,10 @@ __device__ __forceinline__ unsigned block_scan_excl(unsigned v, unsigned* s_warp
     return r;
 }
 
-// ---- asynchronous bulk copies (global <-> shared, no registers, no per-element instructions) -------------
-// Every source / destination here is a row of float4 (or the tile's class bytes padded to 16): 16-byte
-// aligned on both sides, sizes multiples of 16.
+// ---- asynchronous copies into shared memory, completion on an mbarrier ----------------------------------
+// Tensor copy: the box starts at float column 4 * tx0 (a multiple of 4 floats = 16 bytes) and row ty0; cells
+// of the box that lie outside the table arrive as zeros.  Plain bulk copies: 16-byte aligned on both sides,
+// sizes multiples of 16.  No multicast anywhere.
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
@@ -80,25 +86,33 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, unsigned bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_commit_wait_read() {
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+__device__ __forceinline__ void tensor_g2s_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 :: "r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-constexpr unsigned WAIT_LIMIT = 1u << 22;    // polls of the copy barrier before the block gives up and flags an error
-
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
 }
-// Wait for the phase with the given parity; false if the poll limit ran out.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    for (unsigned it = 0; it < WAIT_LIMIT; ++it) if (mbar_try_wait(bar, parity)) return true;
-    return false;
+constexpr unsigned long long WAIT_NS = 2000000000ull;   // a copy that has not landed after two seconds never will
+
+// Wait for the phase with the given parity.  Bounded: by `polls` tries when polls > 0 (tests make the wait run
+// out that way), else by WAIT_NS of wall time.  false = gave up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, unsigned polls) {
+    if (polls) {
+        for (unsigned it = 0; it < polls; ++it) if (mbar_try_wait(bar, parity)) return true;
+        return false;
+    }
+    unsigned long long t0 = 0ull;
+    for (unsigned it = 1u;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 1023u) == 0u) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0ull) t0 = now; else if (now - t0 > WAIT_NS) return false;
+        }
+    }
 }
+
 // ------------------------------------------------------------------------------------------------
 // Why no ordering is needed.  The oracle applies the updates of one (cell, action) one after the other in
 // ascending environment id, each as  q <- fma(lr, target - q, q).  Inside one fused step the target of an
@@ -109,107 +123,51 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 // how many environments chose it -- a histogram in shared memory -- and then apply each map that many times.
 // (update_batch takes arbitrary caller transitions, so it keeps its ordered fold.)
 //
-// The step kernel is persistent: a block walks over tiles blockIdx, blockIdx + gridDim, ...  It has eight
-// CONSUMER warps, which do all the arithmetic on shared memory, and one PRODUCER warp (each lane issues the
-// copies of one or two table rows), which only moves data: while the consumers work on tile k in one stage of shared memory, the producer has
-// the bulk copies of tile k+1 in flight into the other stage and the rows of tile k-1 on their way out.
-//
-// Per stage:  s_q    HS*HS float4   Q_t of the tile and its halo; the consumers turn the interior into
-//                                   Q_{t+1} in place once every read of Q_t is done
-//             s_rec  RC    int4     the first records of the front part of the tile's region
-//             s_recb RCB   int4     the first records of the back part
-//             s_cls  HS*HS u8       cell classes of the tile and its halo
-// Consumer work space, shared by both stages:
-//             s_n    T*T   u64      per cell: how many environments chose action a, 16 bits per action
-//             s_list T*T   u16      occupied cells
-//             s_flag T*T/32 u32     one bit per cell: already listed
+// Shared memory of one warp (nothing is shared between warps):
+//   s_q    T*T  float4   Q_t of the tile, row-major inside the tile; never written by the warp
+//   s_n    T*T  u64      per cell: how many environments chose action a, 16 bits per action; zero between tiles
+//   s_halo 4T   float    max_a Q_t of the cells beyond the north / south / west / east edge (from the border array)
+//   s_bm   4T   float    max_a Q_{t+1} of the tile's own north / south / west / east border cells, on their way out
+//   s_cls  (T+2)^2 u8    cell classes of the tile and a one-cell halo
+//   s_list T*T  u16      occupied cells
 // A tile with more than 65,535 records counts in 32-bit counters in global scratch instead.
-// full[stage] : the producer's copies have landed (transaction barrier);  done[stage] : every consumer thread
-// has finished the tile in that stage.
-constexpr unsigned NSTAGE = 2;           // shared-memory stages per block: tiles loaded ahead of the consumers
-constexpr unsigned CONSUMERS = 256;      // consumer threads per block (+ 32 of the producer warp)
-// Records staged in shared memory (front part, back part of the region); the rest is read from global memory.
-__host__ __device__ constexpr unsigned rc_front(unsigned ct) { return ct + ct / 4u + 32u; }
-__host__ __device__ constexpr unsigned rc_back(unsigned ct) { return ct / 4u + 32u; }
-constexpr unsigned NMAX16 = 65535u;  // records of a tile the 16-bit counters can hold
-
-struct TileHdr {                     // what the producer tells the consumers about the tile in a stage
-    unsigned tile, roff, fcap, n_front, n_in, n_all, nf_s, nb_s;
-    int tx0, ty0;
+template <unsigned TSH> struct WarpSmem {
+    static constexpr unsigned T = 1u << TSH, T2 = T * T, HS = T + 2u;
+    static constexpr unsigned CLS = (HS * HS + 15u) / 16u * 16u;
+    static constexpr unsigned OFF_N = T2 * 16u, OFF_HALO = OFF_N + T2 * 8u, OFF_BM = OFF_HALO + 4u * T * 4u,
+                              OFF_CLS = OFF_BM + 4u * T * 4u, OFF_LIST = OFF_CLS + CLS;
+    static constexpr unsigned BYTES = (OFF_LIST + T2 * 2u + 127u) / 128u * 128u;
+    static constexpr unsigned TX_BYTES = T2 * 16u + CLS + 4u * T * 4u;      // what the three copies of a tile deliver
 };
-
-template <unsigned CT> __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" :: "n"(CT) : "memory"); }
 
 // Everything the per-environment step needs about the tile being processed.
 struct StepCtx {
-    const float4* s_q; const unsigned char* s_cls;
-    int tx0, ty0; unsigned tile, roff, fcap;
+    const float4* s_q; const unsigned char* s_cls; const float* s_halo;
+    int tx0, ty0; unsigned tile;
     float eps; unsigned long long g;
-    int4* out; int4* ovf_out; unsigned* arr_next; unsigned* ovf_cnt_next;
-    unsigned* s_stay; unsigned* s_goals; unsigned* s_timeouts;
 };
 
-// One environment, one step: epsilon-greedy action, move, episode bookkeeping; writes the record of the next
-// step to the region of the tile it will stand on.  Returns the cell (tile-local) and the action.
-// false: the record does not lie in this tile (never seen; flagged by the caller).
-template <bool TRACE, unsigned TSH>
-__device__ __forceinline__ bool step_env(const Params& p, const StepCtx& c, const int4 rec, unsigned& ic, unsigned& act) {
-    constexpr unsigned T = 1u << TSH, HS = T + 2u;
-    const TileP& tp = p.tp;
-    const int x = rec.x, y = rec.y, t = rec.z; const unsigned e = (unsigned)rec.w;
-    const unsigned lx = (unsigned)(x - c.tx0), ly = (unsigned)(y - c.ty0);
-    if (lx >= T || ly >= T) return false;
-    ic = (ly << TSH) + lx;
-    const unsigned hh = (ly + 1u) * HS + lx + 1u;
-    const U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)c.g, (unsigned)(c.g >> 32), p.k0, p.k1 ^ TAG_POLICY);
-    const int a = (u01(w.x) < c.eps) ? (int)(w.y & 3u) : argmax4(c.s_q[hh]);
-    act = (unsigned)a;
-    const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
-    int nx = x + dx, ny = y + dy;
-    const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
-    const unsigned ht = (unsigned)((int)hh + dy * (int)HS + dx);          // inside the halo whenever the move is in bounds
-    const bool moved = inb && !(c.s_cls[inb ? ht : hh] & CW_OBST);
-    nx = moved ? nx : x; ny = moved ? ny : y;
-    const bool done = (c.s_cls[moved ? ht : hh] & CW_GOAL) != 0;
-    if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = done ? 1.0f : -0.01f; p.tr_d[e] = done ? 1 : 0; }
-    // episode bookkeeping and the record of the next step
-    const bool timeout = !done && p.max_steps > 0 && t + 1 >= p.max_steps;
-    int nt = t + 1;
-    if (done || timeout) {
-        const unsigned sn = sample_start(p, p.env_offset + e, c.g + 1ull, TAG_START);
-        nx = (int)(sn % (unsigned)p.W); ny = (int)(sn / (unsigned)p.W); nt = 0;
-        atomicAdd(done ? c.s_goals : c.s_timeouts, 1u);
-    }
-    const int4 nrec = make_int4(nx, ny, nt, (int)e);
-    const unsigned dt = ((unsigned)ny >> TSH) * tp.tiles_x + ((unsigned)nx >> TSH);
-    bool placed = false;
-    if (dt == c.tile) {
-        cg::coalesced_group cgp = cg::coalesced_threads();
-        unsigned pos = 0;
-        if (cgp.thread_rank() == 0) pos = atomicAdd(c.s_stay, cgp.size());
-        pos = cgp.shfl(pos, 0) + cgp.thread_rank();
-        if (pos < c.fcap) { c.out[c.roff + pos] = nrec; placed = true; }
-    }
-    if (!placed) {
-        const unsigned doff = tp.reg_off[dt], dfc = tp.front_cap[dt], dbc = tp.reg_off[dt + 1u] - doff - dfc;
-        const unsigned pos = atomicAdd(&c.arr_next[dt], 1u);
-        if (pos < dbc) c.out[doff + dfc + pos] = nrec;
-        else {
-            const unsigned q = atomicAdd(c.ovf_cnt_next, 1u);
-            if (q < p.N) c.ovf_out[q] = nrec; else atomicOr(&p.ctl->error, ERR_BAD_STATE);
-        }
-    }
-    return true;
+// max_a Q_t of the cell reached from tile-local (lx, ly) by (dx, dy): from the tile, or from the border
+// values when the move crosses an edge.
+template <unsigned TSH>
+__device__ __forceinline__ float next_max(const StepCtx& c, unsigned lx, unsigned ly, int dx, int dy) {
+    constexpr unsigned T = 1u << TSH;
+    const int mx = (int)lx + dx, my = (int)ly + dy;
+    if (my < 0) return c.s_halo[lx];
+    if (my >= (int)T) return c.s_halo[T + lx];
+    if (mx < 0) return c.s_halo[2u * T + ly];
+    if (mx >= (int)T) return c.s_halo[3u * T + ly];
+    return max4(c.s_q[((unsigned)my << TSH) + (unsigned)mx]);
 }
 
-// Q_{t+1} row of one cell from Q_t (still intact in s_q) and the number of environments that chose each action
+// Q_{t+1} row of one cell from Q_t and the number of environments that chose each action
 // (`w`: 16 bits per action, or `n32` when the tile counts in 32 bits).  Only the actions that were chosen are visited.
 template <unsigned TSH>
 __device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c, unsigned ic, unsigned long long w, const unsigned* n32) {
     constexpr unsigned T = 1u << TSH, HS = T + 2u;
     const unsigned lx = ic & (T - 1u), ly = ic >> TSH, hh = (ly + 1u) * HS + lx + 1u;
     const int x = c.tx0 + (int)lx, y = c.ty0 + (int)ly;
-    float4 row = c.s_q[hh];
+    float4 row = c.s_q[ic];
     unsigned mask = n32 ? ((n32[0] != 0u) | ((n32[1] != 0u) << 1) | ((n32[2] != 0u) << 2) | ((n32[3] != 0u) << 3))
                         : (((w & 0xFFFFull) != 0ull) | (((w >> 16) & 0xFFFFull) != 0ull) << 1 | (((w >> 32) & 0xFFFFull) != 0ull) << 2 | ((w >> 48) != 0ull) << 3);
     while (mask) {
@@ -220,10 +178,9 @@ __device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c,
         const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
         const unsigned ht = (unsigned)((int)hh + dy * (int)HS + dx);
         const bool moved = inb && !(c.s_cls[inb ? ht : hh] & CW_OBST);
-        const unsigned h2 = moved ? ht : hh;
-        const bool done = (c.s_cls[h2] & CW_GOAL) != 0;
+        const bool done = (c.s_cls[moved ? ht : hh] & CW_GOAL) != 0;
         float m = 0.0f;
-        if (!done) { m = max4(c.s_q[h2]); if (p.legacy_clamp && m < 0.0f) m = 0.0f; }
+        if (!done) { m = moved ? next_max<TSH>(c, lx, ly, dx, dy) : max4(c.s_q[ic]); if (p.legacy_clamp && m < 0.0f) m = 0.0f; }
         const float d = __fmaf_rn(p.gamma, m, done ? 1.0f : -0.01f);     // the TD target of (cell, a), from Q_t
         float v = pick(row, a);
         for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(d, v), v);       // one application per environment
@@ -232,212 +189,246 @@ __device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c,
     return row;
 }
 
-template <bool TRACE, unsigned TSH, unsigned CT>
-__global__ void __launch_bounds__(CT + 32u, 3) k_tile_step(Params p) {
-    constexpr unsigned T = 1u << TSH, HS = T + 2u, T2 = T * T, HS2 = HS * HS;
-    constexpr unsigned RC = rc_front(CT), RCB = rc_back(CT);
-    constexpr unsigned CPT = (T2 + CT - 1u) / CT;              // cells per consumer thread when every cell is occupied
+template <bool TRACE, unsigned TSH, unsigned MINB>
+__global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_constant__ Params p) {
+    using L = WarpSmem<TSH>;
+    constexpr unsigned T = L::T, T2 = L::T2, HS = L::HS;
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_full[NSTAGE], s_done[NSTAGE];
-    __shared__ TileHdr s_hdr[NSTAGE];
-    __shared__ unsigned s_stay, s_nocc, s_base, s_abort;
-    __shared__ unsigned s_goals, s_timeouts, s_conf, s_nbig, s_nbigent, s_bad;     // accumulated over the block's tiles
+    __shared__ __align__(8) unsigned long long s_bar[WPB];
+    __shared__ unsigned s_acc[6];            // goals, timeouts, conflicts, crowded cells, environments on them, bad records
 
     const TileP& tp = p.tp;
-    const unsigned stage_bytes = HS2 * 16u + RC * 16u + RCB * 16u + tp.cls_stride;
-    unsigned long long* s_n = reinterpret_cast<unsigned long long*>(smem + NSTAGE * stage_bytes);
-    unsigned short* s_list = reinterpret_cast<unsigned short*>(s_n + T2);
-    unsigned* s_flag = reinterpret_cast<unsigned*>(s_list + T2);       // one bit per cell: listed
+    const unsigned lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const unsigned lt = (1u << lane) - 1u;
+    unsigned char* wb = smem + warp * L::BYTES;
+    float4* s_q = reinterpret_cast<float4*>(wb);
+    unsigned long long* s_n = reinterpret_cast<unsigned long long*>(wb + L::OFF_N);
+    float* s_halo = reinterpret_cast<float*>(wb + L::OFF_HALO);
+    float* s_bm = reinterpret_cast<float*>(wb + L::OFF_BM);
+    unsigned char* s_cls = wb + L::OFF_CLS;
+    unsigned short* s_list = reinterpret_cast<unsigned short*>(wb + L::OFF_LIST);
+    unsigned long long* bar = &s_bar[warp];
 
-    const unsigned tid = threadIdx.x, lane = tid & 31u;
     const unsigned long long g = p.step;
     const unsigned par = (unsigned)(g & 1ull);
-    const float4* __restrict__ Qin = tp.Qd[par];
-    float4* __restrict__ Qout = tp.Qd[par ^ 1u];
     const int4* __restrict__ in = tp.rec[par];
+    const int4* __restrict__ arr_in = tp.arr[par];
     const int4* __restrict__ ovf_in = tp.ovf[par];
-    const unsigned ntl = blockIdx.x < tp.ntiles ? (tp.ntiles - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;   // tiles of this block
+    int4* __restrict__ out = tp.rec[par ^ 1u];
+    int4* __restrict__ arr_out = tp.arr[par ^ 1u];
+    int4* __restrict__ ovf_out = tp.ovf[par ^ 1u];
+    unsigned* __restrict__ arr_next = tp.arr_cnt[par ^ 1u];
+    unsigned* ovf_cnt_next = tp.tctl + (unsigned)((g + 1ull) % 3ull);
+    const float* __restrict__ halo_in = tp.bmax[par];
+    float* __restrict__ halo_out = tp.bmax[par ^ 1u];
+    const unsigned gw = blockIdx.x * WPB + warp, nw = gridDim.x * WPB;
 
-    if (tid == 0) {
-        s_goals = 0; s_timeouts = 0; s_conf = 0; s_nbig = 0; s_nbigent = 0; s_bad = 0; s_abort = 0;
-        for (unsigned q = 0; q < NSTAGE; ++q) { mbar_init(&s_full[q], 1u); mbar_init(&s_done[q], CT); }
-        if (blockIdx.x == 0) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
-    }
+    if (threadIdx.x < 6u) s_acc[threadIdx.x] = 0u;
+    if (lane == 0) mbar_init(bar, 1u);
+    for (unsigned q = lane; q < T2; q += 32u) s_n[q] = 0ull;
+    if (gw == 0u && lane == 0u) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
     __syncthreads();
 
-    if (tid >= CT) {
-        // =========================== producer warp: moves all the data ===================================
-        // Lane r issues the bulk copies of rows r and r + 32, so a tile's copies are issued in a few instructions
-        // per lane; the region header of the tile to load next is fetched BEFORE waiting for the consumers, so its
-        // round trip to global memory is off the path.
-        const unsigned n_spill = min(tp.tctl[(unsigned)(g % 3ull)], p.N);
-        struct Raw { unsigned roff, fcap, rend, seg, arr; };
-        auto fetch_hdr = [&](unsigned k) -> Raw {
-            Raw r{0u, 0u, 0u, 0u, 0u};
-            if (k < ntl) {
-                const unsigned tile = blockIdx.x + k * gridDim.x;
-                r.roff = tp.reg_off[tile]; r.fcap = tp.front_cap[tile]; r.rend = tp.reg_off[tile + 1u];
-                r.seg = tp.seg_cnt[par][tile]; r.arr = tp.arr_cnt[par][tile];
-            }
-            return r;
-        };
-        auto load_tile = [&](unsigned k, const Raw& raw) {    // header + bulk copies of the block's k-th tile into stage k % NSTAGE
-            const unsigned b = k % NSTAGE, tile = blockIdx.x + k * gridDim.x;
-            unsigned char* st = smem + b * stage_bytes;
-            float4* s_q = reinterpret_cast<float4*>(st);
-            int4* s_rec = reinterpret_cast<int4*>(st + HS2 * 16u);
-            int4* s_recb = s_rec + RC;
-            unsigned char* s_cls = reinterpret_cast<unsigned char*>(s_recb + RCB);
-            const int tx0 = (int)((tile % tp.tiles_x) << TSH), ty0 = (int)((tile / tp.tiles_x) << TSH);
-            const unsigned roff = raw.roff, fcap = raw.fcap, bcap = raw.rend - roff - fcap;
-            const unsigned n_front = min(raw.seg, fcap), n_back = min(raw.arr, bcap);
-            const unsigned nf_s = min(n_front, RC), nb_s = min(n_back, RCB);
-            const int xs = max(tx0 - 1, 0), xe = min(tx0 + (int)T, p.W - 1);
-            const int gy_lo = max(ty0 - 1, 0), gy_hi = min(ty0 + (int)T, p.H - 1);
-            const unsigned bytes_h = (unsigned)(xe - xs + 1) * 16u;
-            if (lane == 0) {
-                TileHdr& h = s_hdr[b];
-                h.tile = tile; h.roff = roff; h.fcap = fcap; h.n_front = n_front; h.n_in = n_front + n_back; h.n_all = n_front + n_back + n_spill;
-                h.nf_s = nf_s; h.nb_s = nb_s; h.tx0 = tx0; h.ty0 = ty0;
-                mbar_arrive_expect_tx(&s_full[b], (unsigned)(gy_hi - gy_lo + 1) * bytes_h + tp.cls_stride + (nf_s + nb_s) * 16u);
-                if (nf_s) bulk_g2s(s_rec, in + roff, nf_s * 16u, &s_full[b]);
-            }
-            if (lane == 1 && nb_s) bulk_g2s(s_recb, in + roff + fcap, nb_s * 16u, &s_full[b]);
-            if (lane == 2) bulk_g2s(s_cls, tp.tcls + (size_t)tile * tp.cls_stride, tp.cls_stride, &s_full[b]);
-            for (int gy = gy_lo + (int)lane; gy <= gy_hi; gy += 32)
-                bulk_g2s(s_q + (unsigned)(gy - (ty0 - 1)) * HS + (unsigned)(xs - (tx0 - 1)), Qin + (size_t)gy * (size_t)p.W + (size_t)xs, bytes_h, &s_full[b]);
-        };
-        for (unsigned q = 0; q < NSTAGE; ++q) if (ntl > q) load_tile(q, fetch_hdr(q));
-        for (unsigned k = 0; k < ntl; ++k) {
-            const unsigned b = k % NSTAGE;
-            const Raw nxt = fetch_hdr(k + NSTAGE);             // in flight while this warp waits
-            // one lane polls; the others park at the warp barrier instead of spinning
-            if (lane == 0 && !mbar_wait(&s_done[b], (k / NSTAGE) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
-            __syncwarp();
-            if (*(volatile unsigned*)&s_abort) break;
-            // rows of Q_{t+1} out (the consumers fenced their writes towards the async proxy before arriving)
-            const unsigned tile = blockIdx.x + k * gridDim.x;
-            const int tx0 = (int)((tile % tp.tiles_x) << TSH), ty0 = (int)((tile / tp.tiles_x) << TSH);
-            const unsigned wi = (unsigned)min((int)T, p.W - tx0), ri = (unsigned)min((int)T, p.H - ty0);
-            const float4* s_q = reinterpret_cast<const float4*>(smem + b * stage_bytes);
-            for (unsigned r = lane; r < ri; r += 32u)
-                bulk_s2g(Qout + (size_t)(ty0 + (int)r) * (size_t)p.W + (size_t)tx0, s_q + (r + 1u) * HS + 1u, wi * 16u);
-            bulk_commit_wait_read();                            // the stage may be overwritten once its rows have been read
-            __syncwarp();
-            if (k + NSTAGE < ntl) load_tile(k + NSTAGE, nxt);
-        }
-        return;
-    }
-
-    // ================================= consumers ======================================================
     StepCtx c;
-    c.eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx]; c.g = g;
-    c.out = tp.rec[par ^ 1u]; c.ovf_out = tp.ovf[par ^ 1u]; c.arr_next = tp.arr_cnt[par ^ 1u];
-    c.ovf_cnt_next = tp.tctl + (unsigned)((g + 1ull) % 3ull);
-    c.s_stay = &s_stay; c.s_goals = &s_goals; c.s_timeouts = &s_timeouts;
-    unsigned conf = 0;
-    for (unsigned k = 0; k < ntl; ++k) {
-        const unsigned b = k % NSTAGE;
-        unsigned char* st = smem + b * stage_bytes;
-        float4* s_q = reinterpret_cast<float4*>(st);
-        const int4* s_rec = reinterpret_cast<const int4*>(st + HS2 * 16u);
-        const int4* s_recb = s_rec + RC;
-        c.s_q = s_q; c.s_cls = reinterpret_cast<const unsigned char*>(s_recb + RCB);
+    c.s_q = s_q; c.s_cls = s_cls; c.s_halo = s_halo; c.g = g;
+    c.eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx];
+    const unsigned n_spill = min(tp.tctl[(unsigned)(g % 3ull)], p.N);
+    unsigned goals = 0, timeouts = 0, conf = 0, nbig = 0, nbigent = 0, bad = 0, phase = 0;
 
-        if (tid == 0) { s_stay = 0; s_nocc = 0; s_base = 0xFFFFFFFFu; }
-        for (unsigned q = 2u * tid; q < T2; q += 2u * CT) *reinterpret_cast<uint4*>(s_n + q) = make_uint4(0u, 0u, 0u, 0u);
-        for (unsigned q = tid; q < (T2 + 31u) / 32u; q += CT) s_flag[q] = 0u;
-        // one thread waits for the copies; the barrier below passes the news (and the data) on to the others
-        if (tid == 0 && !mbar_wait(&s_full[b], (k / NSTAGE) & 1u)) { atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT); s_abort = 1u; }
-        cons_sync<CT>();
-        if (s_abort) break;                                    // never seen; the producer gives up at its next wait
-        const TileHdr h = s_hdr[b];
-        const unsigned tile = h.tile, roff = h.roff, fcap = h.fcap, n_front = h.n_front, n_in = h.n_in, n_all = h.n_all, nf_s = h.nf_s, nb_s = h.nb_s;
-        c.tx0 = h.tx0; c.ty0 = h.ty0; c.tile = tile; c.roff = roff; c.fcap = fcap;
-        const bool crowded = n_all > NMAX16;                        // block-uniform
-        unsigned* gcnt = nullptr;
-        if (crowded) {                                               // 4 x 32-bit counters per cell in global scratch
-            if (tid == 0) {
-                const unsigned need = T2 * 2u, q = atomicAdd(&tp.tctl[3u + par], need);
-                if (q + need <= p.N) s_base = q; else { s_base = 0xFFFFFFFEu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
-            }
-            cons_sync<CT>();
-            if (s_base != 0xFFFFFFFEu) gcnt = reinterpret_cast<unsigned*>(tp.scratch + s_base);
-            if (gcnt) for (unsigned q = tid; q < T2 * 4u; q += CT) gcnt[q] = 0u;
-            cons_sync<CT>();
+    // Header of a tile: lanes 0..3 each load one word {region start, capacity, records in the region, arrivals};
+    // the words are only exchanged when the tile comes up, so the loads are off the path.
+    auto fetch_hdr = [&](unsigned tile) -> unsigned {
+        if (tile >= tp.ntiles || lane >= 4u) return 0u;
+        const unsigned* src = lane == 0u ? &tp.reg[tile].x : lane == 1u ? &tp.reg[tile].y : lane == 2u ? &tp.seg_cnt[par][tile] : &tp.arr_cnt[par][tile];
+        return *src;
+    };
+    unsigned hw = fetch_hdr(gw);
+
+    for (unsigned tile = gw; tile < tp.ntiles; tile += nw) {
+        const unsigned roff = __shfl_sync(FULL, hw, 0), fcap = __shfl_sync(FULL, hw, 1);
+        const unsigned n_front = min(__shfl_sync(FULL, hw, 2), fcap), n_in = n_front + min(__shfl_sync(FULL, hw, 3), ARR_CAP);
+        const unsigned n_all = n_in + n_spill;
+        const unsigned tyi = tile / tp.tiles_x, txi = tile - tyi * tp.tiles_x;
+        const int tx0 = (int)(txi << TSH), ty0 = (int)(tyi << TSH);
+        c.tx0 = tx0; c.ty0 = ty0; c.tile = tile;
+
+        // ---- the tile's copies: table box, class bytes, border values -------------------------------------
+        if (lane == 0u) mbar_arrive_expect_tx(bar, L::TX_BYTES);
+        __syncwarp();
+        if (lane == 0u) tensor_g2s_2d(s_q, &tp.tmq, tx0 * 4, ty0, bar);
+        else if (lane == 1u) bulk_g2s(s_cls, tp.tcls + (size_t)tile * L::CLS, L::CLS, bar);
+        else if (lane == 2u) bulk_g2s(s_halo, halo_in + (size_t)tile * (4u * T), 4u * T * 4u, bar);
+
+        // record j of this tile's input: its region, then its arrival buffer (the spill list is filtered in the loop)
+        auto load_rec = [&](unsigned j) -> int4 { return j < n_front ? in[roff + j] : arr_in[(size_t)tile * ARR_CAP + (j - n_front)]; };
+        int4 pre[PRE];
+#pragma unroll
+        for (unsigned q = 0; q < PRE; ++q) { const unsigned j = q * 32u + lane; pre[q] = j < n_in ? load_rec(j) : make_int4(0, 0, 0, 0); }
+        hw = fetch_hdr(tile + nw);                              // in flight while this tile is worked on
+
+        if (!__all_sync(FULL, mbar_wait(bar, phase, tp.wait_polls))) {
+            // Never seen with the time bound.  Flag it, let the copies land (they target this warp's shared memory), stop.
+            if (lane == 0u) atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT);
+            mbar_wait(bar, phase, 0u);
+            break;
         }
+        phase ^= 1u;
 
-        // record j of this tile's input (front part, back part, then the spill list filtered by tile)
-        auto fetch = [&](unsigned j, int4& r) -> bool {
-            if (j < n_front) { r = j < nf_s ? s_rec[j] : in[roff + j]; return true; }
-            if (j < n_in) { const unsigned q = j - n_front; r = q < nb_s ? s_recb[q] : in[roff + fcap + q]; return true; }
-            r = ovf_in[j - n_in];
-            return tile_of(tp, r.x, r.y) == tile;
-        };
+        const bool crowded = n_all > NMAX16;                    // warp-uniform
+        unsigned* gcnt = nullptr;
+        if (crowded) {                                           // 4 x 32-bit counters per cell in global scratch
+            unsigned q = 0;
+            if (lane == 0u) {
+                q = atomicAdd(&tp.tctl[3u + par], T2 * 2u);
+                if (q + T2 * 2u > p.N) { q = 0xFFFFFFFFu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
+            }
+            q = __shfl_sync(FULL, q, 0);
+            if (q != 0xFFFFFFFFu) {
+                gcnt = reinterpret_cast<unsigned*>(tp.scratch + q);
+                for (unsigned k = lane; k < T2 * 4u; k += 32u) gcnt[k] = 0u;
+            }
+            __syncwarp();
+        }
 
         // ---- the step: every environment acts, moves and counts itself in its cell's histogram ----------
-        for (unsigned j = tid; j < n_all; j += CT) {
-            int4 rec; unsigned ic, a;
-            if (!fetch(j, rec)) continue;
-            if (!step_env<TRACE, TSH>(p, c, rec, ic, a)) { s_bad = 1u; continue; }
-            if (!crowded) {
-                // 32-bit shared-memory atomics are native; the 64-bit word of a cell is counted in its two halves
-                const unsigned old = atomicAdd(reinterpret_cast<unsigned*>(s_n) + 2u * ic + (a >> 1), 1u << (16u * (a & 1u)));
-                if (old == 0u) {                                                           // first on this half: maybe first on the cell
-                    const unsigned bit = 1u << (ic & 31u);
-                    if (!(atomicOr(&s_flag[ic >> 5], bit) & bit)) s_list[atomicAdd(&s_nocc, 1u)] = (unsigned short)ic;
+        unsigned nstay = 0;
+        for (unsigned it = 0; it * 32u < n_all; ++it) {
+            const unsigned j = it * 32u + lane;
+            bool act = j < n_all;
+            int4 rec = it == 0u ? pre[0] : it == 1u ? pre[1] : pre[2];
+            if (act && j >= n_in) { rec = ovf_in[j - n_in]; act = tile_of(tp, rec.x, rec.y) == tile; }
+            else if (act && it >= PRE) rec = load_rec(j);
+            const unsigned e = (unsigned)rec.w;
+            const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
+            if (act && (lx >= T || ly >= T)) { bad = 1u; act = false; }        // never seen: the record does not lie in this tile
+            int4 nrec = make_int4(0, 0, 0, 0); unsigned dt = 0xFFFFFFFFu;
+            if (act) {
+                const unsigned ic = (ly << TSH) + lx, hh = (ly + 1u) * HS + lx + 1u;
+                const U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
+                const int a = (u01(w.x) < c.eps) ? (int)(w.y & 3u) : argmax4(s_q[ic]);
+                const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
+                int nx = rec.x + dx, ny = rec.y + dy;
+                const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
+                const unsigned ht = (unsigned)((int)hh + dy * (int)HS + dx);      // inside the halo whenever the move is in bounds
+                const bool moved = inb && !(s_cls[inb ? ht : hh] & CW_OBST);
+                nx = moved ? nx : rec.x; ny = moved ? ny : rec.y;
+                const bool done = (s_cls[moved ? ht : hh] & CW_GOAL) != 0;
+                if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = done ? 1.0f : -0.01f; p.tr_d[e] = done ? 1 : 0; }
+                // the histogram: 32-bit shared-memory atomics are native; the 64-bit word of a cell is counted in its two halves
+                if (!crowded) atomicAdd(reinterpret_cast<unsigned*>(s_n) + 2u * ic + ((unsigned)a >> 1), 1u << (16u * ((unsigned)a & 1u)));
+                else if (gcnt) atomicAdd(&gcnt[ic * 4u + (unsigned)a], 1u);
+                // episode bookkeeping and the record of the next step
+                const bool timeout = !done && p.max_steps > 0 && rec.z + 1 >= p.max_steps;
+                int nt = rec.z + 1;
+                if (done || timeout) {
+                    const unsigned sn = sample_start(p, p.env_offset + e, g + 1ull, TAG_START);
+                    nx = (int)(sn % (unsigned)p.W); ny = (int)(sn / (unsigned)p.W); nt = 0;
+                    if (done) ++goals; else ++timeouts;
                 }
-            } else if (gcnt) atomicAdd(&gcnt[ic * 4u + a], 1u);
+                nrec = make_int4(nx, ny, nt, (int)e);
+                dt = ((unsigned)ny >> TSH) * tp.tiles_x + ((unsigned)nx >> TSH);
+            }
+            // stays: position in the tile's own region from a ballot; leaves (or no room): one atomic on the new tile's arrival buffer
+            const bool stay = act && dt == tile;
+            const unsigned sm = __ballot_sync(FULL, stay);
+            const unsigned pos = nstay + __popc(sm & lt);
+            nstay += __popc(sm);
+            if (stay && pos < fcap) out[roff + pos] = nrec;
+            else if (act) {
+                const unsigned apos = atomicAdd(&arr_next[dt], 1u);
+                if (apos < ARR_CAP) arr_out[(size_t)dt * ARR_CAP + apos] = nrec;
+                else {
+                    const unsigned q = atomicAdd(ovf_cnt_next, 1u);
+                    if (q < p.N) ovf_out[q] = nrec; else bad = 1u;
+                }
+            }
         }
-        cons_sync<CT>();
-        if (tid == 0) {
-            tp.seg_cnt[par ^ 1u][tile] = min(s_stay, fcap);
+        if (lane == 0u) {
+            tp.seg_cnt[par ^ 1u][tile] = min(nstay, fcap);
             tp.arr_cnt[par][tile] = 0u;                                   // consumed; it is the append counter again in the next step
         }
+        __syncwarp();
 
-        // ---- Q_{t+1} of the occupied cells: computed from Q_t into registers, written after everybody has read ---
-        float4 nrow[CPT]; unsigned nh[CPT];
-        const unsigned nocc = crowded ? T2 : s_nocc;
+        // ---- the occupied cells, compacted; the border ring starts out as max Q_t ----------------------------
+        unsigned nocc = 0;
+        if (!crowded) {
 #pragma unroll
-        for (unsigned q = 0; q < CPT; ++q) {
-            const unsigned idx = tid + q * CT;
-            nh[q] = 0xFFFFFFFFu;
-            if (idx >= nocc) continue;
+            for (unsigned k = 0; k < T2 / 32u; ++k) {
+                const unsigned ic = k * 32u + lane;
+                const bool nz = s_n[ic] != 0ull;
+                const unsigned m = __ballot_sync(FULL, nz);
+                if (nz) s_list[nocc + __popc(m & lt)] = (unsigned short)ic;
+                nocc += __popc(m);
+            }
+        } else nocc = gcnt ? T2 : 0u;
+        for (unsigned k = lane; k < 4u * T; k += 32u) {
+            const unsigned e = k >> TSH, i = k & (T - 1u);
+            const unsigned ic = e == 0u ? i : e == 1u ? ((T - 1u) << TSH) + i : e == 2u ? (i << TSH) : (i << TSH) + T - 1u;
+            s_bm[k] = max4(s_q[ic]);
+        }
+        __syncwarp();
+
+        // ---- Q_{t+1} of the occupied cells, from Q_t in shared memory straight into the table -----------------
+        for (unsigned idx = lane; idx < nocc; idx += 32u) {
             unsigned ic, tot; unsigned long long w = 0ull; unsigned n32[4];
             if (!crowded) {
                 ic = s_list[idx];
-                w = s_n[ic];
+                w = s_n[ic]; s_n[ic] = 0ull;
                 tot = ((unsigned)w & 0xFFFFu) + ((unsigned)(w >> 16) & 0xFFFFu) + ((unsigned)(w >> 32) & 0xFFFFu) + (unsigned)(w >> 48);
             } else {
                 ic = idx;
-                if (!gcnt) continue;
                 const uint4 v = *reinterpret_cast<const uint4*>(gcnt + 4u * ic);
                 n32[0] = v.x; n32[1] = v.y; n32[2] = v.z; n32[3] = v.w;
                 tot = v.x + v.y + v.z + v.w;
             }
             if (!tot) continue;
             if (tot > 1u) conf += tot;
-            if (tot > CROWDED_CELL) { atomicAdd(&s_nbig, 1u); atomicAdd(&s_nbigent, tot); }
-            nrow[q] = updated_row<TSH>(p, c, ic, w, crowded ? n32 : nullptr);
-            nh[q] = ((ic >> TSH) + 1u) * HS + (ic & (T - 1u)) + 1u;
+            if (tot > CROWDED_CELL) { ++nbig; nbigent += tot; }
+            const float4 row = updated_row<TSH>(p, c, ic, w, crowded ? n32 : nullptr);
+            const unsigned lx = ic & (T - 1u), ly = ic >> TSH;
+            p.Q[(size_t)(ty0 + (int)ly) * (size_t)p.W + (size_t)(tx0 + (int)lx)] = row;
+            const float mx = max4(row);
+            if (ly == 0u) s_bm[lx] = mx;
+            if (ly == T - 1u) s_bm[T + lx] = mx;
+            if (lx == 0u) s_bm[2u * T + ly] = mx;
+            if (lx == T - 1u) s_bm[3u * T + ly] = mx;
         }
-        cons_sync<CT>();
-#pragma unroll
-        for (unsigned q = 0; q < CPT; ++q) if (nh[q] != 0xFFFFFFFFu) s_q[nh[q]] = nrow[q];
-        // hand the stage to the producer: rows written through the generic proxy, read by the bulk copy
-        fence_async_smem();
-        mbar_arrive(&s_done[b]);
+        __syncwarp();
+
+        // ---- border values out: my north row is the south halo of the tile above, and so on ----------------
+        for (unsigned k = lane; k < 4u * T; k += 32u) {
+            const unsigned e = k >> TSH, i = k & (T - 1u);
+            bool there; unsigned nt, slot;
+            if (e == 0u)      { there = tyi > 0u;               nt = tile - tp.tiles_x; slot = 1u; }
+            else if (e == 1u) { there = tyi + 1u < tp.tiles_y;  nt = tile + tp.tiles_x; slot = 0u; }
+            else if (e == 2u) { there = txi > 0u;               nt = tile - 1u;         slot = 3u; }
+            else              { there = txi + 1u < tp.tiles_x;  nt = tile + 1u;         slot = 2u; }
+            if (there) halo_out[((size_t)nt * 4u + slot) * T + i] = s_bm[k];
+        }
+        fence_async_smem();                                      // this lane's reads of the tile come before the next copies' writes
+        __syncwarp();                                            // every lane is done with the tile before the next copies are issued
     }
-    for (int o = 16; o; o >>= 1) conf += __shfl_xor_sync(FULL, conf, o);
-    if (lane == 0u && conf) atomicAdd(&s_conf, conf);
-    cons_sync<CT>();
-    if (tid == 0) {
-        if (s_conf) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_conf);
-        if (s_goals) atomicAdd(&p.ctl->goals, (unsigned long long)s_goals);
-        if (s_timeouts) atomicAdd(&p.ctl->timeouts, (unsigned long long)s_timeouts);
-        if (s_goals + s_timeouts) atomicAdd(&p.ctl->episodes, (unsigned long long)(s_goals + s_timeouts));
-        if (s_nbig) { atomicAdd(&p.ctl->long_chains, (unsigned long long)s_nbig); atomicAdd(&p.ctl->general, (unsigned long long)s_nbigent); }
-        if (s_bad) atomicOr(&p.ctl->error, ERR_BAD_STATE);
+
+    // ---- run statistics: warp -> block -> one atomic per counter and block ----------------------------------
+    for (int o = 16; o; o >>= 1) {
+        goals += __shfl_xor_sync(FULL, goals, o); timeouts += __shfl_xor_sync(FULL, timeouts, o); conf += __shfl_xor_sync(FULL, conf, o);
+        nbig += __shfl_xor_sync(FULL, nbig, o); nbigent += __shfl_xor_sync(FULL, nbigent, o); bad |= __shfl_xor_sync(FULL, bad, o);
+    }
+    if (lane == 0u) {
+        if (goals) atomicAdd(&s_acc[0], goals);
+        if (timeouts) atomicAdd(&s_acc[1], timeouts);
+        if (conf) atomicAdd(&s_acc[2], conf);
+        if (nbig) { atomicAdd(&s_acc[3], nbig); atomicAdd(&s_acc[4], nbigent); }
+        if (bad) atomicOr(&s_acc[5], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (s_acc[2]) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_acc[2]);
+        if (s_acc[0]) atomicAdd(&p.ctl->goals, (unsigned long long)s_acc[0]);
+        if (s_acc[1]) atomicAdd(&p.ctl->timeouts, (unsigned long long)s_acc[1]);
+        if (s_acc[0] + s_acc[1]) atomicAdd(&p.ctl->episodes, (unsigned long long)(s_acc[0] + s_acc[1]));
+        if (s_acc[3]) { atomicAdd(&p.ctl->long_chains, (unsigned long long)s_acc[3]); atomicAdd(&p.ctl->general, (unsigned long long)s_acc[4]); }
+        if (s_acc[5]) atomicOr(&p.ctl->error, ERR_BAD_STATE);
     }
 }
 
@@ -459,7 +450,7 @@ __global__ void k_te_count(Params p) {
     const int4 r = p.st[i];
     atomicAdd(&p.tp.seg_cnt[p.step & 1ull][tile_of(p.tp, r.x, r.y)], 1u);
 }
-// One block: region sizes (front = population + 25 % + 32, back = 25 % + 64), their exclusive scan, counters reset.
+// One block: region capacities (population + 25 % + 32), their exclusive scan, counters reset.
 __global__ void __launch_bounds__(1024) k_te_layout(Params p) {
     __shared__ unsigned s_warp[33];
     __shared__ unsigned s_carry;
@@ -470,19 +461,19 @@ __global__ void __launch_bounds__(1024) k_te_layout(Params p) {
     for (unsigned base = 0; base < tp.ntiles; base += 1024u) {
         const unsigned k = base + threadIdx.x;
         const unsigned cnt = k < tp.ntiles ? tp.seg_cnt[par][k] : 0u;
-        const unsigned F = cnt + cnt / 4u + 32u, B = cnt / 4u + 64u;
+        const unsigned F = cnt + cnt / 4u + 32u;
         unsigned total = 0;
-        const unsigned ex = block_scan_excl(k < tp.ntiles ? F + B : 0u, s_warp, &total);
+        const unsigned ex = block_scan_excl(k < tp.ntiles ? F : 0u, s_warp, &total);
         const unsigned carry = s_carry;
         if (k < tp.ntiles) {
-            tp.reg_off[k] = carry + ex; tp.front_cap[k] = F;
+            tp.reg[k] = make_uint2(carry + ex, F);
             tp.seg_cnt[par][k] = 0u; tp.seg_cnt[par ^ 1u][k] = 0u; tp.arr_cnt[0][k] = 0u; tp.arr_cnt[1][k] = 0u;
         }
         __syncthreads();
         if (threadIdx.x == 0) s_carry = carry + total;
         __syncthreads();
     }
-    if (threadIdx.x == 0) { tp.reg_off[tp.ntiles] = s_carry; for (int k = 0; k < 5; ++k) tp.tctl[k] = 0u; }
+    if (threadIdx.x == 0) { tp.reg[tp.ntiles] = make_uint2(s_carry, 0u); for (int k = 0; k < 5; ++k) tp.tctl[k] = 0u; }
 }
 __global__ void k_te_scatter(Params p) {
     const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -492,7 +483,7 @@ __global__ void k_te_scatter(Params p) {
     const int4 r = p.st[i];
     const unsigned tile = tile_of(tp, r.x, r.y);
     const unsigned pos = atomicAdd(&tp.seg_cnt[par][tile], 1u);
-    tp.rec[par][tp.reg_off[tile] + pos] = r;
+    tp.rec[par][tp.reg[tile].x + pos] = r;
 }
 // The class bytes (obstacle / goal bits) of every tile with its halo, laid out as the step kernel copies them.
 __global__ void __launch_bounds__(BLOCK) k_te_cls(Params p) {
@@ -507,15 +498,35 @@ __global__ void __launch_bounds__(BLOCK) k_te_cls(Params p) {
         tp.tcls[(size_t)tile * tp.cls_stride + k] = (unsigned char)cls;
     }
 }
+// The border array of the current parity from the table: for every tile the max over actions of the cells just
+// outside its four edges (0 where the grid ends).  Needed whenever the table was changed by anything but a train step.
+__global__ void __launch_bounds__(BLOCK) k_te_border(Params p) {
+    const TileP& tp = p.tp;
+    const unsigned T = tp.T, per = 4u * T;
+    const size_t total = (size_t)tp.ntiles * per;
+    float* dst = tp.bmax[p.step & 1ull];
+    for (size_t k = (size_t)blockIdx.x * BLOCK + threadIdx.x; k < total; k += (size_t)gridDim.x * BLOCK) {
+        const unsigned tile = (unsigned)(k / per), r = (unsigned)(k - (size_t)tile * per), e = r >> tp.tshift, i = r & (T - 1u);
+        const int tx0 = (int)((tile % tp.tiles_x) << tp.tshift), ty0 = (int)((tile / tp.tiles_x) << tp.tshift);
+        const int x = e == 2u ? tx0 - 1 : e == 3u ? tx0 + (int)T : tx0 + (int)i;
+        const int y = e == 0u ? ty0 - 1 : e == 1u ? ty0 + (int)T : ty0 + (int)i;
+        float m = 0.0f;
+        if (x >= 0 && x < p.W && y >= 0 && y < p.H) m = max4(p.Q[(size_t)y * (size_t)p.W + (size_t)x]);
+        dst[k] = m;
+    }
+}
 // Back to environment order: st[id] = record.
 __global__ void __launch_bounds__(BLOCK) k_te_export(Params p) {
     const TileP& tp = p.tp;
-    const unsigned par = (unsigned)(p.step & 1ull), tile = blockIdx.x;
-    const unsigned roff = tp.reg_off[tile], fcap = tp.front_cap[tile], bcap = tp.reg_off[tile + 1u] - roff - fcap;
-    const unsigned n_front = min(tp.seg_cnt[par][tile], fcap), n_back = min(tp.arr_cnt[par][tile], bcap);
-    const int4* in = tp.rec[par];
-    for (unsigned j = threadIdx.x; j < n_front; j += BLOCK) { const int4 r = in[roff + j]; if ((unsigned)r.w < p.N) p.st[r.w] = r; }
-    for (unsigned j = threadIdx.x; j < n_back; j += BLOCK) { const int4 r = in[roff + fcap + j]; if ((unsigned)r.w < p.N) p.st[r.w] = r; }
+    const unsigned par = (unsigned)(p.step & 1ull);
+    for (unsigned tile = blockIdx.x; tile < tp.ntiles; tile += gridDim.x) {
+        const uint2 rg = tp.reg[tile];
+        const unsigned n_front = min(tp.seg_cnt[par][tile], rg.y), n_arr = min(tp.arr_cnt[par][tile], ARR_CAP);
+        const int4* in = tp.rec[par] + rg.x;
+        const int4* ain = tp.arr[par] + (size_t)tile * ARR_CAP;
+        for (unsigned j = threadIdx.x; j < n_front; j += BLOCK) { const int4 r = in[j]; if ((unsigned)r.w < p.N) p.st[r.w] = r; }
+        for (unsigned j = threadIdx.x; j < n_arr; j += BLOCK) { const int4 r = ain[j]; if ((unsigned)r.w < p.N) p.st[r.w] = r; }
+    }
 }
 __global__ void k_te_export_ovf(Params p) {
     const TileP& tp = p.tp;
@@ -524,34 +535,39 @@ __global__ void k_te_export_ovf(Params p) {
     for (unsigned j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x) { const int4 r = in[j]; if ((unsigned)r.w < p.N) p.st[r.w] = r; }
 }
 
-// Replica averaging on a dense table: rows [cell0, cell0+n) of every rank, rank after rank, summed in rank
-// order 0..R-1 in fp32 (the order of the CPU oracle), scaled by 1/R.
-__global__ void k_q_average_dense(float4* table, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale) {
-    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float4 acc = gathered[i];
-    for (unsigned r = 1; r < R; ++r) {
-        const float4 v = gathered[(size_t)r * n + i];
-        acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+// Replica averaging, the slice this rank owns.  The other ranks' rows of the slice lie in `others`, R - 1 blocks of
+// n rows in ascending rank order; this rank's own rows are the table's.  Summed in rank order 0..R-1 in fp32 (the
+// order of the CPU oracle), scaled by 1/R, written back into the table.
+__global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const float4* others, unsigned R, unsigned self, size_t cell0, size_t n, float scale) {
+    for (size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (size_t)gridDim.x * BLOCK) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (unsigned r = 0; r < R; ++r) {
+            const float4 v = r == self ? table[cell0 + i] : others[(size_t)(r - (r > self ? 1u : 0u)) * n + i];
+            if (r == 0u) acc = v;
+            else { acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w); }
+        }
+        acc.x = __fmul_rn(acc.x, scale); acc.y = __fmul_rn(acc.y, scale); acc.z = __fmul_rn(acc.z, scale); acc.w = __fmul_rn(acc.w, scale);
+        table[cell0 + i] = acc;
     }
-    acc.x = __fmul_rn(acc.x, scale); acc.y = __fmul_rn(acc.y, scale); acc.z = __fmul_rn(acc.z, scale); acc.w = __fmul_rn(acc.w, scale);
-    table[cell0 + i] = acc;
 }
 
 // ------------------------------------------------------------------------------------------------
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
+static inline unsigned capped_blocks(size_t n) { const size_t b = (n + BLOCK - 1) / BLOCK; return (unsigned)(b < 1 ? 1 : (b > 2368 ? 2368 : b)); }
 
-static size_t work_bytes(size_t T2) { return (T2 * 8 + T2 * 2 + (T2 + 31) / 32 * 4 + 15) / 16 * 16; }
-size_t tile_step_smem(const Params& p) {
-    const size_t T = p.tp.T, HS = T + 2;
-    const size_t stage = HS * HS * 16 + (size_t)rc_front(CONSUMERS) * 16 + (size_t)rc_back(CONSUMERS) * 16 + p.tp.cls_stride;
-    return NSTAGE * stage + work_bytes(T * T);
-}
-template <unsigned TSH>
+constexpr unsigned MINB16 = 6, MINB8 = 6;     // resident blocks per SM the register budget is cut for
+size_t tile_step_smem(const Params& p) { return (size_t)WPB * (p.tp.tshift == 4u ? WarpSmem<4>::BYTES : WarpSmem<3>::BYTES); }
+unsigned tile_cls_stride(unsigned tshift) { return tshift == 4u ? WarpSmem<4>::CLS : WarpSmem<3>::CLS; }
+
+template <unsigned TSH, unsigned MINB>
 static cudaError_t configure_one(int bytes, int* per_sm) {
-    cudaError_t e = cudaFuncSetAttribute(k_tile_step<false, TSH, CONSUMERS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_tile_step<true, TSH, CONSUMERS>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH, CONSUMERS>, (int)(CONSUMERS + 32u), (size_t)bytes);
+    cudaError_t e = cudaSuccess;
+    const void* fns[2] = {(const void*)k_tile_step<false, TSH, MINB>, (const void*)k_tile_step<true, TSH, MINB>};
+    for (const void* f : fns) {
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    }
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH, MINB>, (int)(WPB * 32u), (size_t)bytes);
     return e;
 }
 int tile_engine_configure(Params& p, int device) {
@@ -560,9 +576,8 @@ int tile_engine_configure(Params& p, int device) {
     cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     if (e != cudaSuccess) return (int)e;
     switch (p.tp.tshift) {
-        case 3: e = configure_one<3>(bytes, &per_sm); break;
-        case 4: e = configure_one<4>(bytes, &per_sm); break;
-        case 5: e = configure_one<5>(bytes, &per_sm); break;
+        case 3: e = configure_one<3, MINB8>(bytes, &per_sm); break;
+        case 4: e = configure_one<4, MINB16>(bytes, &per_sm); break;
         default: return (int)cudaErrorInvalidValue;
     }
     if (e != cudaSuccess) return (int)e;
@@ -577,32 +592,26 @@ void launch_tile_bucket(const Params& p, cudaStream_t st) {
     if (p.N) k_te_scatter<<<nblk(p.N), BLOCK, 0, st>>>(p);
 }
 void launch_tile_classes(const Params& p, cudaStream_t st) { k_te_cls<<<p.tp.ntiles, BLOCK, 0, st>>>(p); }
+void launch_tile_border(const Params& p, cudaStream_t st) { k_te_border<<<capped_blocks((size_t)p.tp.ntiles * 4u * p.tp.T), BLOCK, 0, st>>>(p); }
 void launch_tile_export(const Params& p, cudaStream_t st) {
-    k_te_export<<<p.tp.ntiles, BLOCK, 0, st>>>(p);
+    k_te_export<<<p.tp.ntiles < 4736u ? p.tp.ntiles : 4736u, BLOCK, 0, st>>>(p);
     k_te_export_ovf<<<64, BLOCK, 0, st>>>(p);
 }
-static unsigned tile_step_grid(const Params& p) { return p.tp.ntiles < p.tp.grid ? p.tp.ntiles : p.tp.grid; }
-template <unsigned TSH>
+static unsigned tile_step_grid(const Params& p) { const unsigned need = (p.tp.ntiles + WPB - 1u) / WPB; return need < p.tp.grid ? need : p.tp.grid; }
+template <unsigned TSH, unsigned MINB>
 static void launch_step_one(const Params& p, bool trace, unsigned grid, size_t smem, cudaStream_t st) {
-    if (trace) k_tile_step<true, TSH, CONSUMERS><<<grid, CONSUMERS + 32u, smem, st>>>(p);
-    else       k_tile_step<false, TSH, CONSUMERS><<<grid, CONSUMERS + 32u, smem, st>>>(p);
+    if (trace) k_tile_step<true, TSH, MINB><<<grid, WPB * 32u, smem, st>>>(p);
+    else       k_tile_step<false, TSH, MINB><<<grid, WPB * 32u, smem, st>>>(p);
 }
-void launch_tile_step(const Params& p, bool trace, cudaStream_t st, cudaEvent_t ev_a, cudaEvent_t ev_b, cudaEvent_t ev_c) {
+void launch_tile_step(const Params& p, bool trace, cudaStream_t st) {
     const size_t smem = tile_step_smem(p);
     const unsigned grid = tile_step_grid(p);
-    if (ev_a) cudaEventRecord(ev_a, st);
-    switch (p.tp.tshift) {
-        case 3: launch_step_one<3>(p, trace, grid, smem, st); break;
-        case 4: launch_step_one<4>(p, trace, grid, smem, st); break;
-        default: launch_step_one<5>(p, trace, grid, smem, st); break;
-    }
-    if (ev_b) cudaEventRecord(ev_b, st);
+    if (p.tp.tshift == 3u) launch_step_one<3, MINB8>(p, trace, grid, smem, st);
+    else                   launch_step_one<4, MINB16>(p, trace, grid, smem, st);
     if (p.eps_from_ctl) k_tile_eps_episode<<<1, 1, 0, st>>>(p);
-    if (ev_c) cudaEventRecord(ev_c, st);
 }
-void launch_q_average_dense(const Params& p, float4* table, const float4* gathered, unsigned R, unsigned cell0, unsigned n, float scale, cudaStream_t st) {
-    (void)p;
-    if (n) k_q_average_dense<<<nblk(n), BLOCK, 0, st>>>(table, gathered, R, cell0, n, scale);
+void launch_q_average_slice(float4* table, const float4* others, unsigned R, unsigned self, size_t cell0, size_t n, float scale, cudaStream_t st) {
+    if (n) k_q_average_slice<<<capped_blocks(n), BLOCK, 0, st>>>(table, others, R, self, cell0, n, scale);
 }
 
 }  // namespace cudarl

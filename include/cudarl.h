@@ -11,8 +11,10 @@
  * (paths relative to that project's root).
  *
  * Return value of every `int` function: 0 = ok, <0 = bad argument / bad state,
- * >0 = CUDA (1000+cudaError) or NCCL (2000+ncclResult) failure.  A text for the
- * last failure is kept per context (cudarl_last_error) and per thread for
+ * >0 = CUDA (1000+cudaError) or NCCL (2000+ncclResult) failure, or CUDARL_ERR_DEVICE + bits when a
+ * kernel of this library recorded an internal failure (see CUDARL_DEVERR_*; reported by the next call
+ * that waits for the device: cudarl_synchronize, cudarl_get_stats, cudarl_get_q, cudarl_get_state).
+ * A text for the last failure is kept per context (cudarl_last_error) and per thread for
  * failures of cudarl_create (cudarl_last_global_error).
  *
  * Threading: one context is single-threaded; different contexts may be used
@@ -49,6 +51,13 @@ enum { CUDARL_QINIT_ZERO = 0,           /* src/q_learning.cu:13 */
 
 #define CUDARL_MAX_GOALS 64
 
+/* Failures recorded by kernels (sticky bits, also in cudarl_stats.device_error). */
+#define CUDARL_ERR_DEVICE 3000
+enum { CUDARL_DEVERR_SCRATCH_OVERFLOW = 1, /* a work area was too small for the step */
+       CUDARL_DEVERR_BAD_STATE = 2,        /* a record outside its tile or outside the grid */
+       CUDARL_DEVERR_CHAIN_CYCLE = 8,      /* update_batch: a collision chain longer than the batch */
+       CUDARL_DEVERR_COPY_TIMEOUT = 32 };  /* train step: a tile copy did not land within its wait bound */
+
 typedef struct cudarl_config {
     uint32_t struct_size;   /* = sizeof(cudarl_config); checked */
     int32_t  device;        /* CUDA device ordinal */
@@ -73,7 +82,11 @@ typedef struct cudarl_config {
     float    q_init_scale;
     int32_t  legacy_clamp;  /* 1: max_next = max(0, max_a' Q) as in src/kernels.cu:102-110 */
     int32_t  sync_every;    /* average the replicas every this many train steps; 0 = never */
-    int32_t  reserved[4];   /* reserved[0]: re-size the per-tile record regions every this many train steps (0 = default 128, <0 = only when training starts; results never depend on it) */
+    int32_t  rebucket_every;/* re-size the per-tile record regions every this many train steps (0 = default 128, <0 = only when
+                               training starts); results never depend on it */
+    int32_t  tile_edge;     /* tile edge of the train step in cells: 0 = chosen from the population density, or 8 / 16;
+                               results never depend on it */
+    int32_t  reserved[2];
 } cudarl_config;
 
 typedef struct cudarl_stats {
@@ -134,8 +147,13 @@ int cudarl_train_steps(cudarl_ctx* ctx, int64_t n);
 /* Same, epsilon for each of the n steps read from a caller array in host memory (pinned or not);
  * this is the form whose inputs arrive from the host every call. */
 int cudarl_train_steps_eps(cudarl_ctx* ctx, int64_t n, const float* eps_host);
-/* Wait for everything enqueued on the context's stream. */
+/* Wait for everything enqueued on the context's stream; reports a failure recorded by a kernel. */
 int cudarl_synchronize(cudarl_ctx* ctx);
+/* Test hook, no counterpart in the reference: bound the train step's wait for a tile copy by `polls` tries
+ * of the barrier instead of by time (0 = back to the time bound of two seconds).  With a bound of a few polls
+ * the wait runs out before the copy lands: the warp records CUDARL_DEVERR_COPY_TIMEOUT, lets its copies
+ * land, and leaves -- the path a copy that never arrives would take, exercised without any fault. */
+int cudarl_debug_set_copy_wait_polls(cudarl_ctx* ctx, int32_t polls);
 
 /* When on, cudarl_train_steps records the action, reward and done flag of the LAST step of each
  * call for every environment (the per-step data the reference loop sees at src/train.py:200-201). */
@@ -205,11 +223,11 @@ int cudarl_average_replicas(cudarl_ctx* ctx);
 /* Timing helpers for benchmarks: record events on the context's stream. */
 int cudarl_timer_start(cudarl_ctx* ctx);
 int cudarl_timer_stop_ms(cudarl_ctx* ctx, float* ms); /* synchronises */
-/* When enabled, every train step is bracketed by events: main_ms = time in the step kernel (k_tile_step),
- * fix_ms = time in whatever follows it inside the step (the per-episode epsilon kernel, else nothing),
- * launches = steps measured.  Used for the roofline figure. */
+/* When enabled, every uninterrupted run of step-kernel launches (k_tile_step, back to back; a run ends where the
+ * record regions are re-sized, the replicas are averaged or the call returns) is bracketed by ONE pair of events:
+ * step_ms = summed time of those runs, launches = step kernels inside them.  Used for the roofline figure. */
 int cudarl_kernel_timing(cudarl_ctx* ctx, int on);
-int cudarl_kernel_time_ms(cudarl_ctx* ctx, float* main_ms, float* fix_ms, int64_t* launches);
+int cudarl_kernel_time_ms(cudarl_ctx* ctx, float* step_ms, int64_t* launches);
 
 const char* cudarl_version(void);
 

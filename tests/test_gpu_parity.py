@@ -322,7 +322,7 @@ def test_region_resizing_never_changes_results(pkg, orc):
     want_state, want_q = ref.get_state(), ref.get_q()
     for period in (1, 3, 8, 50, -1):
         cfg = base.copy()
-        cfg.reserved[0] = period
+        cfg.rebucket_every = period
         g = pkg.VecGridWorld(cfg)
         for n in (1, 9, 60):
             g.train_steps(n)
