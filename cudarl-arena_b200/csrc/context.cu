@@ -347,12 +347,12 @@ int alloc_tiles(cudarl_ctx* c) {
         CK(cudaMemsetAsync(c->dbmax[k], 0, nt * 4 * tp.T * sizeof(float), c->st));
         tp.rec[k] = (int4*)c->drec[k]; tp.arr[k] = (int4*)c->darr[k]; tp.ovf[k] = (int4*)c->dovf[k]; tp.bmax[k] = (float*)c->dbmax[k];
     }
-    const size_t meta = 2 * (nt + 1) + 4 * nt + 8;
+    const size_t meta = 2 * (nt + 1) + 4 * nt + 8;          // reg (uint2 x (nt+1)), cnt[2] (uint2 x nt each), tctl
     CK(cudaMalloc(&c->dtmeta, meta * sizeof(unsigned)));
     CK(cudaMemsetAsync(c->dtmeta, 0, meta * sizeof(unsigned), c->st));
     unsigned* m = (unsigned*)c->dtmeta;
     tp.reg = (uint2*)m; m += 2 * (nt + 1);
-    tp.seg_cnt[0] = m; m += nt; tp.seg_cnt[1] = m; m += nt; tp.arr_cnt[0] = m; m += nt; tp.arr_cnt[1] = m; m += nt;
+    tp.cnt[0] = (uint2*)m; m += 2 * nt; tp.cnt[1] = (uint2*)m; m += 2 * nt;
     tp.tctl = m;
     tp.cls_stride = tile_cls_stride(tsh);
     CK(cudaMalloc(&c->dtcls, nt * tp.cls_stride));

@@ -54,12 +54,11 @@ struct TileP {
     unsigned wait_polls;       // 0: copy waits are bounded by time (seconds); > 0: by this many polls (tests only)
     int4* rec[2];              // records {x, y, t, id} of the environments that stayed; [step & 1] is current
     uint2* reg;                // ntiles + 1: {start of the tile's region, its capacity}
-    unsigned* seg_cnt[2];      // ntiles: records in the region
-    unsigned* arr_cnt[2];      // ntiles: records in the arrival buffer
+    uint2* cnt[2];             // ntiles: {records in the region, records in the arrival buffer}
     int4* arr[2];              // ntiles x ARR_CAP arrival slots
     int4* ovf[2];              // records that found their tile's arrival buffer full, any tile, N slots
     unsigned* tctl;            // [0..2] spill counts (read step%3, append (step+1)%3, clear (step+2)%3); [3..4] scratch cursors by parity
-    unsigned char* tcls;       // ntiles x cls_stride: class bytes of each tile with a one-cell halo, row-major (T+2)^2, padded to 16
+    unsigned char* tcls;       // ntiles x cls_stride: one move byte per cell, tile by tile (which of the four moves are blocked / end on a goal)
     unsigned cls_stride;
     float* bmax[2];            // ntiles x 4T: max_a Q of the cells just outside the tile's north / south / west / east edge; [step & 1] is current
     uint2* scratch;            // N x 8 bytes: 32-bit (cell, action) counters of tiles with more than 65,535 records

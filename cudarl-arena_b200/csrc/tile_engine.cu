@@ -38,6 +38,7 @@ namespace cudarl {
 constexpr unsigned CROWDED_CELL = 24;   // a cell with more environments than this counts as "crowded" in the run statistics
 constexpr unsigned NMAX16 = 65535u;     // records of a tile the 16-bit counters can hold
 constexpr unsigned WPB = 4;             // warps per block; every warp works on its own
+constexpr unsigned NST = 1;             // copy stages per warp: 2 = the next tile's copies fly while this tile is worked on
 constexpr unsigned PRE = 3;             // records per lane fetched before the warp waits for its copies
 
 __device__ __forceinline__ unsigned tile_of(const TileP& tp, int x, int y) {
@@ -76,10 +77,18 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned coun
 __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+// One look at the barrier, no waiting.
+__device__ __forceinline__ bool mbar_test_wait(unsigned long long* bar, unsigned parity) {
     unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0u;
+}
+// Sleeps in hardware until the phase completes or about `ns` nanoseconds have passed: a waiting warp issues nothing.
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity, unsigned ns) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
     return ok != 0u;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
@@ -90,6 +99,15 @@ __device__ __forceinline__ void tensor_g2s_2d(void* dst, const CUtensorMap* map,
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  :: "r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
+// Shared memory through 32-bit shared-space addresses: the hot loops index a warp's arrays with plain integer arithmetic.
+__device__ __forceinline__ float4 lds_f4(unsigned a) { float4 v; asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ float lds_f32(unsigned a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ unsigned lds_u8(unsigned a) { unsigned v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ unsigned lds_u16(unsigned a) { unsigned v; asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ uint2 lds_u32x2(unsigned a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ void sts_f32(unsigned a, float v) { asm volatile("st.shared.f32 [%0], %1;" :: "r"(a), "f"(v) : "memory"); }
+__device__ __forceinline__ void sts_zero8(unsigned a) { asm volatile("st.shared.v2.u32 [%0], {%1, %1};" :: "r"(a), "r"(0u) : "memory"); }
+__device__ __forceinline__ unsigned atoms_add(unsigned a, unsigned v) { unsigned o; asm volatile("atom.shared.add.u32 %0, [%1], %2;" : "=r"(o) : "r"(a), "r"(v) : "memory"); return o; }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
@@ -100,13 +118,13 @@ constexpr unsigned long long WAIT_NS = 2000000000ull;   // a copy that has not l
 // out that way), else by WAIT_NS of wall time.  false = gave up.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, unsigned polls) {
     if (polls) {
-        for (unsigned it = 0; it < polls; ++it) if (mbar_try_wait(bar, parity)) return true;
+        for (unsigned it = 0; it < polls; ++it) if (mbar_test_wait(bar, parity)) return true;
         return false;
     }
     unsigned long long t0 = 0ull;
     for (unsigned it = 1u;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 0u) {
+        if (mbar_try_wait(bar, parity, 20000u)) return true;
+        if ((it & 15u) == 0u) {
             const unsigned long long now = global_ns();
             if (t0 == 0ull) t0 = now; else if (now - t0 > WAIT_NS) return false;
         }
@@ -123,65 +141,66 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 // how many environments chose it -- a histogram in shared memory -- and then apply each map that many times.
 // (update_batch takes arbitrary caller transitions, so it keeps its ordered fold.)
 //
-// Shared memory of one warp (nothing is shared between warps):
-//   s_q    T*T  float4   Q_t of the tile, row-major inside the tile; never written by the warp
-//   s_n    T*T  u64      per cell: how many environments chose action a, 16 bits per action; zero between tiles
+// Shared memory of one warp (nothing is shared between warps).  Two STAGES, so that the copies of the next tile are
+// in flight while the warp works on this one:
+//   s_q    T*T  float4   Q_t of the tile, row-major inside the tile
+//   s_mv   T*T  u8       per cell: bit a = a move in direction a is blocked (grid edge or obstacle), bit 4+a = the
+//                        cell an environment stands on after choosing a (the next cell, or its own when blocked) is a goal
 //   s_halo 4T   float    max_a Q_t of the cells beyond the north / south / west / east edge (from the border array)
-//   s_bm   4T   float    max_a Q_{t+1} of the tile's own north / south / west / east border cells, on their way out
-//   s_cls  (T+2)^2 u8    cell classes of the tile and a one-cell halo
-//   s_list T*T  u16      occupied cells
+// and one work area:
+//   s_n    T*T  u64      per cell: how many environments chose action a, 16 bits per action; zero between tiles
+//   s_bm   4T   float    max_a Q_{t+1} of the tile's own north / south / west / east border cells (general path only)
+//   s_list               general path: T*T u16, the occupied cells; fast path: up to 32 records that leave the tile
 // A tile with more than 65,535 records counts in 32-bit counters in global scratch instead.
 template <unsigned TSH> struct WarpSmem {
-    static constexpr unsigned T = 1u << TSH, T2 = T * T, HS = T + 2u;
-    static constexpr unsigned CLS = (HS * HS + 15u) / 16u * 16u;
-    static constexpr unsigned OFF_N = T2 * 16u, OFF_HALO = OFF_N + T2 * 8u, OFF_BM = OFF_HALO + 4u * T * 4u,
-                              OFF_CLS = OFF_BM + 4u * T * 4u, OFF_LIST = OFF_CLS + CLS;
-    static constexpr unsigned BYTES = (OFF_LIST + T2 * 2u + 127u) / 128u * 128u;
+    static constexpr unsigned T = 1u << TSH, T2 = T * T;
+    static constexpr unsigned CLS = T2;                              // a multiple of 16 for T = 8 and 16
+    static constexpr unsigned ST_MV = T2 * 16u, ST_HALO = ST_MV + CLS, STAGE = (ST_HALO + 4u * T * 4u + 127u) / 128u * 128u;
+    static constexpr unsigned OFF_N = NST * STAGE, OFF_BM = OFF_N + T2 * 8u, OFF_LIST = OFF_BM + 4u * T * 4u;
+    static constexpr unsigned LIST_BYTES = T2 * 2u > 512u ? T2 * 2u : 512u;
+    static constexpr unsigned BYTES = (OFF_LIST + LIST_BYTES + 127u) / 128u * 128u;
     static constexpr unsigned TX_BYTES = T2 * 16u + CLS + 4u * T * 4u;      // what the three copies of a tile deliver
 };
 
 // Everything the per-environment step needs about the tile being processed.
 struct StepCtx {
-    const float4* s_q; const unsigned char* s_cls; const float* s_halo;
-    int tx0, ty0; unsigned tile;
-    float eps; unsigned long long g;
+    const float4* s_q; const unsigned char* s_mv; const float* s_halo;
+    float eps; int tmax;
+    unsigned eps_thr;      // explore iff (w0 >> 8) < eps_thr: the same test as (w0 >> 8) * 2^-24 < eps, in integers
 };
 
-// max_a Q_t of the cell reached from tile-local (lx, ly) by (dx, dy): from the tile, or from the border
-// values when the move crosses an edge.
+// TD target of (cell, action) from Q_t:  r + gamma * max_a' Q_t[s'],  0 for the max when the episode ends there.
+// The next cell's max comes from the tile, or from the border values when the move crosses an edge.
 template <unsigned TSH>
-__device__ __forceinline__ float next_max(const StepCtx& c, unsigned lx, unsigned ly, int dx, int dy) {
+__device__ __forceinline__ float td_target(const Params& p, const StepCtx& c, unsigned ic, int a, unsigned mvb) {
     constexpr unsigned T = 1u << TSH;
-    const int mx = (int)lx + dx, my = (int)ly + dy;
-    if (my < 0) return c.s_halo[lx];
-    if (my >= (int)T) return c.s_halo[T + lx];
-    if (mx < 0) return c.s_halo[2u * T + ly];
-    if (mx >= (int)T) return c.s_halo[3u * T + ly];
-    return max4(c.s_q[((unsigned)my << TSH) + (unsigned)mx]);
+    const bool blocked = (mvb >> a) & 1u, done = (mvb >> (4 + a)) & 1u;
+    float m = 0.0f;
+    if (!done) {
+        if (blocked) m = max4(c.s_q[ic]);
+        else {
+            const unsigned lx = ic & (T - 1u), ly = ic >> TSH;
+            const int mx = (int)lx + (a == 1) - (a == 3), my = (int)ly + (a == 2) - (a == 0);
+            if ((unsigned)mx < T && (unsigned)my < T) m = max4(c.s_q[((unsigned)my << TSH) + (unsigned)mx]);
+            else m = c.s_halo[my < 0 ? lx : my >= (int)T ? T + lx : mx < 0 ? 2u * T + ly : 3u * T + ly];
+        }
+        if (p.legacy_clamp && m < 0.0f) m = 0.0f;
+    }
+    return __fmaf_rn(p.gamma, m, done ? 1.0f : -0.01f);
 }
 
 // Q_{t+1} row of one cell from Q_t and the number of environments that chose each action
 // (`w`: 16 bits per action, or `n32` when the tile counts in 32 bits).  Only the actions that were chosen are visited.
 template <unsigned TSH>
 __device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c, unsigned ic, unsigned long long w, const unsigned* n32) {
-    constexpr unsigned T = 1u << TSH, HS = T + 2u;
-    const unsigned lx = ic & (T - 1u), ly = ic >> TSH, hh = (ly + 1u) * HS + lx + 1u;
-    const int x = c.tx0 + (int)lx, y = c.ty0 + (int)ly;
     float4 row = c.s_q[ic];
+    const unsigned mvb = c.s_mv[ic];
     unsigned mask = n32 ? ((n32[0] != 0u) | ((n32[1] != 0u) << 1) | ((n32[2] != 0u) << 2) | ((n32[3] != 0u) << 3))
                         : (((w & 0xFFFFull) != 0ull) | (((w >> 16) & 0xFFFFull) != 0ull) << 1 | (((w >> 32) & 0xFFFFull) != 0ull) << 2 | ((w >> 48) != 0ull) << 3);
     while (mask) {
         const int a = __ffs((int)mask) - 1; mask &= mask - 1u;
         const unsigned n = n32 ? n32[a] : (unsigned)(w >> (16 * a)) & 0xFFFFu;
-        const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
-        const int nx = x + dx, ny = y + dy;
-        const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
-        const unsigned ht = (unsigned)((int)hh + dy * (int)HS + dx);
-        const bool moved = inb && !(c.s_cls[inb ? ht : hh] & CW_OBST);
-        const bool done = (c.s_cls[moved ? ht : hh] & CW_GOAL) != 0;
-        float m = 0.0f;
-        if (!done) { m = moved ? next_max<TSH>(c, lx, ly, dx, dy) : max4(c.s_q[ic]); if (p.legacy_clamp && m < 0.0f) m = 0.0f; }
-        const float d = __fmaf_rn(p.gamma, m, done ? 1.0f : -0.01f);     // the TD target of (cell, a), from Q_t
+        const float d = td_target<TSH>(p, c, ic, a, mvb);
         float v = pick(row, a);
         for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(d, v), v);       // one application per environment
         row.x = a == 0 ? v : row.x; row.y = a == 1 ? v : row.y; row.z = a == 2 ? v : row.z; row.w = a == 3 ? v : row.w;
@@ -192,22 +211,19 @@ __device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c,
 template <bool TRACE, unsigned TSH, unsigned MINB>
 __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_constant__ Params p) {
     using L = WarpSmem<TSH>;
-    constexpr unsigned T = L::T, T2 = L::T2, HS = L::HS;
+    constexpr unsigned T = L::T, T2 = L::T2;
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_bar[WPB];
+    __shared__ __align__(8) unsigned long long s_bar[WPB][2];
     __shared__ unsigned s_acc[6];            // goals, timeouts, conflicts, crowded cells, environments on them, bad records
 
     const TileP& tp = p.tp;
     const unsigned lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const unsigned lt = (1u << lane) - 1u;
     unsigned char* wb = smem + warp * L::BYTES;
-    float4* s_q = reinterpret_cast<float4*>(wb);
     unsigned long long* s_n = reinterpret_cast<unsigned long long*>(wb + L::OFF_N);
-    float* s_halo = reinterpret_cast<float*>(wb + L::OFF_HALO);
     float* s_bm = reinterpret_cast<float*>(wb + L::OFF_BM);
-    unsigned char* s_cls = wb + L::OFF_CLS;
     unsigned short* s_list = reinterpret_cast<unsigned short*>(wb + L::OFF_LIST);
-    unsigned long long* bar = &s_bar[warp];
+    const unsigned sbase = smem_u32(wb), sn = sbase + L::OFF_N, sleave = sbase + L::OFF_LIST;
 
     const unsigned long long g = p.step;
     const unsigned par = (unsigned)(g & 1ull);
@@ -217,197 +233,329 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     int4* __restrict__ out = tp.rec[par ^ 1u];
     int4* __restrict__ arr_out = tp.arr[par ^ 1u];
     int4* __restrict__ ovf_out = tp.ovf[par ^ 1u];
-    unsigned* __restrict__ arr_next = tp.arr_cnt[par ^ 1u];
+    uint2* __restrict__ cnt_next = tp.cnt[par ^ 1u];
     unsigned* ovf_cnt_next = tp.tctl + (unsigned)((g + 1ull) % 3ull);
     const float* __restrict__ halo_in = tp.bmax[par];
     float* __restrict__ halo_out = tp.bmax[par ^ 1u];
     const unsigned gw = blockIdx.x * WPB + warp, nw = gridDim.x * WPB;
 
     if (threadIdx.x < 6u) s_acc[threadIdx.x] = 0u;
-    if (lane == 0) mbar_init(bar, 1u);
+    if (lane == 0) { mbar_init(&s_bar[warp][0], 1u); mbar_init(&s_bar[warp][1], 1u); }
     for (unsigned q = lane; q < T2; q += 32u) s_n[q] = 0ull;
     if (gw == 0u && lane == 0u) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
     __syncthreads();
 
     StepCtx c;
-    c.s_q = s_q; c.s_cls = s_cls; c.s_halo = s_halo; c.g = g;
     c.eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx];
+    c.tmax = p.max_steps > 0 ? p.max_steps : 0x7FFFFFFF;
+    c.eps_thr = !(c.eps > 0.0f) ? 0u : c.eps >= 1.0f ? (1u << 24) : (unsigned)ceilf(c.eps * 16777216.0f);   // scaling by 2^24 is exact
     const unsigned n_spill = min(tp.tctl[(unsigned)(g % 3ull)], p.N);
-    unsigned goals = 0, timeouts = 0, conf = 0, nbig = 0, nbigent = 0, bad = 0, phase = 0;
+    unsigned goals = 0, timeouts = 0, conf = 0, nbig = 0, nbigent = 0, bad = 0;
 
-    // Header of a tile: lanes 0..3 each load one word {region start, capacity, records in the region, arrivals};
-    // the words are only exchanged when the tile comes up, so the loads are off the path.
-    auto fetch_hdr = [&](unsigned tile) -> unsigned {
-        if (tile >= tp.ntiles || lane >= 4u) return 0u;
-        const unsigned* src = lane == 0u ? &tp.reg[tile].x : lane == 1u ? &tp.reg[tile].y : lane == 2u ? &tp.seg_cnt[par][tile] : &tp.arr_cnt[par][tile];
-        return *src;
-    };
-    unsigned hw = fetch_hdr(gw);
+    // Border cells this lane reports at the end of a tile: entry k = lane + 32 r of the ring (north row, south row, west
+    // column, east column), its cell inside the tile, and where it goes in the neighbour's block of the border array.
+    constexpr unsigned BR = (4u * T + 31u) / 32u;
+    unsigned b_ic[BR]; int b_dst[BR];
+#pragma unroll
+    for (unsigned r = 0; r < BR; ++r) {
+        const unsigned k = lane + 32u * r, e = k >> TSH, i = k & (T - 1u);
+        b_ic[r] = e == 0u ? i : e == 1u ? ((T - 1u) << TSH) + i : e == 2u ? (i << TSH) : (i << TSH) + T - 1u;
+        // my north row is the south halo (slot 1) of the tile above, my south row the north halo (0) of the tile below, west -> east (3), east -> west (2)
+        const int dtile = e == 0u ? -(int)tp.tiles_x : e == 1u ? (int)tp.tiles_x : e == 2u ? -1 : 1;
+        const unsigned slot = e == 0u ? 1u : e == 1u ? 0u : e == 2u ? 3u : 2u;
+        b_dst[r] = (dtile * 4 + (int)slot) * (int)T + (int)i;
+    }
 
-    for (unsigned tile = gw; tile < tp.ntiles; tile += nw) {
-        const unsigned roff = __shfl_sync(FULL, hw, 0), fcap = __shfl_sync(FULL, hw, 1);
-        const unsigned n_front = min(__shfl_sync(FULL, hw, 2), fcap), n_in = n_front + min(__shfl_sync(FULL, hw, 3), ARR_CAP);
-        const unsigned n_all = n_in + n_spill;
-        const unsigned tyi = tile / tp.tiles_x, txi = tile - tyi * tp.tiles_x;
-        const int tx0 = (int)(txi << TSH), ty0 = (int)(tyi << TSH);
-        c.tx0 = tx0; c.ty0 = ty0; c.tile = tile;
-
-        // ---- the tile's copies: table box, class bytes, border values -------------------------------------
+    // Header of a tile: lane 0 loads {region start, capacity}, lane 1 {records in the region, arrivals}; the words
+    // are only exchanged when the tile's copies are issued, one tile after the loads.
+    const uint2* hdr_src = lane == 0u ? tp.reg : tp.cnt[par];
+    auto fetch_hdr = [&](unsigned tile) -> uint2 { return (tile < tp.ntiles && lane < 2u) ? hdr_src[tile] : make_uint2(0u, 0u); };
+    struct Hdr { unsigned roff, fcap, n_front, n_in; int tx0, ty0; unsigned txi, tyi; };
+    // Issue the copies of a tile into a stage and fetch its first records into registers.
+    auto issue = [&](unsigned tile, unsigned stage, const uint2 hw, Hdr& h, int4 (&rec)[PRE]) {
+        h.roff = __shfl_sync(FULL, hw.x, 0); h.fcap = __shfl_sync(FULL, hw.y, 0);
+        h.n_front = min(__shfl_sync(FULL, hw.x, 1), h.fcap); h.n_in = h.n_front + min(__shfl_sync(FULL, hw.y, 1), ARR_CAP);
+        h.tx0 = (int)(h.txi << TSH); h.ty0 = (int)(h.tyi << TSH);
+        unsigned long long* bar = &s_bar[warp][stage];
+        unsigned char* st = wb + stage * L::STAGE;
         if (lane == 0u) mbar_arrive_expect_tx(bar, L::TX_BYTES);
         __syncwarp();
-        if (lane == 0u) tensor_g2s_2d(s_q, &tp.tmq, tx0 * 4, ty0, bar);
-        else if (lane == 1u) bulk_g2s(s_cls, tp.tcls + (size_t)tile * L::CLS, L::CLS, bar);
-        else if (lane == 2u) bulk_g2s(s_halo, halo_in + (size_t)tile * (4u * T), 4u * T * 4u, bar);
-
-        // record j of this tile's input: its region, then its arrival buffer (the spill list is filtered in the loop)
-        auto load_rec = [&](unsigned j) -> int4 { return j < n_front ? in[roff + j] : arr_in[(size_t)tile * ARR_CAP + (j - n_front)]; };
-        int4 pre[PRE];
+        if (lane == 0u) tensor_g2s_2d(st, &tp.tmq, h.tx0 * 4, h.ty0, bar);
+        else if (lane == 1u) bulk_g2s(st + L::ST_MV, tp.tcls + (size_t)tile * L::CLS, L::CLS, bar);
+        else if (lane == 2u) bulk_g2s(st + L::ST_HALO, halo_in + (size_t)tile * (4u * T), 4u * T * 4u, bar);
 #pragma unroll
-        for (unsigned q = 0; q < PRE; ++q) { const unsigned j = q * 32u + lane; pre[q] = j < n_in ? load_rec(j) : make_int4(0, 0, 0, 0); }
-        hw = fetch_hdr(tile + nw);                              // in flight while this tile is worked on
+        for (unsigned q = 0; q < PRE; ++q) {
+            const unsigned j = q * 32u + lane;
+            rec[q] = j < h.n_front ? in[h.roff + j] : j < h.n_in ? arr_in[(size_t)tile * ARR_CAP + (j - h.n_front)] : make_int4(0, 0, 0, 0);
+        }
+    };
+    // A record that leaves its tile: one atomic on the new tile's arrival counter, then the store.  The fast path issues the
+    // atomic at the end of a tile and stores a tile later, when the counter value has long arrived.
+    auto store_arrival = [&](const int4 r, unsigned dt, unsigned apos) {
+        if (apos < ARR_CAP) arr_out[(size_t)dt * ARR_CAP + apos] = r;
+        else {
+            const unsigned qq = atomicAdd(ovf_cnt_next, 1u);
+            if (qq < p.N) ovf_out[qq] = r; else bad = 1u;
+        }
+    };
 
-        if (!__all_sync(FULL, mbar_wait(bar, phase, tp.wait_polls))) {
+    Hdr hc{}, hn{};
+    int4 pre[PRE], nxt[PRE];
+    const unsigned dty = nw / tp.tiles_x, dtx = nw - dty * tp.tiles_x;
+    hn.tyi = gw / tp.tiles_x; hn.txi = gw - hn.tyi * tp.tiles_x;
+    uint2 hw = fetch_hdr(gw);
+    if (gw < tp.ntiles) { issue(gw, 0u, hw, hn, nxt); hw = fetch_hdr(gw + nw); }
+    bool pend = false; int4 pend_rec = make_int4(0, 0, 0, 0); unsigned pend_dt = 0, pend_pos = 0;
+
+    unsigned k = 0;
+    for (unsigned tile = gw; tile < tp.ntiles; tile += nw, ++k) {
+        const unsigned stage = NST == 2u ? (k & 1u) : 0u, phase = NST == 2u ? ((k >> 1) & 1u) : (k & 1u);
+        hc = hn;
+#pragma unroll
+        for (unsigned q = 0; q < PRE; ++q) pre[q] = nxt[q];
+        // ---- the next tile's copies and records: with two stages they go out before this tile is touched, else after it ----
+        auto issue_next = [&]() {
+            if (tile + nw < tp.ntiles) {
+                hn.txi = hc.txi + dtx; hn.tyi = hc.tyi + dty;
+                if (hn.txi >= tp.tiles_x) { hn.txi -= tp.tiles_x; ++hn.tyi; }
+                issue(tile + nw, NST == 2u ? (stage ^ 1u) : 0u, hw, hn, nxt);
+                hw = fetch_hdr(tile + 2u * nw);
+            }
+        };
+        if (NST == 2u) issue_next();
+        const unsigned roff = hc.roff, fcap = hc.fcap, n_front = hc.n_front, n_in = hc.n_in, n_all = n_in + n_spill;
+        const int tx0 = hc.tx0, ty0 = hc.ty0;
+        const unsigned txi = hc.txi, tyi = hc.tyi;
+        unsigned char* st = wb + stage * L::STAGE;
+        const float4* s_q = reinterpret_cast<const float4*>(st);
+        const unsigned sq = sbase + stage * L::STAGE, smv = sq + L::ST_MV, shalo = sq + L::ST_HALO;
+        c.s_q = s_q; c.s_mv = st + L::ST_MV; c.s_halo = reinterpret_cast<const float*>(st + L::ST_HALO);
+
+        if (!__all_sync(FULL, mbar_wait(&s_bar[warp][stage], phase, tp.wait_polls))) {
             // Never seen with the time bound.  Flag it, let the copies land (they target this warp's shared memory), stop.
             if (lane == 0u) atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT);
-            mbar_wait(bar, phase, 0u);
+            mbar_wait(&s_bar[warp][stage], phase, 0u);
+            if (NST == 2u && tile + nw < tp.ntiles) mbar_wait(&s_bar[warp][stage ^ 1u], ((k + 1u) >> 1) & 1u, 0u);
             break;
         }
-        phase ^= 1u;
 
-        const bool crowded = n_all > NMAX16;                    // warp-uniform
-        unsigned* gcnt = nullptr;
-        if (crowded) {                                           // 4 x 32-bit counters per cell in global scratch
-            unsigned q = 0;
-            if (lane == 0u) {
-                q = atomicAdd(&tp.tctl[3u + par], T2 * 2u);
-                if (q + T2 * 2u > p.N) { q = 0xFFFFFFFFu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
-            }
-            q = __shfl_sync(FULL, q, 0);
-            if (q != 0xFFFFFFFFu) {
-                gcnt = reinterpret_cast<unsigned*>(tp.scratch + q);
-                for (unsigned k = lane; k < T2 * 4u; k += 32u) gcnt[k] = 0u;
-            }
-            __syncwarp();
-        }
-
-        // ---- the step: every environment acts, moves and counts itself in its cell's histogram ----------
+        // stays: position in the tile's own region from a ballot.  Gives back whether the record still has to go somewhere else.
         unsigned nstay = 0;
-        for (unsigned it = 0; it * 32u < n_all; ++it) {
-            const unsigned j = it * 32u + lane;
-            bool act = j < n_all;
-            int4 rec = it == 0u ? pre[0] : it == 1u ? pre[1] : pre[2];
-            if (act && j >= n_in) { rec = ovf_in[j - n_in]; act = tile_of(tp, rec.x, rec.y) == tile; }
-            else if (act && it >= PRE) rec = load_rec(j);
-            const unsigned e = (unsigned)rec.w;
-            const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
-            if (act && (lx >= T || ly >= T)) { bad = 1u; act = false; }        // never seen: the record does not lie in this tile
-            int4 nrec = make_int4(0, 0, 0, 0); unsigned dt = 0xFFFFFFFFu;
-            if (act) {
-                const unsigned ic = (ly << TSH) + lx, hh = (ly + 1u) * HS + lx + 1u;
-                const U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
-                const int a = (u01(w.x) < c.eps) ? (int)(w.y & 3u) : argmax4(s_q[ic]);
-                const int dx = (a == 1) - (a == 3), dy = (a == 2) - (a == 0);
-                int nx = rec.x + dx, ny = rec.y + dy;
-                const bool inb = nx >= 0 && nx < p.W && ny >= 0 && ny < p.H;
-                const unsigned ht = (unsigned)((int)hh + dy * (int)HS + dx);      // inside the halo whenever the move is in bounds
-                const bool moved = inb && !(s_cls[inb ? ht : hh] & CW_OBST);
-                nx = moved ? nx : rec.x; ny = moved ? ny : rec.y;
-                const bool done = (s_cls[moved ? ht : hh] & CW_GOAL) != 0;
-                if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = done ? 1.0f : -0.01f; p.tr_d[e] = done ? 1 : 0; }
-                // the histogram: 32-bit shared-memory atomics are native; the 64-bit word of a cell is counted in its two halves
-                if (!crowded) atomicAdd(reinterpret_cast<unsigned*>(s_n) + 2u * ic + ((unsigned)a >> 1), 1u << (16u * ((unsigned)a & 1u)));
-                else if (gcnt) atomicAdd(&gcnt[ic * 4u + (unsigned)a], 1u);
-                // episode bookkeeping and the record of the next step
-                const bool timeout = !done && p.max_steps > 0 && rec.z + 1 >= p.max_steps;
-                int nt = rec.z + 1;
-                if (done || timeout) {
-                    const unsigned sn = sample_start(p, p.env_offset + e, g + 1ull, TAG_START);
-                    nx = (int)(sn % (unsigned)p.W); ny = (int)(sn / (unsigned)p.W); nt = 0;
-                    if (done) ++goals; else ++timeouts;
-                }
-                nrec = make_int4(nx, ny, nt, (int)e);
-                dt = ((unsigned)ny >> TSH) * tp.tiles_x + ((unsigned)nx >> TSH);
-            }
-            // stays: position in the tile's own region from a ballot; leaves (or no room): one atomic on the new tile's arrival buffer
-            const bool stay = act && dt == tile;
-            const unsigned sm = __ballot_sync(FULL, stay);
+        auto put_stay = [&](bool act, bool stays, const int4 nrec) -> bool {
+            const unsigned sm = __ballot_sync(FULL, act && stays);
             const unsigned pos = nstay + __popc(sm & lt);
             nstay += __popc(sm);
-            if (stay && pos < fcap) out[roff + pos] = nrec;
-            else if (act) {
-                const unsigned apos = atomicAdd(&arr_next[dt], 1u);
-                if (apos < ARR_CAP) arr_out[(size_t)dt * ARR_CAP + apos] = nrec;
-                else {
-                    const unsigned q = atomicAdd(ovf_cnt_next, 1u);
-                    if (q < p.N) ovf_out[q] = nrec; else bad = 1u;
+            const bool placed = act && stays && pos < fcap;
+            if (placed) out[roff + pos] = nrec;
+            return act && !placed;
+        };
+
+        const bool fast = n_all <= PRE * 32u && n_spill == 0u;  // warp-uniform: every record of the tile is already in registers
+        if (fast) {
+            // ---- few records: one pass, everything an update needs stays in registers ---------------------------
+            // Each environment computes the TD target of its own (cell, action) -- it has the next cell at hand -- and
+            // counts itself; the FIRST to count on a (cell, action) owns it and, once every count is in, applies the
+            // map that many times to the one table entry: a 4-byte store into the table, and into the tile in shared
+            // memory, which thereby becomes Q_{t+1} for the border values.
+            unsigned rw0[PRE], rw1[PRE], key[PRE]; float dd[PRE];
+#pragma unroll
+            for (unsigned q = 0; q < PRE; ++q) {                 // the random draws first: independent chains the scheduler can interleave
+                key[q] = 0u; dd[q] = 0.0f; rw0[q] = 0u; rw1[q] = 0u;
+                if (q * 32u < n_all) {
+                    const U4 w = philox4x32_10(p.env_offset + (unsigned)pre[q].w, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
+                    rw0[q] = w.x; rw1[q] = w.y;
                 }
             }
-        }
-        if (lane == 0u) {
-            tp.seg_cnt[par ^ 1u][tile] = min(nstay, fcap);
-            tp.arr_cnt[par][tile] = 0u;                                   // consumed; it is the append counter again in the next step
-        }
-        __syncwarp();
-
-        // ---- the occupied cells, compacted; the border ring starts out as max Q_t ----------------------------
-        unsigned nocc = 0;
-        if (!crowded) {
+            unsigned nleave = 0;
 #pragma unroll
-            for (unsigned k = 0; k < T2 / 32u; ++k) {
-                const unsigned ic = k * 32u + lane;
-                const bool nz = s_n[ic] != 0ull;
-                const unsigned m = __ballot_sync(FULL, nz);
-                if (nz) s_list[nocc + __popc(m & lt)] = (unsigned short)ic;
-                nocc += __popc(m);
+            for (unsigned q = 0; q < PRE; ++q) {
+                if (q * 32u >= n_all) break;
+                const int4 rec = pre[q];
+                const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
+                bool act = q * 32u + lane < n_all;
+                if (act && (lx | ly) >= T) { bad = 1u; act = false; }             // never seen: the record does not lie in this tile
+                int4 nrec = rec; bool stays = false;
+                if (act) {
+                    const unsigned ic = (ly << TSH) | lx;
+                    const float4 row = lds_f4(sq + ic * 16u);
+                    const unsigned mvb = lds_u8(smv + ic);
+                    int a = argmax4(row);
+                    if ((rw0[q] >> 8) < c.eps_thr) a = (int)(rw1[q] & 3u);
+                    const bool blocked = (mvb >> a) & 1u, done = (mvb >> (a + 4)) & 1u;
+                    // per action: dx = {0, 1, 0, -1}, dy = {-1, 0, 1, 0}, one signed byte each
+                    const int dx = blocked ? 0 : (int)(signed char)(0xFF000100u >> (8 * a)), dy = blocked ? 0 : (int)(signed char)(0x000100FFu >> (8 * a));
+                    const unsigned mx = lx + (unsigned)dx, my = ly + (unsigned)dy;      // wraps when the move leaves the tile
+                    stays = (mx | my) < T;
+                    float m;
+                    if (stays) m = max4(lds_f4(sq + ((my << TSH) | mx) * 16u));
+                    else m = lds_f32(shalo + 4u * ((int)my < 0 ? lx : my >= T ? T + lx : (int)mx < 0 ? 2u * T + ly : 3u * T + ly));
+                    if (p.legacy_clamp && m < 0.0f) m = 0.0f;
+                    dd[q] = done ? 1.0f : __fmaf_rn(p.gamma, m, -0.01f);              // the TD target of (cell, a), from Q_t
+                    if (TRACE) { p.tr_a[rec.w] = a; p.tr_r[rec.w] = done ? 1.0f : -0.01f; p.tr_d[rec.w] = done ? 1 : 0; }
+                    const unsigned idx = ic * 4u + (unsigned)a, sh = 16u * ((unsigned)a & 1u);
+                    const unsigned old = atoms_add(sn + (idx >> 1) * 4u, 1u << sh);
+                    key[q] = ((((old >> sh) & 0xFFFFu) == 0u) ? 0x40000000u : 0u) | idx;
+                    nrec.x = rec.x + dx; nrec.y = rec.y + dy; nrec.z = rec.z + 1;
+                    if (done || nrec.z >= c.tmax) {
+                        const unsigned sn2 = sample_start(p, p.env_offset + (unsigned)rec.w, g + 1ull, TAG_START);
+                        nrec.y = (int)(sn2 / (unsigned)p.W); nrec.x = (int)(sn2 - (unsigned)nrec.y * (unsigned)p.W); nrec.z = 0;
+                        stays = (((unsigned)(nrec.x - tx0)) | ((unsigned)(nrec.y - ty0))) < T;
+                        if (done) ++goals; else ++timeouts;
+                    }
+                }
+                // a record that leaves is queued in shared memory; its atomic goes out when the tile is done
+                const bool leaves = put_stay(act, stays, nrec);
+                const unsigned lm = __ballot_sync(FULL, leaves);
+                if (lm) {
+                    const unsigned qpos = nleave + __popc(lm & lt);
+                    nleave += __popc(lm);
+                    if (leaves) {
+                        if (qpos < 32u) asm volatile("st.shared.v4.s32 [%0], {%1, %2, %3, %4};" :: "r"(sleave + qpos * 16u), "r"(nrec.x), "r"(nrec.y), "r"(nrec.z), "r"(nrec.w) : "memory");
+                        else { const unsigned dt = tile_of(tp, nrec.x, nrec.y); store_arrival(nrec, dt, atomicAdd(&cnt_next[dt].y, 1u)); }
+                    }
+                }
             }
-        } else nocc = gcnt ? T2 : 0u;
-        for (unsigned k = lane; k < 4u * T; k += 32u) {
-            const unsigned e = k >> TSH, i = k & (T - 1u);
-            const unsigned ic = e == 0u ? i : e == 1u ? ((T - 1u) << TSH) + i : e == 2u ? (i << TSH) : (i << TSH) + T - 1u;
-            s_bm[k] = max4(s_q[ic]);
-        }
-        __syncwarp();
+            __syncwarp();
+            float* const qtile = reinterpret_cast<float*>(p.Q + ((size_t)ty0 * (size_t)p.W + (size_t)tx0));
+#pragma unroll
+            for (unsigned q = 0; q < PRE; ++q) {
+                if (!(key[q] & 0x40000000u)) continue;
+                const unsigned idx = key[q] & 0xFFFFu, ic = idx >> 2, a = idx & 3u;
+                const unsigned n = lds_u16(sn + idx * 2u);
+                const uint2 w = lds_u32x2(sn + ic * 8u);
+                const unsigned s2 = w.x + w.y, tot = (s2 & 0xFFFFu) + (s2 >> 16);       // at most 96 per tile: no carry between the fields
+                if (tot > 1u) conf += n;
+                if (tot > CROWDED_CELL) {                                              // the lowest chosen action speaks for the cell
+                    const unsigned long long ww = ((unsigned long long)w.y << 32) | w.x;
+                    if ((ww & ((1ull << (16u * a)) - 1ull)) == 0ull) { ++nbig; nbigent += tot; }
+                }
+                float v = lds_f32(sq + idx * 4u);
+                for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(dd[q], v), v);      // one application per environment
+                sts_f32(sq + idx * 4u, v);
+                qtile[((ic >> TSH) * (unsigned)p.W + (ic & (T - 1u))) * 4u + a] = v;    // (row inside the tile) * W + column < cells < 2^28
+            }
+            // the previous tile's leavers: their counter values have arrived by now
+            if (pend) store_arrival(pend_rec, pend_dt, pend_pos);
+            pend = lane < min(nleave, 32u);
+            __syncwarp();
+            if (pend) {
+                asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(pend_rec.x), "=r"(pend_rec.y), "=r"(pend_rec.z), "=r"(pend_rec.w) : "r"(sleave + lane * 16u) : "memory");
+                pend_dt = tile_of(tp, pend_rec.x, pend_rec.y);
+                pend_pos = atomicAdd(&cnt_next[pend_dt].y, 1u);
+            }
+#pragma unroll
+            for (unsigned kk = 0; kk < T2 / 32u; ++kk) sts_zero8(sn + (kk * 32u + lane) * 8u);
+        } else {
+            const bool crowded = n_all > NMAX16;                    // warp-uniform
+            unsigned* gcnt = nullptr;
+            if (crowded) {                                           // 4 x 32-bit counters per cell in global scratch
+                unsigned q = 0;
+                if (lane == 0u) {
+                    q = atomicAdd(&tp.tctl[3u + par], T2 * 2u);
+                    if (q + T2 * 2u > p.N) { q = 0xFFFFFFFFu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
+                }
+                q = __shfl_sync(FULL, q, 0);
+                if (q != 0xFFFFFFFFu) {
+                    gcnt = reinterpret_cast<unsigned*>(tp.scratch + q);
+                    for (unsigned kk = lane; kk < T2 * 4u; kk += 32u) gcnt[kk] = 0u;
+                }
+                __syncwarp();
+            }
 
-        // ---- Q_{t+1} of the occupied cells, from Q_t in shared memory straight into the table -----------------
-        for (unsigned idx = lane; idx < nocc; idx += 32u) {
-            unsigned ic, tot; unsigned long long w = 0ull; unsigned n32[4];
+            // ---- the step: every environment acts, moves and counts itself in its cell's histogram ----------
+            for (unsigned it = 0; it * 32u < n_all; ++it) {
+                const unsigned j = it * 32u + lane;
+                bool act = j < n_all;
+                int4 rec = it == 0u ? pre[0] : it == 1u ? pre[1] : pre[2];
+                if (act && j >= n_in) { rec = ovf_in[j - n_in]; act = tile_of(tp, rec.x, rec.y) == tile; }
+                else if (act && it >= PRE) rec = j < n_front ? in[roff + j] : arr_in[(size_t)tile * ARR_CAP + (j - n_front)];
+                const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
+                if (act && (lx | ly) >= T) { bad = 1u; act = false; }
+                int4 nrec = rec; bool stays = false;
+                if (act) {
+                    const unsigned ic = (ly << TSH) | lx, e = (unsigned)rec.w;
+                    const U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
+                    const unsigned mvb = c.s_mv[ic];
+                    const int a = ((w.x >> 8) < c.eps_thr) ? (int)(w.y & 3u) : argmax4(s_q[ic]);
+                    const bool blocked = (mvb >> a) & 1u, done = (mvb >> (4 + a)) & 1u;
+                    const int dx = blocked ? 0 : (a == 1) - (a == 3), dy = blocked ? 0 : (a == 2) - (a == 0);
+                    nrec.x = rec.x + dx; nrec.y = rec.y + dy; nrec.z = rec.z + 1;
+                    if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = done ? 1.0f : -0.01f; p.tr_d[e] = done ? 1 : 0; }
+                    // 32-bit shared-memory atomics are native; the 64-bit word of a cell is counted in its two halves
+                    if (!crowded) atomicAdd(reinterpret_cast<unsigned*>(s_n) + 2u * ic + ((unsigned)a >> 1), 1u << (16u * ((unsigned)a & 1u)));
+                    else if (gcnt) atomicAdd(&gcnt[ic * 4u + (unsigned)a], 1u);
+                    if (done || nrec.z >= c.tmax) {
+                        const unsigned sn2 = sample_start(p, p.env_offset + e, g + 1ull, TAG_START);
+                        nrec.y = (int)(sn2 / (unsigned)p.W); nrec.x = (int)(sn2 - (unsigned)nrec.y * (unsigned)p.W); nrec.z = 0;
+                        if (done) ++goals; else ++timeouts;
+                    }
+                    stays = (((unsigned)(nrec.x - tx0)) | ((unsigned)(nrec.y - ty0))) < T;
+                }
+                if (put_stay(act, stays, nrec)) { const unsigned dt = tile_of(tp, nrec.x, nrec.y); store_arrival(nrec, dt, atomicAdd(&cnt_next[dt].y, 1u)); }
+            }
+            __syncwarp();
+
+            // ---- the occupied cells, compacted; the border ring starts out as max Q_t ----------------------------
+            unsigned nocc = 0;
             if (!crowded) {
-                ic = s_list[idx];
-                w = s_n[ic]; s_n[ic] = 0ull;
-                tot = ((unsigned)w & 0xFFFFu) + ((unsigned)(w >> 16) & 0xFFFFu) + ((unsigned)(w >> 32) & 0xFFFFu) + (unsigned)(w >> 48);
-            } else {
-                ic = idx;
-                const uint4 v = *reinterpret_cast<const uint4*>(gcnt + 4u * ic);
-                n32[0] = v.x; n32[1] = v.y; n32[2] = v.z; n32[3] = v.w;
-                tot = v.x + v.y + v.z + v.w;
+#pragma unroll
+                for (unsigned kk = 0; kk < T2 / 32u; ++kk) {
+                    const unsigned ic = kk * 32u + lane;
+                    const bool nz = s_n[ic] != 0ull;
+                    const unsigned m = __ballot_sync(FULL, nz);
+                    if (nz) s_list[nocc + __popc(m & lt)] = (unsigned short)ic;
+                    nocc += __popc(m);
+                }
+            } else nocc = gcnt ? T2 : 0u;
+#pragma unroll
+            for (unsigned r = 0; r < BR; ++r) if (lane + 32u * r < 4u * T) s_bm[lane + 32u * r] = max4(s_q[b_ic[r]]);
+            __syncwarp();
+
+            // ---- Q_{t+1} of the occupied cells, from Q_t in shared memory straight into the table -----------------
+            for (unsigned idx = lane; idx < nocc; idx += 32u) {
+                unsigned ic, tot; unsigned long long w = 0ull; unsigned n32[4];
+                if (!crowded) {
+                    ic = s_list[idx];
+                    w = s_n[ic]; s_n[ic] = 0ull;
+                    tot = ((unsigned)w & 0xFFFFu) + ((unsigned)(w >> 16) & 0xFFFFu) + ((unsigned)(w >> 32) & 0xFFFFu) + (unsigned)(w >> 48);
+                } else {
+                    ic = idx;
+                    const uint4 v = *reinterpret_cast<const uint4*>(gcnt + 4u * ic);
+                    n32[0] = v.x; n32[1] = v.y; n32[2] = v.z; n32[3] = v.w;
+                    tot = v.x + v.y + v.z + v.w;
+                }
+                if (!tot) continue;
+                if (tot > 1u) conf += tot;
+                if (tot > CROWDED_CELL) { ++nbig; nbigent += tot; }
+                const float4 row = updated_row<TSH>(p, c, ic, w, crowded ? n32 : nullptr);
+                const unsigned lx = ic & (T - 1u), ly = ic >> TSH;
+                p.Q[(size_t)(ty0 + (int)ly) * (size_t)p.W + (size_t)(tx0 + (int)lx)] = row;
+                const float mx = max4(row);
+                if (ly == 0u) s_bm[lx] = mx;
+                if (ly == T - 1u) s_bm[T + lx] = mx;
+                if (lx == 0u) s_bm[2u * T + ly] = mx;
+                if (lx == T - 1u) s_bm[3u * T + ly] = mx;
             }
-            if (!tot) continue;
-            if (tot > 1u) conf += tot;
-            if (tot > CROWDED_CELL) { ++nbig; nbigent += tot; }
-            const float4 row = updated_row<TSH>(p, c, ic, w, crowded ? n32 : nullptr);
-            const unsigned lx = ic & (T - 1u), ly = ic >> TSH;
-            p.Q[(size_t)(ty0 + (int)ly) * (size_t)p.W + (size_t)(tx0 + (int)lx)] = row;
-            const float mx = max4(row);
-            if (ly == 0u) s_bm[lx] = mx;
-            if (ly == T - 1u) s_bm[T + lx] = mx;
-            if (lx == 0u) s_bm[2u * T + ly] = mx;
-            if (lx == T - 1u) s_bm[3u * T + ly] = mx;
         }
+        if (lane == 0u) tp.cnt[par ^ 1u][tile].x = min(nstay, fcap);
+        else if (lane == 1u) tp.cnt[par][tile] = make_uint2(0u, 0u);        // consumed; .y is the append counter again in the next step
         __syncwarp();
 
-        // ---- border values out: my north row is the south halo of the tile above, and so on ----------------
-        for (unsigned k = lane; k < 4u * T; k += 32u) {
-            const unsigned e = k >> TSH, i = k & (T - 1u);
-            bool there; unsigned nt, slot;
-            if (e == 0u)      { there = tyi > 0u;               nt = tile - tp.tiles_x; slot = 1u; }
-            else if (e == 1u) { there = tyi + 1u < tp.tiles_y;  nt = tile + tp.tiles_x; slot = 0u; }
-            else if (e == 2u) { there = txi > 0u;               nt = tile - 1u;         slot = 3u; }
-            else              { there = txi + 1u < tp.tiles_x;  nt = tile + 1u;         slot = 2u; }
-            if (there) halo_out[((size_t)nt * 4u + slot) * T + i] = s_bm[k];
+        // ---- border values out: max_a Q_{t+1} of my border ring into the neighbours' blocks of the other parity ----------
+        {
+            float* const hbase = halo_out + (size_t)tile * (4u * T);
+#pragma unroll
+            for (unsigned r = 0; r < BR; ++r) {
+                const unsigned kk = lane + 32u * r, e = kk >> TSH;
+                const bool there = kk < 4u * T && (e == 0u ? tyi > 0u : e == 1u ? tyi + 1u < tp.tiles_y : e == 2u ? txi > 0u : txi + 1u < tp.tiles_x);
+                if (there) hbase[b_dst[r]] = fast ? max4(lds_f4(sq + b_ic[r] * 16u)) : s_bm[kk];
+            }
         }
-        fence_async_smem();                                      // this lane's reads of the tile come before the next copies' writes
-        __syncwarp();                                            // every lane is done with the tile before the next copies are issued
+        fence_async_smem();                                      // this lane's reads of the stage come before the copies that will refill it
+        __syncwarp();                                            // every lane is done with the tile
+        if (NST == 1u) issue_next();
     }
+    if (pend) store_arrival(pend_rec, pend_dt, pend_pos);
 
     // ---- run statistics: warp -> block -> one atomic per counter and block ----------------------------------
     for (int o = 16; o; o >>= 1) {
@@ -448,7 +596,7 @@ __global__ void k_te_count(Params p) {
     const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.N) return;
     const int4 r = p.st[i];
-    atomicAdd(&p.tp.seg_cnt[p.step & 1ull][tile_of(p.tp, r.x, r.y)], 1u);
+    atomicAdd(&p.tp.cnt[p.step & 1ull][tile_of(p.tp, r.x, r.y)].x, 1u);
 }
 // One block: region capacities (population + 25 % + 32), their exclusive scan, counters reset.
 __global__ void __launch_bounds__(1024) k_te_layout(Params p) {
@@ -460,14 +608,14 @@ __global__ void __launch_bounds__(1024) k_te_layout(Params p) {
     __syncthreads();
     for (unsigned base = 0; base < tp.ntiles; base += 1024u) {
         const unsigned k = base + threadIdx.x;
-        const unsigned cnt = k < tp.ntiles ? tp.seg_cnt[par][k] : 0u;
+        const unsigned cnt = k < tp.ntiles ? tp.cnt[par][k].x : 0u;
         const unsigned F = cnt + cnt / 4u + 32u;
         unsigned total = 0;
         const unsigned ex = block_scan_excl(k < tp.ntiles ? F : 0u, s_warp, &total);
         const unsigned carry = s_carry;
         if (k < tp.ntiles) {
             tp.reg[k] = make_uint2(carry + ex, F);
-            tp.seg_cnt[par][k] = 0u; tp.seg_cnt[par ^ 1u][k] = 0u; tp.arr_cnt[0][k] = 0u; tp.arr_cnt[1][k] = 0u;
+            tp.cnt[0][k] = make_uint2(0u, 0u); tp.cnt[1][k] = make_uint2(0u, 0u);
         }
         __syncthreads();
         if (threadIdx.x == 0) s_carry = carry + total;
@@ -482,20 +630,33 @@ __global__ void k_te_scatter(Params p) {
     const unsigned par = (unsigned)(p.step & 1ull);
     const int4 r = p.st[i];
     const unsigned tile = tile_of(tp, r.x, r.y);
-    const unsigned pos = atomicAdd(&tp.seg_cnt[par][tile], 1u);
+    const unsigned pos = atomicAdd(&tp.cnt[par][tile].x, 1u);
     tp.rec[par][tp.reg[tile].x + pos] = r;
 }
-// The class bytes (obstacle / goal bits) of every tile with its halo, laid out as the step kernel copies them.
+// The move byte of every cell, tile by tile as the step kernel copies them: bit a = a move in direction a is blocked (grid
+// edge or obstacle, src/kernels.cu:29-44 of the reference), bit 4+a = the cell an environment stands on after choosing a is a
+// goal (src/kernels.cu:56-59, src/environment.cu:43-46).  Cells of an edge tile that lie outside the grid: all blocked.
 __global__ void __launch_bounds__(BLOCK) k_te_cls(Params p) {
     const TileP& tp = p.tp;
-    const unsigned tile = blockIdx.x, HS = tp.T + 2u;
-    const int tx0 = (int)((tile % tp.tiles_x) << tp.tshift), ty0 = (int)((tile / tp.tiles_x) << tp.tshift);
-    for (unsigned k = threadIdx.x; k < tp.cls_stride; k += BLOCK) {
-        const unsigned hy = k / HS, hx = k - hy * HS;
-        const int gx = tx0 + (int)hx - 1, gy = ty0 + (int)hy - 1;
-        unsigned cls = CW_OBST;
-        if (hy < HS && gx >= 0 && gx < p.W && gy >= 0 && gy < p.H) cls = p.cw[(unsigned)gy * (unsigned)p.W + (unsigned)gx] & (CW_OBST | CW_GOAL);
-        tp.tcls[(size_t)tile * tp.cls_stride + k] = (unsigned char)cls;
+    const unsigned T = tp.T, T2 = T * T;
+    const size_t total = (size_t)tp.ntiles * T2;
+    for (size_t k = (size_t)blockIdx.x * BLOCK + threadIdx.x; k < total; k += (size_t)gridDim.x * BLOCK) {
+        const unsigned tile = (unsigned)(k / T2), ic = (unsigned)(k - (size_t)tile * T2);
+        const int x = (int)(((tile % tp.tiles_x) << tp.tshift) + (ic & (T - 1u))), y = (int)(((tile / tp.tiles_x) << tp.tshift) + (ic >> tp.tshift));
+        unsigned b = 0x0Fu;
+        if (x < p.W && y < p.H) {
+            const unsigned own = p.cw[(unsigned)y * (unsigned)p.W + (unsigned)x];
+            b = 0u;
+            for (int a = 0; a < 4; ++a) {
+                const int nx = x + (a == 1) - (a == 3), ny = y + (a == 2) - (a == 0);
+                unsigned cls = CW_OBST;
+                if (nx >= 0 && nx < p.W && ny >= 0 && ny < p.H) cls = p.cw[(unsigned)ny * (unsigned)p.W + (unsigned)nx];
+                const bool blocked = (cls & CW_OBST) != 0u;
+                if (blocked) b |= 1u << a;
+                if ((blocked ? own : cls) & CW_GOAL) b |= 16u << a;
+            }
+        }
+        tp.tcls[k] = (unsigned char)b;
     }
 }
 // The border array of the current parity from the table: for every tile the max over actions of the cells just
@@ -521,7 +682,8 @@ __global__ void __launch_bounds__(BLOCK) k_te_export(Params p) {
     const unsigned par = (unsigned)(p.step & 1ull);
     for (unsigned tile = blockIdx.x; tile < tp.ntiles; tile += gridDim.x) {
         const uint2 rg = tp.reg[tile];
-        const unsigned n_front = min(tp.seg_cnt[par][tile], rg.y), n_arr = min(tp.arr_cnt[par][tile], ARR_CAP);
+        const uint2 cn = tp.cnt[par][tile];
+        const unsigned n_front = min(cn.x, rg.y), n_arr = min(cn.y, ARR_CAP);
         const int4* in = tp.rec[par] + rg.x;
         const int4* ain = tp.arr[par] + (size_t)tile * ARR_CAP;
         for (unsigned j = threadIdx.x; j < n_front; j += BLOCK) { const int4 r = in[j]; if ((unsigned)r.w < p.N) p.st[r.w] = r; }
@@ -555,7 +717,7 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const 
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 static inline unsigned capped_blocks(size_t n) { const size_t b = (n + BLOCK - 1) / BLOCK; return (unsigned)(b < 1 ? 1 : (b > 2368 ? 2368 : b)); }
 
-constexpr unsigned MINB16 = 6, MINB8 = 6;     // resident blocks per SM the register budget is cut for
+constexpr unsigned MINB16 = 5, MINB8 = 5;     // resident blocks per SM the register budget is cut for: the most that compiles without spills
 size_t tile_step_smem(const Params& p) { return (size_t)WPB * (p.tp.tshift == 4u ? WarpSmem<4>::BYTES : WarpSmem<3>::BYTES); }
 unsigned tile_cls_stride(unsigned tshift) { return tshift == 4u ? WarpSmem<4>::CLS : WarpSmem<3>::CLS; }
 
@@ -568,6 +730,12 @@ static cudaError_t configure_one(int bytes, int* per_sm) {
         if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
     }
     if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH, MINB>, (int)(WPB * 32u), (size_t)bytes);
+    if (e == cudaSuccess && *per_sm > 0) {
+        // no more shared memory than the resident blocks need (1 KB per block is the system's): the rest stays first-level cache
+        int pct = (int)(((size_t)*per_sm * ((size_t)bytes + 1024u + 256u) * 100u + 228u * 1024u - 1u) / (228u * 1024u));
+        pct = pct > 100 ? 100 : pct;
+        for (const void* f : fns) if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, pct);
+    }
     return e;
 }
 int tile_engine_configure(Params& p, int device) {
@@ -586,12 +754,12 @@ int tile_engine_configure(Params& p, int device) {
     return 0;
 }
 void launch_tile_bucket(const Params& p, cudaStream_t st) {
-    cudaMemsetAsync(p.tp.seg_cnt[p.step & 1ull], 0, (size_t)p.tp.ntiles * sizeof(unsigned), st);
+    cudaMemsetAsync(p.tp.cnt[p.step & 1ull], 0, (size_t)p.tp.ntiles * sizeof(uint2), st);
     if (p.N) k_te_count<<<nblk(p.N), BLOCK, 0, st>>>(p);
     k_te_layout<<<1, 1024, 0, st>>>(p);
     if (p.N) k_te_scatter<<<nblk(p.N), BLOCK, 0, st>>>(p);
 }
-void launch_tile_classes(const Params& p, cudaStream_t st) { k_te_cls<<<p.tp.ntiles, BLOCK, 0, st>>>(p); }
+void launch_tile_classes(const Params& p, cudaStream_t st) { k_te_cls<<<capped_blocks((size_t)p.tp.ntiles * p.tp.T * p.tp.T), BLOCK, 0, st>>>(p); }
 void launch_tile_border(const Params& p, cudaStream_t st) { k_te_border<<<capped_blocks((size_t)p.tp.ntiles * 4u * p.tp.T), BLOCK, 0, st>>>(p); }
 void launch_tile_export(const Params& p, cudaStream_t st) {
     k_te_export<<<p.tp.ntiles < 4736u ? p.tp.ntiles : 4736u, BLOCK, 0, st>>>(p);
