@@ -38,7 +38,6 @@ namespace cudarl {
 constexpr unsigned CROWDED_CELL = 24;   // a cell with more environments than this counts as "crowded" in the run statistics
 constexpr unsigned NMAX16 = 65535u;     // records of a tile the 16-bit counters can hold
 constexpr unsigned WPB = 4;             // warps per block; every warp works on its own
-constexpr unsigned NST = 1;             // copy stages per warp: 2 = the next tile's copies fly while this tile is worked on
 constexpr unsigned PRE = 3;             // records per lane fetched before the warp waits for its copies
 
 __device__ __forceinline__ unsigned tile_of(const TileP& tp, int x, int y) {
@@ -141,8 +140,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 // how many environments chose it -- a histogram in shared memory -- and then apply each map that many times.
 // (update_batch takes arbitrary caller transitions, so it keeps its ordered fold.)
 //
-// Shared memory of one warp (nothing is shared between warps).  Two STAGES, so that the copies of the next tile are
-// in flight while the warp works on this one:
+// Shared memory of one warp (nothing is shared between warps).  What the copies of a tile deliver:
 //   s_q    T*T  float4   Q_t of the tile, row-major inside the tile
 //   s_mv   T*T  u8       per cell: bit a = a move in direction a is blocked (grid edge or obstacle), bit 4+a = the
 //                        cell an environment stands on after choosing a (the next cell, or its own when blocked) is a goal
@@ -156,7 +154,7 @@ template <unsigned TSH> struct WarpSmem {
     static constexpr unsigned T = 1u << TSH, T2 = T * T;
     static constexpr unsigned CLS = T2;                              // a multiple of 16 for T = 8 and 16
     static constexpr unsigned ST_MV = T2 * 16u, ST_HALO = ST_MV + CLS, STAGE = (ST_HALO + 4u * T * 4u + 127u) / 128u * 128u;
-    static constexpr unsigned OFF_N = NST * STAGE, OFF_BM = OFF_N + T2 * 8u, OFF_LIST = OFF_BM + 4u * T * 4u;
+    static constexpr unsigned OFF_N = STAGE, OFF_BM = OFF_N + T2 * 8u, OFF_LIST = OFF_BM + 4u * T * 4u;
     static constexpr unsigned LIST_BYTES = T2 * 2u > 512u ? T2 * 2u : 512u;
     static constexpr unsigned BYTES = (OFF_LIST + LIST_BYTES + 127u) / 128u * 128u;
     static constexpr unsigned TX_BYTES = T2 * 16u + CLS + 4u * T * 4u;      // what the three copies of a tile deliver
@@ -164,7 +162,6 @@ template <unsigned TSH> struct WarpSmem {
 
 // Everything the per-environment step needs about the tile being processed.
 struct StepCtx {
-    const float4* s_q; const unsigned char* s_mv; const float* s_halo;
     float eps; int tmax;
     unsigned eps_thr;      // explore iff (w0 >> 8) < eps_thr: the same test as (w0 >> 8) * 2^-24 < eps, in integers
 };
@@ -172,17 +169,17 @@ struct StepCtx {
 // TD target of (cell, action) from Q_t:  r + gamma * max_a' Q_t[s'],  0 for the max when the episode ends there.
 // The next cell's max comes from the tile, or from the border values when the move crosses an edge.
 template <unsigned TSH>
-__device__ __forceinline__ float td_target(const Params& p, const StepCtx& c, unsigned ic, int a, unsigned mvb) {
+__device__ __forceinline__ float td_target(const Params& p, const float4* s_q, const float* s_halo, unsigned ic, int a, unsigned mvb) {
     constexpr unsigned T = 1u << TSH;
     const bool blocked = (mvb >> a) & 1u, done = (mvb >> (4 + a)) & 1u;
     float m = 0.0f;
     if (!done) {
-        if (blocked) m = max4(c.s_q[ic]);
+        if (blocked) m = max4(s_q[ic]);
         else {
             const unsigned lx = ic & (T - 1u), ly = ic >> TSH;
             const int mx = (int)lx + (a == 1) - (a == 3), my = (int)ly + (a == 2) - (a == 0);
-            if ((unsigned)mx < T && (unsigned)my < T) m = max4(c.s_q[((unsigned)my << TSH) + (unsigned)mx]);
-            else m = c.s_halo[my < 0 ? lx : my >= (int)T ? T + lx : mx < 0 ? 2u * T + ly : 3u * T + ly];
+            if ((unsigned)mx < T && (unsigned)my < T) m = max4(s_q[((unsigned)my << TSH) + (unsigned)mx]);
+            else m = s_halo[my < 0 ? lx : my >= (int)T ? T + lx : mx < 0 ? 2u * T + ly : 3u * T + ly];
         }
         if (p.legacy_clamp && m < 0.0f) m = 0.0f;
     }
@@ -192,15 +189,17 @@ __device__ __forceinline__ float td_target(const Params& p, const StepCtx& c, un
 // Q_{t+1} row of one cell from Q_t and the number of environments that chose each action
 // (`w`: 16 bits per action, or `n32` when the tile counts in 32 bits).  Only the actions that were chosen are visited.
 template <unsigned TSH>
-__device__ __forceinline__ float4 updated_row(const Params& p, const StepCtx& c, unsigned ic, unsigned long long w, const unsigned* n32) {
-    float4 row = c.s_q[ic];
-    const unsigned mvb = c.s_mv[ic];
+__device__ __forceinline__ float4 updated_row(const Params& p, const unsigned char* st, unsigned ic, unsigned long long w, const unsigned* n32) {
+    using L = WarpSmem<TSH>;
+    const float4* s_q = reinterpret_cast<const float4*>(st);
+    float4 row = s_q[ic];
+    const unsigned mvb = st[L::ST_MV + ic];
     unsigned mask = n32 ? ((n32[0] != 0u) | ((n32[1] != 0u) << 1) | ((n32[2] != 0u) << 2) | ((n32[3] != 0u) << 3))
                         : (((w & 0xFFFFull) != 0ull) | (((w >> 16) & 0xFFFFull) != 0ull) << 1 | (((w >> 32) & 0xFFFFull) != 0ull) << 2 | ((w >> 48) != 0ull) << 3);
     while (mask) {
         const int a = __ffs((int)mask) - 1; mask &= mask - 1u;
         const unsigned n = n32 ? n32[a] : (unsigned)(w >> (16 * a)) & 0xFFFFu;
-        const float d = td_target<TSH>(p, c, ic, a, mvb);
+        const float d = td_target<TSH>(p, s_q, reinterpret_cast<const float*>(st + L::ST_HALO), ic, a, mvb);
         float v = pick(row, a);
         for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(d, v), v);       // one application per environment
         row.x = a == 0 ? v : row.x; row.y = a == 1 ? v : row.y; row.z = a == 2 ? v : row.z; row.w = a == 3 ? v : row.w;
@@ -213,7 +212,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     using L = WarpSmem<TSH>;
     constexpr unsigned T = L::T, T2 = L::T2;
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_bar[WPB][2];
+    __shared__ __align__(8) unsigned long long s_bar[WPB];
     __shared__ unsigned s_acc[6];            // goals, timeouts, conflicts, crowded cells, environments on them, bad records
 
     const TileP& tp = p.tp;
@@ -240,7 +239,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     const unsigned gw = blockIdx.x * WPB + warp, nw = gridDim.x * WPB;
 
     if (threadIdx.x < 6u) s_acc[threadIdx.x] = 0u;
-    if (lane == 0) { mbar_init(&s_bar[warp][0], 1u); mbar_init(&s_bar[warp][1], 1u); }
+    if (lane == 0) mbar_init(&s_bar[warp], 1u);
     for (unsigned q = lane; q < T2; q += 32u) s_n[q] = 0ull;
     if (gw == 0u && lane == 0u) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
     __syncthreads();
@@ -250,43 +249,44 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     c.tmax = p.max_steps > 0 ? p.max_steps : 0x7FFFFFFF;
     c.eps_thr = !(c.eps > 0.0f) ? 0u : c.eps >= 1.0f ? (1u << 24) : (unsigned)ceilf(c.eps * 16777216.0f);   // scaling by 2^24 is exact
     const unsigned n_spill = min(tp.tctl[(unsigned)(g % 3ull)], p.N);
-    unsigned goals = 0, timeouts = 0, conf = 0, nbig = 0, nbigent = 0, bad = 0;
+    unsigned conf = 0;     // the rarer counters go straight to the block's shared-memory words
 
-    // Border cells this lane reports at the end of a tile: entry k = lane + 32 r of the ring (north row, south row, west
-    // column, east column), its cell inside the tile, and where it goes in the neighbour's block of the border array.
+    // Border cells a lane reports at the end of a tile: entry k = lane + 32 r of the ring (north row, south row, west column,
+    // east column): its cell inside the tile, and where it goes in the neighbour's block of the border array -- my north row is
+    // the south halo (slot 1) of the tile above, my south row the north halo (0) of the tile below, west -> east (3), east -> west (2).
     constexpr unsigned BR = (4u * T + 31u) / 32u;
-    unsigned b_ic[BR]; int b_dst[BR];
-#pragma unroll
-    for (unsigned r = 0; r < BR; ++r) {
-        const unsigned k = lane + 32u * r, e = k >> TSH, i = k & (T - 1u);
-        b_ic[r] = e == 0u ? i : e == 1u ? ((T - 1u) << TSH) + i : e == 2u ? (i << TSH) : (i << TSH) + T - 1u;
-        // my north row is the south halo (slot 1) of the tile above, my south row the north halo (0) of the tile below, west -> east (3), east -> west (2)
+    auto ring_cell = [&](unsigned k) -> unsigned {
+        const unsigned e = k >> TSH, i = k & (T - 1u);
+        return e == 0u ? i : e == 1u ? ((T - 1u) << TSH) + i : e == 2u ? (i << TSH) : (i << TSH) + T - 1u;
+    };
+    auto ring_dst = [&](unsigned k) -> int {
+        const unsigned e = k >> TSH, i = k & (T - 1u);
         const int dtile = e == 0u ? -(int)tp.tiles_x : e == 1u ? (int)tp.tiles_x : e == 2u ? -1 : 1;
         const unsigned slot = e == 0u ? 1u : e == 1u ? 0u : e == 2u ? 3u : 2u;
-        b_dst[r] = (dtile * 4 + (int)slot) * (int)T + (int)i;
-    }
+        return (dtile * 4 + (int)slot) * (int)T + (int)i;
+    };
 
     // Header of a tile: lane 0 loads {region start, capacity}, lane 1 {records in the region, arrivals}; the words
     // are only exchanged when the tile's copies are issued, one tile after the loads.
     const uint2* hdr_src = lane == 0u ? tp.reg : tp.cnt[par];
     auto fetch_hdr = [&](unsigned tile) -> uint2 { return (tile < tp.ntiles && lane < 2u) ? hdr_src[tile] : make_uint2(0u, 0u); };
-    struct Hdr { unsigned roff, fcap, n_front, n_in; int tx0, ty0; unsigned txi, tyi; };
-    // Issue the copies of a tile into a stage and fetch its first records into registers.
-    auto issue = [&](unsigned tile, unsigned stage, const uint2 hw, Hdr& h, int4 (&rec)[PRE]) {
-        h.roff = __shfl_sync(FULL, hw.x, 0); h.fcap = __shfl_sync(FULL, hw.y, 0);
-        h.n_front = min(__shfl_sync(FULL, hw.x, 1), h.fcap); h.n_in = h.n_front + min(__shfl_sync(FULL, hw.y, 1), ARR_CAP);
-        h.tx0 = (int)(h.txi << TSH); h.ty0 = (int)(h.tyi << TSH);
-        unsigned long long* bar = &s_bar[warp][stage];
-        unsigned char* st = wb + stage * L::STAGE;
+    // Issue the copies of a tile and fetch its first records into registers.  (One stage: a second one, with the next tile's
+    // copies in flight during the work, cost more in registers and resident warps than it hid: 176 us against 127 us per step.)
+    unsigned roff = 0, fcap = 0, n_front = 0, n_in = 0;
+    int4 pre[PRE];
+    unsigned long long* const bar = &s_bar[warp];
+    auto issue = [&](unsigned tile, unsigned txi, unsigned tyi, const uint2 hw) {
+        roff = __shfl_sync(FULL, hw.x, 0); fcap = __shfl_sync(FULL, hw.y, 0);
+        n_front = min(__shfl_sync(FULL, hw.x, 1), fcap); n_in = n_front + min(__shfl_sync(FULL, hw.y, 1), ARR_CAP);
         if (lane == 0u) mbar_arrive_expect_tx(bar, L::TX_BYTES);
         __syncwarp();
-        if (lane == 0u) tensor_g2s_2d(st, &tp.tmq, h.tx0 * 4, h.ty0, bar);
-        else if (lane == 1u) bulk_g2s(st + L::ST_MV, tp.tcls + (size_t)tile * L::CLS, L::CLS, bar);
-        else if (lane == 2u) bulk_g2s(st + L::ST_HALO, halo_in + (size_t)tile * (4u * T), 4u * T * 4u, bar);
+        if (lane == 0u) tensor_g2s_2d(wb, &tp.tmq, (int)(txi << TSH) * 4, (int)(tyi << TSH), bar);
+        else if (lane == 1u) bulk_g2s(wb + L::ST_MV, tp.tcls + (size_t)tile * L::CLS, L::CLS, bar);
+        else if (lane == 2u) bulk_g2s(wb + L::ST_HALO, halo_in + (size_t)tile * (4u * T), 4u * T * 4u, bar);
 #pragma unroll
         for (unsigned q = 0; q < PRE; ++q) {
             const unsigned j = q * 32u + lane;
-            rec[q] = j < h.n_front ? in[h.roff + j] : j < h.n_in ? arr_in[(size_t)tile * ARR_CAP + (j - h.n_front)] : make_int4(0, 0, 0, 0);
+            pre[q] = j < n_front ? in[roff + j] : j < n_in ? arr_in[(size_t)tile * ARR_CAP + (j - n_front)] : make_int4(0, 0, 0, 0);
         }
     };
     // A record that leaves its tile: one atomic on the new tile's arrival counter, then the store.  The fast path issues the
@@ -295,49 +295,31 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
         if (apos < ARR_CAP) arr_out[(size_t)dt * ARR_CAP + apos] = r;
         else {
             const unsigned qq = atomicAdd(ovf_cnt_next, 1u);
-            if (qq < p.N) ovf_out[qq] = r; else bad = 1u;
+            if (qq < p.N) ovf_out[qq] = r; else s_acc[5] = 1u;
         }
     };
 
-    Hdr hc{}, hn{};
-    int4 pre[PRE], nxt[PRE];
     const unsigned dty = nw / tp.tiles_x, dtx = nw - dty * tp.tiles_x;
-    hn.tyi = gw / tp.tiles_x; hn.txi = gw - hn.tyi * tp.tiles_x;
+    unsigned tyi = gw / tp.tiles_x, txi = gw - tyi * tp.tiles_x, phase = 0;
     uint2 hw = fetch_hdr(gw);
-    if (gw < tp.ntiles) { issue(gw, 0u, hw, hn, nxt); hw = fetch_hdr(gw + nw); }
     bool pend = false; int4 pend_rec = make_int4(0, 0, 0, 0); unsigned pend_dt = 0, pend_pos = 0;
 
-    unsigned k = 0;
-    for (unsigned tile = gw; tile < tp.ntiles; tile += nw, ++k) {
-        const unsigned stage = NST == 2u ? (k & 1u) : 0u, phase = NST == 2u ? ((k >> 1) & 1u) : (k & 1u);
-        hc = hn;
-#pragma unroll
-        for (unsigned q = 0; q < PRE; ++q) pre[q] = nxt[q];
-        // ---- the next tile's copies and records: with two stages they go out before this tile is touched, else after it ----
-        auto issue_next = [&]() {
-            if (tile + nw < tp.ntiles) {
-                hn.txi = hc.txi + dtx; hn.tyi = hc.tyi + dty;
-                if (hn.txi >= tp.tiles_x) { hn.txi -= tp.tiles_x; ++hn.tyi; }
-                issue(tile + nw, NST == 2u ? (stage ^ 1u) : 0u, hw, hn, nxt);
-                hw = fetch_hdr(tile + 2u * nw);
-            }
-        };
-        if (NST == 2u) issue_next();
-        const unsigned roff = hc.roff, fcap = hc.fcap, n_front = hc.n_front, n_in = hc.n_in, n_all = n_in + n_spill;
-        const int tx0 = hc.tx0, ty0 = hc.ty0;
-        const unsigned txi = hc.txi, tyi = hc.tyi;
-        unsigned char* st = wb + stage * L::STAGE;
+    for (unsigned tile = gw; tile < tp.ntiles; tile += nw) {
+        issue(tile, txi, tyi, hw);
+        hw = fetch_hdr(tile + nw);                              // in flight while this tile is worked on
+        const unsigned n_all = n_in + n_spill;
+        const int tx0 = (int)(txi << TSH), ty0 = (int)(tyi << TSH);
+        const unsigned char* st = wb;
         const float4* s_q = reinterpret_cast<const float4*>(st);
-        const unsigned sq = sbase + stage * L::STAGE, smv = sq + L::ST_MV, shalo = sq + L::ST_HALO;
-        c.s_q = s_q; c.s_mv = st + L::ST_MV; c.s_halo = reinterpret_cast<const float*>(st + L::ST_HALO);
+        const unsigned sq = sbase, smv = sq + L::ST_MV, shalo = sq + L::ST_HALO;
 
-        if (!__all_sync(FULL, mbar_wait(&s_bar[warp][stage], phase, tp.wait_polls))) {
+        if (!__all_sync(FULL, mbar_wait(bar, phase, tp.wait_polls))) {
             // Never seen with the time bound.  Flag it, let the copies land (they target this warp's shared memory), stop.
             if (lane == 0u) atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT);
-            mbar_wait(&s_bar[warp][stage], phase, 0u);
-            if (NST == 2u && tile + nw < tp.ntiles) mbar_wait(&s_bar[warp][stage ^ 1u], ((k + 1u) >> 1) & 1u, 0u);
+            mbar_wait(bar, phase, 0u);
             break;
         }
+        phase ^= 1u;
 
         // stays: position in the tile's own region from a ballot.  Gives back whether the record still has to go somewhere else.
         unsigned nstay = 0;
@@ -357,13 +339,14 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             // counts itself; the FIRST to count on a (cell, action) owns it and, once every count is in, applies the
             // map that many times to the one table entry: a 4-byte store into the table, and into the tile in shared
             // memory, which thereby becomes Q_{t+1} for the border values.
-            unsigned rw0[PRE], rw1[PRE], key[PRE]; float dd[PRE];
+            unsigned key[PRE]; float dd[PRE];
+            unsigned draws = 0u;                                 // per record 3 bits: explore, random action
 #pragma unroll
             for (unsigned q = 0; q < PRE; ++q) {                 // the random draws first: independent chains the scheduler can interleave
-                key[q] = 0u; dd[q] = 0.0f; rw0[q] = 0u; rw1[q] = 0u;
+                key[q] = 0u; dd[q] = 0.0f;
                 if (q * 32u < n_all) {
                     const U4 w = philox4x32_10(p.env_offset + (unsigned)pre[q].w, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
-                    rw0[q] = w.x; rw1[q] = w.y;
+                    draws |= ((((w.x >> 8) < c.eps_thr) ? 4u : 0u) | (w.y & 3u)) << (3u * q);
                 }
             }
             unsigned nleave = 0;
@@ -373,14 +356,14 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 const int4 rec = pre[q];
                 const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
                 bool act = q * 32u + lane < n_all;
-                if (act && (lx | ly) >= T) { bad = 1u; act = false; }             // never seen: the record does not lie in this tile
+                if (act && (lx | ly) >= T) { s_acc[5] = 1u; act = false; }             // never seen: the record does not lie in this tile
                 int4 nrec = rec; bool stays = false;
                 if (act) {
                     const unsigned ic = (ly << TSH) | lx;
                     const float4 row = lds_f4(sq + ic * 16u);
                     const unsigned mvb = lds_u8(smv + ic);
                     int a = argmax4(row);
-                    if ((rw0[q] >> 8) < c.eps_thr) a = (int)(rw1[q] & 3u);
+                    if ((draws >> (3u * q)) & 4u) a = (int)((draws >> (3u * q)) & 3u);
                     const bool blocked = (mvb >> a) & 1u, done = (mvb >> (a + 4)) & 1u;
                     // per action: dx = {0, 1, 0, -1}, dy = {-1, 0, 1, 0}, one signed byte each
                     const int dx = blocked ? 0 : (int)(signed char)(0xFF000100u >> (8 * a)), dy = blocked ? 0 : (int)(signed char)(0x000100FFu >> (8 * a));
@@ -400,7 +383,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                         const unsigned sn2 = sample_start(p, p.env_offset + (unsigned)rec.w, g + 1ull, TAG_START);
                         nrec.y = (int)(sn2 / (unsigned)p.W); nrec.x = (int)(sn2 - (unsigned)nrec.y * (unsigned)p.W); nrec.z = 0;
                         stays = (((unsigned)(nrec.x - tx0)) | ((unsigned)(nrec.y - ty0))) < T;
-                        if (done) ++goals; else ++timeouts;
+                        atomicAdd(&s_acc[done ? 0 : 1], 1u);
                     }
                 }
                 // a record that leaves is queued in shared memory; its atomic goes out when the tile is done
@@ -427,15 +410,14 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 if (tot > 1u) conf += n;
                 if (tot > CROWDED_CELL) {                                              // the lowest chosen action speaks for the cell
                     const unsigned long long ww = ((unsigned long long)w.y << 32) | w.x;
-                    if ((ww & ((1ull << (16u * a)) - 1ull)) == 0ull) { ++nbig; nbigent += tot; }
+                    if ((ww & ((1ull << (16u * a)) - 1ull)) == 0ull) { atomicAdd(&s_acc[3], 1u); atomicAdd(&s_acc[4], tot); }
                 }
                 float v = lds_f32(sq + idx * 4u);
                 for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(dd[q], v), v);      // one application per environment
                 sts_f32(sq + idx * 4u, v);
                 qtile[((ic >> TSH) * (unsigned)p.W + (ic & (T - 1u))) * 4u + a] = v;    // (row inside the tile) * W + column < cells < 2^28
             }
-            // the previous tile's leavers: their counter values have arrived by now
-            if (pend) store_arrival(pend_rec, pend_dt, pend_pos);
+            // the tile's leavers: one atomic each now, the store after the border values (the counter value is on its way meanwhile)
             pend = lane < min(nleave, 32u);
             __syncwarp();
             if (pend) {
@@ -470,12 +452,12 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 if (act && j >= n_in) { rec = ovf_in[j - n_in]; act = tile_of(tp, rec.x, rec.y) == tile; }
                 else if (act && it >= PRE) rec = j < n_front ? in[roff + j] : arr_in[(size_t)tile * ARR_CAP + (j - n_front)];
                 const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
-                if (act && (lx | ly) >= T) { bad = 1u; act = false; }
+                if (act && (lx | ly) >= T) { s_acc[5] = 1u; act = false; }
                 int4 nrec = rec; bool stays = false;
                 if (act) {
                     const unsigned ic = (ly << TSH) | lx, e = (unsigned)rec.w;
                     const U4 w = philox4x32_10(p.env_offset + e, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
-                    const unsigned mvb = c.s_mv[ic];
+                    const unsigned mvb = st[L::ST_MV + ic];
                     const int a = ((w.x >> 8) < c.eps_thr) ? (int)(w.y & 3u) : argmax4(s_q[ic]);
                     const bool blocked = (mvb >> a) & 1u, done = (mvb >> (4 + a)) & 1u;
                     const int dx = blocked ? 0 : (a == 1) - (a == 3), dy = blocked ? 0 : (a == 2) - (a == 0);
@@ -487,7 +469,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     if (done || nrec.z >= c.tmax) {
                         const unsigned sn2 = sample_start(p, p.env_offset + e, g + 1ull, TAG_START);
                         nrec.y = (int)(sn2 / (unsigned)p.W); nrec.x = (int)(sn2 - (unsigned)nrec.y * (unsigned)p.W); nrec.z = 0;
-                        if (done) ++goals; else ++timeouts;
+                        atomicAdd(&s_acc[done ? 0 : 1], 1u);
                     }
                     stays = (((unsigned)(nrec.x - tx0)) | ((unsigned)(nrec.y - ty0))) < T;
                 }
@@ -508,7 +490,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 }
             } else nocc = gcnt ? T2 : 0u;
 #pragma unroll
-            for (unsigned r = 0; r < BR; ++r) if (lane + 32u * r < 4u * T) s_bm[lane + 32u * r] = max4(s_q[b_ic[r]]);
+            for (unsigned r = 0; r < BR; ++r) if (lane + 32u * r < 4u * T) s_bm[lane + 32u * r] = max4(s_q[ring_cell(lane + 32u * r)]);
             __syncwarp();
 
             // ---- Q_{t+1} of the occupied cells, from Q_t in shared memory straight into the table -----------------
@@ -526,8 +508,8 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 }
                 if (!tot) continue;
                 if (tot > 1u) conf += tot;
-                if (tot > CROWDED_CELL) { ++nbig; nbigent += tot; }
-                const float4 row = updated_row<TSH>(p, c, ic, w, crowded ? n32 : nullptr);
+                if (tot > CROWDED_CELL) { atomicAdd(&s_acc[3], 1u); atomicAdd(&s_acc[4], tot); }
+                const float4 row = updated_row<TSH>(p, st, ic, w, crowded ? n32 : nullptr);
                 const unsigned lx = ic & (T - 1u), ly = ic >> TSH;
                 p.Q[(size_t)(ty0 + (int)ly) * (size_t)p.W + (size_t)(tx0 + (int)lx)] = row;
                 const float mx = max4(row);
@@ -548,27 +530,19 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             for (unsigned r = 0; r < BR; ++r) {
                 const unsigned kk = lane + 32u * r, e = kk >> TSH;
                 const bool there = kk < 4u * T && (e == 0u ? tyi > 0u : e == 1u ? tyi + 1u < tp.tiles_y : e == 2u ? txi > 0u : txi + 1u < tp.tiles_x);
-                if (there) hbase[b_dst[r]] = fast ? max4(lds_f4(sq + b_ic[r] * 16u)) : s_bm[kk];
+                if (there) hbase[ring_dst(kk)] = fast ? max4(lds_f4(sq + ring_cell(kk) * 16u)) : s_bm[kk];
             }
         }
+        if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
         fence_async_smem();                                      // this lane's reads of the stage come before the copies that will refill it
         __syncwarp();                                            // every lane is done with the tile
-        if (NST == 1u) issue_next();
+        txi += dtx; tyi += dty;
+        if (txi >= tp.tiles_x) { txi -= tp.tiles_x; ++tyi; }
     }
-    if (pend) store_arrival(pend_rec, pend_dt, pend_pos);
 
     // ---- run statistics: warp -> block -> one atomic per counter and block ----------------------------------
-    for (int o = 16; o; o >>= 1) {
-        goals += __shfl_xor_sync(FULL, goals, o); timeouts += __shfl_xor_sync(FULL, timeouts, o); conf += __shfl_xor_sync(FULL, conf, o);
-        nbig += __shfl_xor_sync(FULL, nbig, o); nbigent += __shfl_xor_sync(FULL, nbigent, o); bad |= __shfl_xor_sync(FULL, bad, o);
-    }
-    if (lane == 0u) {
-        if (goals) atomicAdd(&s_acc[0], goals);
-        if (timeouts) atomicAdd(&s_acc[1], timeouts);
-        if (conf) atomicAdd(&s_acc[2], conf);
-        if (nbig) { atomicAdd(&s_acc[3], nbig); atomicAdd(&s_acc[4], nbigent); }
-        if (bad) atomicOr(&s_acc[5], 1u);
-    }
+    for (int o = 16; o; o >>= 1) conf += __shfl_xor_sync(FULL, conf, o);
+    if (lane == 0u && conf) atomicAdd(&s_acc[2], conf);
     __syncthreads();
     if (threadIdx.x == 0) {
         if (s_acc[2]) atomicAdd(&p.ctl->conflicts, (unsigned long long)s_acc[2]);

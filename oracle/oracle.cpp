@@ -20,6 +20,10 @@
 #include <cmath>
 #include <vector>
 #include <thread>
+#include <mutex>
+#include <condition_variable>
+#include <functional>
+#include <unordered_map>
 #include <algorithm>
 #include <string>
 #include "../include/cudarl.h"
@@ -51,6 +55,40 @@ const uint32_t TAG_GRID = 0x47524944u, TAG_WALL = 0x57414C4Cu, TAG_GOAL = 0x474F
 inline uint32_t mulhi32(uint32_t a, uint32_t b) { return (uint32_t)(((uint64_t)a * b) >> 32); }
 inline float u01(uint32_t w) { return (float)(w >> 8) * 5.9604644775390625e-08f; }  // * 2^-24
 
+// Worker threads that live as long as the oracle: run(f) calls f(k) on thread k for k = 0..T-1 (the caller is thread 0)
+// and returns when all are done.  Timing runs use it; results never depend on the number of threads.
+struct Pool {
+    int T = 1; std::vector<std::thread> th;
+    std::mutex mu; std::condition_variable cv_go, cv_done;
+    std::function<void(int)> job; uint64_t gen = 0; int left = 0; bool stop = false;
+    void start(int threads) {
+        shutdown(); T = threads < 1 ? 1 : threads; stop = false;
+        for (int k = 1; k < T; ++k) th.emplace_back([this, k] {
+            uint64_t seen = 0;
+            for (;;) {
+                std::function<void(int)> f;
+                { std::unique_lock<std::mutex> l(mu); cv_go.wait(l, [&] { return stop || gen != seen; }); if (stop) return; seen = gen; f = job; }
+                f(k);
+                { std::lock_guard<std::mutex> l(mu); if (--left == 0) cv_done.notify_one(); }
+            }
+        });
+    }
+    void run(const std::function<void(int)>& f) {
+        if (T <= 1) { f(0); return; }
+        { std::lock_guard<std::mutex> l(mu); job = f; left = T - 1; ++gen; }
+        cv_go.notify_all();
+        f(0);
+        std::unique_lock<std::mutex> l(mu); cv_done.wait(l, [&] { return left == 0; });
+    }
+    void shutdown() {
+        { std::lock_guard<std::mutex> l(mu); stop = true; }
+        cv_go.notify_all();
+        for (auto& t : th) t.join();
+        th.clear();
+    }
+    ~Pool() { shutdown(); }
+};
+
 struct Oracle {
     cudarl_config cfg;
     int W, H; int64_t S, N;
@@ -70,6 +108,21 @@ struct Oracle {
     // scratch of a train step
     std::vector<int32_t> ps; std::vector<uint8_t> pa; std::vector<float> pd;
     std::vector<uint32_t> occ; bool count_conflicts = true;
+    std::unordered_map<int64_t, float> traps;      // cell -> penalty in (-1, 0); the cell is an obstacle as well (src/kernels.cu:29-36,61-63)
+    Pool pool;
+    std::vector<std::vector<int32_t>> bins;        // [thread * T + stripe]: transitions of that thread's environments whose cell lies in the stripe
+
+    // Reward of a step that did not end on a goal, given the cell the action pointed at: the step cost, or the penalty of a
+    // trap the agent walked into (it does not move: a trap is an obstacle) -- src/kernels.cu:47,61-63.
+    float step_reward(int x, int y, int action) const {
+        if (traps.empty()) return -0.01f;
+        int dx = 0, dy = 0;
+        switch (action) { case 0: dy = -1; break; case 1: dx = 1; break; case 2: dy = 1; break; case 3: dx = -1; break; default: break; }
+        const int nx = x + dx, ny = y + dy;
+        if (nx < 0 || nx >= W || ny < 0 || ny >= H) return -0.01f;
+        auto it = traps.find((int64_t)ny * W + nx);
+        return it == traps.end() ? -0.01f : it->second;
+    }
 
     uint32_t key1(uint32_t tag) const { return k1base ^ tag; }
     bool is_obst(int64_t c) const { return cells[c] == 1; }
@@ -220,27 +273,20 @@ float epsilon_for_step(Oracle& o) {
     return (float)c.eps0;
 }
 
-template <class F> void parallel_for(int threads, int64_t n, F f) {
-    if (threads <= 1 || n < 4096) { f(0, n, 0); return; }
-    std::vector<std::thread> th;
-    int64_t chunk = (n + threads - 1) / threads;
-    for (int k = 0; k < threads; ++k) {
-        int64_t lo = k * chunk, hi = std::min(n, lo + chunk);
-        if (lo >= hi) break;
-        th.emplace_back([=] { f(lo, hi, k); });
-    }
-    for (auto& t : th) t.join();
-}
-
 // One batched train step.  Phase 1 reads only Q_t (so it may run on several threads); phase 2
 // folds the TD errors into the table in ascending environment index.
 void train_step(Oracle& o, float eps) {
     const cudarl_config& c = o.cfg;
     const uint64_t g = (uint64_t)o.step;
     o.eps_last = eps;
-    std::vector<int64_t> ep(o.threads, 0), go(o.threads, 0), to(o.threads, 0);
+    const int T = (o.threads > 1 && o.N >= 4096) ? o.threads : 1;
+    if (T > 1 && o.pool.T != T) o.pool.start(T);
+    std::vector<int64_t> ep(T, 0), go(T, 0), to(T, 0);
     std::vector<int32_t> nxs(o.N), nys(o.N), nts(o.N);
-    parallel_for(o.threads, o.N, [&](int64_t lo, int64_t hi, int tid) {
+    const int64_t chunk = (o.N + T - 1) / T, stripe = (o.S + T - 1) / T;
+    if (T > 1) { o.bins.resize((size_t)T * T); for (auto& b : o.bins) b.clear(); }
+    auto phase1 = [&](int tid) {
+        const int64_t lo = tid * chunk, hi = std::min(o.N, lo + chunk);
         for (int64_t i = lo; i < hi; ++i) {
             uint32_t gi = (uint32_t)(c.env_offset + i);
             int x = o.x[i], y = o.y[i];
@@ -251,12 +297,13 @@ void train_step(Oracle& o, float eps) {
             int a = (u01(w.v[0]) < eps) ? (int)(w.v[1] & 3u) : argmax4(row);
             int64_t s2 = move_cell(o, x, y, a);
             bool done = o.is_goal(s2);                       // src/environment.cu:43-46
-            float r = done ? 1.0f : -0.01f;                  // src/environment.cu:40,44
+            float r = done ? 1.0f : o.step_reward(x, y, a);  // src/environment.cu:40,44; trap: src/kernels.cu:61-63
             float m = 0.0f;                                  // src/kernels.cu:100-110
             if (!done) { m = max4(&o.q[s2 * 4]); if (c.legacy_clamp && m < 0.0f) m = 0.0f; }
             float target = std::fmaf(c.gamma, m, r);         // src/kernels.cu:113 as nvcc contracts it
             o.ps[i] = (int32_t)s; o.pa[i] = (uint8_t)a; o.pd[i] = target;
             o.tr_a[i] = a; o.tr_r[i] = r; o.tr_d[i] = done ? 1 : 0;
+            if (T > 1) o.bins[(size_t)tid * T + (size_t)(s / stripe)].push_back((int32_t)i);
             // episode bookkeeping: src/train.py:191-222 (reset on done or after max_steps)
             bool timeout = c.max_steps > 0 && o.t[i] + 1 >= c.max_steps;
             if (done || timeout) {
@@ -267,32 +314,26 @@ void train_step(Oracle& o, float eps) {
                 nxs[i] = (int32_t)(s2 % o.W); nys[i] = (int32_t)(s2 / o.W); nts[i] = o.t[i] + 1;
             }
         }
-    });
+    };
     // Phase 2: the reference update Q[s,a] = fma(lr, target - Q[s,a], Q[s,a]) (src/kernels.cu:113-114 as compiled)
     // applied one transition after the other in environment order: an update of the same (s,a) sees the value
     // the previous one left; the targets were taken from Q_t in phase 1.  (The reference kernel leaves
     // same-(s,a) collisions to a data race.)
-    if (o.threads <= 1) {
+    if (T <= 1) {
+        phase1(0);
         for (int64_t i = 0; i < o.N; ++i) {
             float* p = &o.q[(int64_t)o.ps[i] * 4 + o.pa[i]];
             *p = std::fmaf(c.lr, o.pd[i] - *p, *p);
         }
     } else {
-        // Same fold, split by cell stripe: each thread applies, in environment order, the updates
-        // whose state falls in its stripe, so the per-(s,a) order is unchanged.
-        int T = o.threads; int64_t stripe = (o.S + T - 1) / T;
-        std::vector<std::thread> th;
-        for (int k = 0; k < T; ++k) {
-            int64_t clo = k * stripe, chi = std::min(o.S, clo + stripe);
-            if (clo >= chi) break;
-            th.emplace_back([&o, &c, clo, chi] {
-                for (int64_t i = 0; i < o.N; ++i) {
-                    int64_t s = o.ps[i];
-                    if (s >= clo && s < chi) { float* p = &o.q[s * 4 + o.pa[i]]; *p = std::fmaf(c.lr, o.pd[i] - *p, *p); }
-                }
-            });
-        }
-        for (auto& t : th) t.join();
+        // Same fold, split by cell stripe: thread k applies the updates whose cell falls in stripe k.  Phase 1 has sorted every
+        // thread's transitions into stripes already; visiting the source threads in order 0..T-1 (their environments are
+        // ascending ranges) keeps every (s,a) in ascending environment index.
+        o.pool.run(phase1);
+        o.pool.run([&](int k) {
+            for (int j = 0; j < T; ++j)
+                for (int32_t i : o.bins[(size_t)j * T + k]) { float* p = &o.q[(int64_t)o.ps[i] * 4 + o.pa[i]]; *p = std::fmaf(c.lr, o.pd[i] - *p, *p); }
+        });
     }
     if (o.count_conflicts) {
         if ((int64_t)o.occ.size() != o.S) o.occ.assign(o.S, 0);
@@ -301,7 +342,7 @@ void train_step(Oracle& o, float eps) {
         for (int64_t i = 0; i < o.N; ++i) o.occ[o.ps[i]] = 0;
     }
     o.x.swap(nxs); o.y.swap(nys); o.t.swap(nts);
-    for (int k = 0; k < o.threads; ++k) { o.episodes += ep[k]; o.goals += go[k]; o.timeouts += to[k]; }
+    for (int k = 0; k < T; ++k) { o.episodes += ep[k]; o.goals += go[k]; o.timeouts += to[k]; }
     o.step += 1;
     if (c.eps_kind == CUDARL_EPS_MULT_PER_STEP) o.eps_running *= (double)c.eps_decay;
 }
@@ -342,9 +383,10 @@ void orc_reset_all(void* h) { reset_all(*(Oracle*)h); }
 void orc_step_actions(void* h, const int32_t* actions, float* rewards, uint8_t* dones) {
     Oracle& o = *(Oracle*)h;
     for (int64_t i = 0; i < o.N; ++i) {
+        const float r0 = o.step_reward(o.x[i], o.y[i], actions[i]);
         int64_t s2 = move_cell(o, o.x[i], o.y[i], actions[i]);
         o.x[i] = (int32_t)(s2 % o.W); o.y[i] = (int32_t)(s2 / o.W); o.t[i] += 1;
-        o.reward[i] = -0.01f;
+        o.reward[i] = r0;
         if (o.is_goal(s2)) { o.reward[i] = 1.0f; o.done[i] = 1; }
         if (rewards) rewards[i] = o.reward[i];
         if (dones) dones[i] = o.done[i];
@@ -424,12 +466,21 @@ void orc_set_q(void* h, const float* q) { Oracle& o = *(Oracle*)h; std::memcpy(o
 void orc_get_cells(void* h, uint8_t* c) { Oracle& o = *(Oracle*)h; std::memcpy(c, o.cells.data(), o.S); }
 int orc_add_obstacle(void* h, int x, int y) {
     Oracle& o = *(Oracle*)h; if (x < 0 || x >= o.W || y < 0 || y >= o.H) return -1;
-    o.cells[(int64_t)y * o.W + x] = 1; refresh_fallback(o); return 0;
+    o.cells[(int64_t)y * o.W + x] = 1; o.traps.erase((int64_t)y * o.W + x); refresh_fallback(o); return 0;
+}
+// A trap: an obstacle whose penalty (in (-1, 0)) replaces the step cost of an agent that walks into it (src/kernels.cu:61-63;
+// stub at src/environment_bridge.cu:72-78).  Any other penalty leaves a plain obstacle.
+int orc_add_trap(void* h, int x, int y, float penalty) {
+    Oracle& o = *(Oracle*)h; if (x < 0 || x >= o.W || y < 0 || y >= o.H) return -1;
+    const int64_t cell = (int64_t)y * o.W + x;
+    o.cells[cell] = 1; o.traps.erase(cell);
+    if (penalty < 0.0f && penalty > -1.0f) o.traps[cell] = penalty;
+    refresh_fallback(o); return 0;
 }
 int orc_set_goal(void* h, int x, int y) {
     Oracle& o = *(Oracle*)h; if (x < 0 || x >= o.W || y < 0 || y >= o.H) return -1;
     for (auto& c : o.cells) if (c == 2) c = 0;
-    o.cells[(int64_t)y * o.W + x] = 2; refresh_fallback(o); return 0;
+    o.cells[(int64_t)y * o.W + x] = 2; o.traps.erase((int64_t)y * o.W + x); refresh_fallback(o); return 0;
 }
 void orc_get_stats(void* h, cudarl_stats* s) {
     Oracle& o = *(Oracle*)h; std::memset(s, 0, sizeof(*s));
