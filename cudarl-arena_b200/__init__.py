@@ -92,6 +92,8 @@ ABI = {
     "cudarl_get_cells": (C.c_int, [_P, _P]),
     "cudarl_add_obstacle": (C.c_int, [_P, C.c_int32, C.c_int32]),
     "cudarl_set_goal": (C.c_int, [_P, C.c_int32, C.c_int32]),
+    "cudarl_add_trap": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_float]),
+    "cudarl_get_traps": (C.c_int, [_P, C.c_int32, _P, _P, C.POINTER(C.c_int32)]),
     "cudarl_set_legacy_clamp": (C.c_int, [_P, C.c_int]),
     "cudarl_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "cudarl_get_config": (C.c_int, [_P, C.POINTER(Config)]),
@@ -317,6 +319,16 @@ class VecGridWorld:
 
     def set_goal(self, x, y):
         self._ck(self.lib.cudarl_set_goal(self.h, x, y))
+
+    def add_trap(self, x, y, penalty=-0.5):
+        self._ck(self.lib.cudarl_add_trap(self.h, x, y, penalty))
+
+    def get_traps(self):
+        n = C.c_int32()
+        self._ck(self.lib.cudarl_get_traps(self.h, 0, None, None, C.byref(n)))
+        cells, pen = np.empty(n.value, np.int32), np.empty(n.value, np.float32)
+        self._ck(self.lib.cudarl_get_traps(self.h, n.value, _ptr(cells), _ptr(pen), C.byref(n)))
+        return cells, pen
 
     def get_stats(self):
         s = Stats()

@@ -5,6 +5,8 @@
   oracle/liboracle.so   the CPU oracle (test infrastructure)
   oracle/_ref/libref.so the reference's own kernels, compiled from the reference checkout when it
                         is present on this machine (never copied into this repository)
+  tests/cpp/facade_consumer   C++ test program written against the reference's header names (csrc/compat/)
+  oracle/_ref/ref_main_demo   the reference's own src/main.cu, compiled unmodified against csrc/compat/ (same condition)
 
 Run as a script (`python cudarl-arena_b200/build.py`) or through `__graft_entry__.build()`.
 """
@@ -22,7 +24,11 @@ ORACLE_DIR = os.path.join(ROOT, "oracle")
 ORACLE_LIB = os.path.join(ORACLE_DIR, "liboracle.so")
 REF_DIR = os.path.join(ORACLE_DIR, "_ref")
 REF_LIB = os.path.join(REF_DIR, "libref.so")
-REFERENCE_SRC = os.environ.get("CUDARL_REFERENCE_SRC", "/root/reference/src")
+# The reference checkout is only read, and only at build time: CUDARL_REFERENCE_SRC names its src/ directory (default: a
+# checkout called `reference` beside this repository).
+REFERENCE_SRC = os.environ.get("CUDARL_REFERENCE_SRC", os.path.join(os.path.dirname(ROOT), "reference", "src"))
+CONSUMER = os.path.join(ROOT, "tests", "cpp", "facade_consumer")
+REF_DEMO = os.path.join(REF_DIR, "ref_main_demo")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
@@ -110,9 +116,42 @@ def build_ref(force=False):
     return REF_LIB
 
 
+def build_consumer(force=False):
+    """tests/cpp/facade_consumer: a C++ program written against the reference's header names, linked with libcudarl.so."""
+    src = os.path.join(ROOT, "tests", "cpp", "facade_consumer.cpp")
+    if not os.path.exists(src):
+        return None
+    deps = [src, os.path.join(CSRC, "facade.h"), LIB]
+    if not force and _newer(CONSUMER, deps):
+        return CONSUMER
+    _run(["g++", "-O1", "-std=c++17", src, "-o", CONSUMER, "-I" + os.path.join(CSRC, "compat"), "-L" + HERE, "-lcudarl",
+          "-Wl,-rpath,$ORIGIN/../../cudarl-arena_b200"])
+    return CONSUMER
+
+
+def build_ref_demo(force=False):
+    """The reference's own demo program src/main.cu, compiled UNMODIFIED from where it lies against this library's
+    compatibility headers (same include names).  Only where the reference checkout exists; the binary travels."""
+    src = os.path.join(REFERENCE_SRC, "main.cu")
+    if not os.path.exists(src):
+        return REF_DEMO if os.path.exists(REF_DEMO) else None
+    if not force and _newer(REF_DEMO, [src, os.path.join(CSRC, "facade.h"), LIB]):
+        return REF_DEMO
+    os.makedirs(REF_DIR, exist_ok=True)
+    _run([_nvcc(), "-O1", "-std=c++17"] + ARCH + ["-I" + os.path.join(CSRC, "compat"), "-o", REF_DEMO, src, "-L" + HERE, "-lcudarl",
+          "-Xlinker", "-rpath,$ORIGIN/../../cudarl-arena_b200"])
+    return REF_DEMO
+
+
 def build_all(force=False):
     out = {"lib": build_lib(force), "oracle": build_oracle(force)}
     out["pybind"] = build_pybind(force)
+    out["consumer"] = build_consumer(force)
+    try:
+        out["ref_demo"] = build_ref_demo(force)
+    except RuntimeError as e:
+        out["ref_demo"] = None
+        sys.stderr.write("reference demo not built: %s\n" % e)
     try:
         out["ref"] = build_ref(force)
     except RuntimeError as e:  # the reference cross-check is optional

@@ -13,6 +13,7 @@
 #include <cstdlib>
 #include <string>
 #include <vector>
+#include <map>
 #include <new>
 
 using namespace cudarl;
@@ -80,6 +81,8 @@ struct cudarl_ctx {
     cudaStream_t st = nullptr;
     std::string err;
     std::vector<uint8_t> cells;           // host copy of the cell classes
+    std::map<uint32_t, float> traps;      // cell -> penalty; mirrored on the device as a table sorted by cell
+    void* dtraps = nullptr; size_t traps_cap = 0;
     // device buffers
     void *dci = nullptr, *dreward = nullptr, *ddone = nullptr;
     void *dstate[2] = {nullptr, nullptr};   // int4 {x,y,t,id} per environment, and a scratch copy of the same size
@@ -454,7 +457,7 @@ void free_all(cudarl_ctx* c) {
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->dgather, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6],
                     c->dQ, c->drec[0], c->drec[1], c->darr[0], c->darr[1], c->dovf[0], c->dovf[1], c->dbmax[0], c->dbmax[1],
-                    c->dtmeta, c->dtscratch, c->dtcls};
+                    c->dtmeta, c->dtscratch, c->dtcls, c->dtraps};
     for (void* b : bufs) if (b) cudaFree(b);
     if (c->h_eps) cudaFreeHost(c->h_eps);
     for (auto e : c->kev) cudaEventDestroy(e);
@@ -780,18 +783,41 @@ int cudarl_get_cells(cudarl_ctx* c, uint8_t* cells) {
     return 0;
 }
 
-static int set_cell(cudarl_ctx* c, int32_t x, int32_t y, unsigned cls, bool single_goal) {
+// The device copy of the trap table: {cell, penalty bits}, ascending by cell (std::map iterates in that order).
+static int upload_traps(cudarl_ctx* c) {
+    const size_t n = c->traps.size();
+    if (n > c->traps_cap) {
+        CK(cudaStreamSynchronize(c->st));
+        if (c->dtraps) cudaFree(c->dtraps);
+        c->dtraps = nullptr; c->traps_cap = 0;
+        const size_t cap = pow2ceil(n < 64 ? 64 : n);
+        CK(cudaMalloc(&c->dtraps, cap * sizeof(uint2)));
+        c->traps_cap = cap;
+    }
+    std::vector<uint2> h; h.reserve(n);
+    for (auto& t : c->traps) { uint2 e; e.x = t.first; std::memcpy(&e.y, &t.second, 4); h.push_back(e); }
+    if (n) CK(cudaMemcpyAsync(c->dtraps, h.data(), n * sizeof(uint2), cudaMemcpyHostToDevice, c->st));
+    CK(cudaStreamSynchronize(c->st));           // `h` is pageable and dies here
+    c->p.traps = (const uint2*)c->dtraps; c->p.ntraps = (unsigned)n;
+    return 0;
+}
+
+static int set_cell(cudarl_ctx* c, int32_t x, int32_t y, unsigned cls, bool single_goal, const float* trap_penalty = nullptr) {
     if (!c) return -1;
     if (x < 0 || x >= c->p.W || y < 0 || y >= c->p.H) return fail(c, -3, "Invalid state");
     CK(cudaSetDevice(c->cfg.device));
     { int rl = leave_tiles(c); if (rl) return rl; }
     const unsigned cell = (unsigned)y * (unsigned)c->p.W + (unsigned)x;
+    const bool is_trap = trap_penalty && *trap_penalty < 0.0f && *trap_penalty > -1.0f;      // src/kernels.cu:61 of the reference
+    const bool had_trap = c->traps.erase(cell) != 0;
+    if (is_trap) c->traps[cell] = *trap_penalty;
+    if (is_trap || had_trap) { int rt = upload_traps(c); if (rt) return rt; }
     if (single_goal) {
         for (auto& v : c->cells) if (v == 2) v = 0;
         launch_cell_set(c->p, 0, 0, 1, c->st);
     }
     c->cells[cell] = (uint8_t)cls; c->cls_dirty = true;
-    launch_cell_set(c->p, cell, cls == 1 ? CW_OBST : (cls == 2 ? CW_GOAL : 0u), 0, c->st);
+    launch_cell_set(c->p, cell, cls == 1 ? (is_trap ? (CW_OBST | CW_TRAP) : CW_OBST) : (cls == 2 ? CW_GOAL : 0u), 0, c->st);
     CK(cudaGetLastError());
     uint32_t fb = 0xFFFFFFFFu;
     for (uint32_t s = 0; s < c->p.S; ++s) if (c->cells[s] == 0) { fb = s; break; }
@@ -801,6 +827,14 @@ static int set_cell(cudarl_ctx* c, int32_t x, int32_t y, unsigned cls, bool sing
 }
 int cudarl_add_obstacle(cudarl_ctx* c, int32_t x, int32_t y) { return set_cell(c, x, y, 1, false); }
 int cudarl_set_goal(cudarl_ctx* c, int32_t x, int32_t y) { return set_cell(c, x, y, 2, true); }
+int cudarl_add_trap(cudarl_ctx* c, int32_t x, int32_t y, float penalty) { return set_cell(c, x, y, 1, false, &penalty); }
+int cudarl_get_traps(cudarl_ctx* c, int32_t capacity, int32_t* cells, float* penalties, int32_t* count) {
+    if (!c || !count || capacity < 0) return fail(c, -1, "bad argument");
+    *count = (int32_t)c->traps.size();
+    int32_t k = 0;
+    for (auto& t : c->traps) { if (k >= capacity) break; if (cells) cells[k] = (int32_t)t.first; if (penalties) penalties[k] = t.second; ++k; }
+    return 0;
+}
 
 int cudarl_set_legacy_clamp(cudarl_ctx* c, int on) {
     if (!c) return -1;

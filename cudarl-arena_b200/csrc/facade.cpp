@@ -27,7 +27,7 @@ Environment& Environment::operator=(Environment&& o) noexcept {
     if (this != &o) {
         if (ctx_) cudarl_destroy(ctx_);
         env_id_ = o.env_id_; width_ = o.width_; height_ = o.height_; x_ = o.x_; y_ = o.y_;
-        reward_ = o.reward_; done_ = o.done_; ctx_ = o.ctx_; grid_ = std::move(o.grid_); traps_ = std::move(o.traps_);
+        reward_ = o.reward_; done_ = o.done_; ctx_ = o.ctx_; grid_ = std::move(o.grid_);
         o.ctx_ = nullptr;
     }
     return *this;
@@ -38,7 +38,11 @@ void Environment::refresh_grid() {
     check(cudarl_get_cells(ctx_, cells.data()), ctx_, "get_cells");
     grid_.assign(cells.size(), 0.0f);
     for (size_t i = 0; i < cells.size(); ++i) grid_[i] = cells[i] == 2 ? 1.0f : (cells[i] == 1 ? -1.0f : 0.0f);
-    for (auto& t : traps_) grid_[t.first] = t.second;
+    int32_t nt = 0;
+    check(cudarl_get_traps(ctx_, 0, nullptr, nullptr, &nt), ctx_, "get_traps");
+    std::vector<int32_t> tc((size_t)nt); std::vector<float> tpn((size_t)nt);
+    if (nt) check(cudarl_get_traps(ctx_, nt, tc.data(), tpn.data(), &nt), ctx_, "get_traps");
+    for (int32_t k = 0; k < nt; ++k) grid_[(size_t)tc[k]] = tpn[k];      // a trap shows its penalty, as src/kernels.cu:61 reads it
 }
 
 void Environment::reset() {
@@ -49,18 +53,10 @@ void Environment::reset() {
 }
 
 void Environment::step(int action) {
-    // a trap is an obstacle whose penalty replaces the step reward when the agent walks into it
-    float trap_penalty = 0.0f; bool hit_trap = false;
-    if (!traps_.empty()) {
-        int dx = (action == 1) - (action == 3), dy = (action == 2) - (action == 0);
-        int nx = x_ + dx, ny = y_ + dy;
-        if (nx >= 0 && nx < width_ && ny >= 0 && ny < height_)
-            for (auto& t : traps_) if (t.first == ny * width_ + nx) { hit_trap = true; trap_penalty = t.second; }
-    }
     int32_t a = action, x, y; float r; uint8_t d;
-    check(cudarl_step_actions(ctx_, &a, &r, &d), ctx_, "step");
+    check(cudarl_step_actions(ctx_, &a, &r, &d), ctx_, "step");       // obstacles, goals and traps are looked up on the device
     check(cudarl_get_state(ctx_, &x, &y, nullptr), ctx_, "get_state");
-    x_ = x; y_ = y; reward_ = hit_trap ? trap_penalty : r; done_ = d != 0;
+    x_ = x; y_ = y; reward_ = r; done_ = d != 0;
 }
 
 float Environment::getCellValue(int x, int y) const {
@@ -71,15 +67,11 @@ std::vector<float> Environment::getGrid() const { return grid_; }
 
 void Environment::addObstacle(int x, int y) { check(cudarl_add_obstacle(ctx_, x, y), ctx_, "add_obstacle"); refresh_grid(); }
 void Environment::setGoal(int x, int y) { check(cudarl_set_goal(ctx_, x, y), ctx_, "set_goal"); refresh_grid(); }
-void Environment::addTrap(int x, int y, float penalty) {
-    check(cudarl_add_obstacle(ctx_, x, y), ctx_, "add_trap");
-    if (penalty < 0.0f && penalty > -1.0f) traps_.emplace_back(y * width_ + x, penalty);   // src/kernels.cu:61
-    refresh_grid();
-}
+void Environment::addTrap(int x, int y, float penalty) { check(cudarl_add_trap(ctx_, x, y, penalty), ctx_, "add_trap"); refresh_grid(); }
 
 // ---- EnvironmentBridge -------------------------------------------------------------------------
-EnvironmentBridge::EnvironmentBridge(int width, int height) : width(width), height(height) {
-    env = std::make_unique<Environment>(0, width, height);
+EnvironmentBridge::EnvironmentBridge(int width, int height, int env_id) : width(width), height(height) {
+    env = std::make_unique<Environment>(env_id, width, height);
 }
 std::vector<float> EnvironmentBridge::reset() { env->reset(); return getObservation(); }
 std::tuple<std::vector<float>, float, bool, std::string> EnvironmentBridge::step(int action) {

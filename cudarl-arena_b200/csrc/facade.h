@@ -61,13 +61,12 @@ private:
     float reward_ = 0.0f;
     bool done_ = false;
     cudarl_ctx* ctx_ = nullptr;
-    std::vector<float> grid_;                   // host copy of the float view of the cell classes
-    std::vector<std::pair<int, float>> traps_;  // (cell, penalty) for penalties in (-1, 0): src/kernels.cu:61-63
+    std::vector<float> grid_;                   // host copy of the float view of the cell classes and traps
 };
 
 class CUDARL_CXX_API EnvironmentBridge {
 public:
-    EnvironmentBridge(int width = 10, int height = 10);
+    EnvironmentBridge(int width = 10, int height = 10, int env_id = 0);   // env_id: third argument of the reference's second binding (src/bindings/python_bindings.cpp:55-81)
     std::vector<float> reset();
     std::tuple<std::vector<float>, float, bool, std::string> step(int action);
     std::vector<float> getObservation() const;
@@ -78,6 +77,7 @@ public:
     void setGoal(int x, int y);
     void addTrap(int x, int y, float penalty = -1.0f);
     // the duck type python/cudarl/environment.py:62-69,89 of the reference expects from its backend
+    int getEnvId() const { return env->getId(); }
     float getReward() const { return env->getReward(); }
     bool isDone() const { return env->isDone(); }
 private:

@@ -369,7 +369,8 @@ __global__ void k_step_actions(Params p, const int* actions, float* rewards, uns
     int a = actions[e];
     if (a < 0 || a > 3) a = -1;                         // any other value: no movement (src/gpu/environment.cu:31)
     unsigned s2 = move_cell(p, x, y, s, cs, a, c2);
-    float r = -0.01f; unsigned char dn = p.done[e];
+    float r = (s2 == s && a >= 0) ? blocked_step_reward(p, x, y, a) : -0.01f;    // a trap charges its penalty (src/kernels.cu:61-63)
+    unsigned char dn = p.done[e];
     if (c2 & CW_GOAL) { r = 1.0f; dn = 1; }
     p.st[i] = make_int4((int)(s2 % (unsigned)p.W), (int)(s2 / (unsigned)p.W), rec.z + 1, rec.w);
     p.reward[e] = r; p.done[e] = dn;
@@ -460,7 +461,7 @@ __global__ void k_cell_set(Params p, unsigned cell, unsigned cls, int clear_goal
             atomicAnd(w32 + i, ~0x00020002u);
     } else if (blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned sh = (cell & 1u) * 16u;
-        atomicAnd(w32 + (cell >> 1), ~(3u << sh));
+        atomicAnd(w32 + (cell >> 1), ~(7u << sh));
         if (cls) atomicOr(w32 + (cell >> 1), cls << sh);
     }
 }

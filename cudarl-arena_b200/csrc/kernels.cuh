@@ -11,6 +11,7 @@ namespace cudarl {
 enum : unsigned {
     CW_OBST = 1u,      // cell blocks movement                     (src/kernels.cu:29-36 of the reference)
     CW_GOAL = 2u,      // cell ends the episode, reward 1          (src/environment.cu:43-46)
+    CW_TRAP = 4u,      // an obstacle whose penalty replaces the step cost of an agent that walks into it (src/kernels.cu:61-63)
 };
 
 // A chain link names a run of consecutive collision entries: low 26 bits = position of the first entry + 1
@@ -80,6 +81,8 @@ struct Params {
     int legacy_clamp;
     float4* Q;             // the table: S float4, row s = the 4 action values of cell s; every kernel updates it in place
     unsigned short* cw;    // S cell words (padded to 16 bytes)
+    const uint2* traps;    // sparse trap table, ascending by cell: {cell, penalty as float bits}
+    unsigned ntraps;
     // environment state outside train steps: one int4 {x, y, t, id} per environment (all int32, one
     // coalesced 16-byte vector per thread), record k = environment k
     int4* st;

@@ -30,6 +30,7 @@ public:
             F(obstacle_kind, int) F(obstacle_p, float) F(goal_mode, int) F(num_goals, int) F(start_mode, int) F(start_x, int) F(start_y, int)
             F(max_steps, int) F(lr, float) F(gamma, float) F(eps_kind, int) F(eps0, double) F(eps_decay, double) F(eps_end, double)
             F(eps_steps, long long) F(q_init_kind, int) F(q_init_scale, float) F(legacy_clamp, int) F(sync_every, int)
+            F(rebucket_every, int) F(tile_edge, int)
 #undef F
             if (k == "goals") {
                 auto lst = py::cast<std::vector<std::pair<int, int>>>(v);
@@ -74,6 +75,9 @@ public:
         if ((size_t)q.size() != (size_t)cfg_.width * cfg_.height * CUDARL_ACTIONS) throw std::runtime_error("Invalid Q-table size");
         ck(cudarl_set_q(ctx_, q.data()));
     }
+    void add_obstacle(int x, int y) { ck(cudarl_add_obstacle(ctx_, x, y)); }
+    void set_goal(int x, int y) { ck(cudarl_set_goal(ctx_, x, y)); }
+    void add_trap(int x, int y, float penalty) { ck(cudarl_add_trap(ctx_, x, y, penalty)); }
     py::array_t<uint8_t> cells() {
         py::array_t<uint8_t> c({(py::ssize_t)cfg_.height, (py::ssize_t)cfg_.width});
         ck(cudarl_get_cells(ctx_, c.mutable_data()));
@@ -83,6 +87,7 @@ public:
         cudarl_stats s; ck(cudarl_get_stats(ctx_, &s));
         py::dict o; o["steps"] = s.steps; o["env_steps"] = s.env_steps; o["episodes"] = s.episodes; o["goals"] = s.goals;
         o["timeouts"] = s.timeouts; o["conflicts"] = s.conflicts; o["reward_sum"] = s.reward_sum; o["epsilon"] = s.epsilon;
+        o["device_error"] = s.device_error;      // always 0 here: a recorded failure makes the call above throw
         return o;
     }
 private:
@@ -97,8 +102,7 @@ PYBIND11_MODULE(cudarl_core, m) {
 
     py::class_<EnvironmentBridge>(m, "Environment")
         .def(py::init<int, int>(), py::arg("width") = 10, py::arg("height") = 10)
-        .def(py::init([](int width, int height, int) { return new EnvironmentBridge(width, height); }),
-             py::arg("width"), py::arg("height"), py::arg("env_id"))
+        .def(py::init<int, int, int>(), py::arg("width"), py::arg("height"), py::arg("env_id"))
         .def("reset", &EnvironmentBridge::reset)
         .def("step", &EnvironmentBridge::step)
         .def("get_observation", &EnvironmentBridge::getObservation)
@@ -111,7 +115,7 @@ PYBIND11_MODULE(cudarl_core, m) {
         // aliases (second binding / backend duck type of the reference)
         .def_property_readonly("width", &EnvironmentBridge::getWidth)
         .def_property_readonly("height", &EnvironmentBridge::getHeight)
-        .def_property_readonly("env_id", [](const EnvironmentBridge&) { return 0; })
+        .def_property_readonly("env_id", &EnvironmentBridge::getEnvId)
         .def("get_reward", &EnvironmentBridge::getReward)
         .def("is_done", &EnvironmentBridge::isDone)
         .def("get_agent_x", [](const EnvironmentBridge& e) { return e.getAgentPosition().first; })
@@ -138,6 +142,9 @@ PYBIND11_MODULE(cudarl_core, m) {
         .def("q_table", &VecEnvironment::q_table)
         .def("set_q_table", &VecEnvironment::set_q_table)
         .def("cells", &VecEnvironment::cells)
+        .def("add_obstacle", &VecEnvironment::add_obstacle)
+        .def("set_goal", &VecEnvironment::set_goal)
+        .def("add_trap", &VecEnvironment::add_trap, py::arg("x"), py::arg("y"), py::arg("penalty") = -0.5f)
         .def("stats", &VecEnvironment::stats);
 
     m.attr("__version__") = "0.1.0";

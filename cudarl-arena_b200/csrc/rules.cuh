@@ -52,6 +52,24 @@ __device__ __forceinline__ unsigned sample_start(const Params& p, unsigned gi, u
     return p.fallback_start;
 }
 
+// Reward of a step that does not end on a goal, for an agent at (x, y) whose action `a` was blocked: the step cost, or -- when
+// the cell it walked into is a trap -- that trap's penalty (src/kernels.cu:47,61-63 of the reference: a trap is an obstacle, the
+// agent stays where it is and is charged the cell's value).  Binary search in the sparse trap table.
+__device__ __forceinline__ float blocked_step_reward(const Params& p, int x, int y, int a) {
+    if (!p.ntraps) return -0.01f;
+    const int nx = x + (a == 1) - (a == 3), ny = y + (a == 2) - (a == 0);
+    if (nx < 0 || nx >= p.W || ny < 0 || ny >= p.H) return -0.01f;
+    const unsigned tgt = (unsigned)ny * (unsigned)p.W + (unsigned)nx;
+    unsigned lo = 0, hi = p.ntraps;
+    while (lo < hi) {
+        const unsigned mid = (lo + hi) >> 1;
+        const uint2 e = p.traps[mid];
+        if (e.x == tgt) return __uint_as_float(e.y);
+        if (e.x < tgt) lo = mid + 1u; else hi = mid;
+    }
+    return -0.01f;
+}
+
 __device__ __forceinline__ int argmax4(float4 r) {   // first maximum wins
     int b = 0; float bv = r.x;
     if (r.y > bv) { bv = r.y; b = 1; }

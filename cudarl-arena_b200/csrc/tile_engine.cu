@@ -169,7 +169,7 @@ struct StepCtx {
 // TD target of (cell, action) from Q_t:  r + gamma * max_a' Q_t[s'],  0 for the max when the episode ends there.
 // The next cell's max comes from the tile, or from the border values when the move crosses an edge.
 template <unsigned TSH>
-__device__ __forceinline__ float td_target(const Params& p, const float4* s_q, const float* s_halo, unsigned ic, int a, unsigned mvb) {
+__device__ __forceinline__ float td_target(const Params& p, const float4* s_q, const float* s_halo, unsigned ic, int a, unsigned mvb, int tx0, int ty0) {
     constexpr unsigned T = 1u << TSH;
     const bool blocked = (mvb >> a) & 1u, done = (mvb >> (4 + a)) & 1u;
     float m = 0.0f;
@@ -183,13 +183,14 @@ __device__ __forceinline__ float td_target(const Params& p, const float4* s_q, c
         }
         if (p.legacy_clamp && m < 0.0f) m = 0.0f;
     }
-    return __fmaf_rn(p.gamma, m, done ? 1.0f : -0.01f);
+    const float r = done ? 1.0f : blocked ? blocked_step_reward(p, tx0 + (int)(ic & (T - 1u)), ty0 + (int)(ic >> TSH), a) : -0.01f;
+    return __fmaf_rn(p.gamma, m, r);
 }
 
 // Q_{t+1} row of one cell from Q_t and the number of environments that chose each action
 // (`w`: 16 bits per action, or `n32` when the tile counts in 32 bits).  Only the actions that were chosen are visited.
 template <unsigned TSH>
-__device__ __forceinline__ float4 updated_row(const Params& p, const unsigned char* st, unsigned ic, unsigned long long w, const unsigned* n32) {
+__device__ __forceinline__ float4 updated_row(const Params& p, const unsigned char* st, unsigned ic, unsigned long long w, const unsigned* n32, int tx0, int ty0) {
     using L = WarpSmem<TSH>;
     const float4* s_q = reinterpret_cast<const float4*>(st);
     float4 row = s_q[ic];
@@ -199,7 +200,7 @@ __device__ __forceinline__ float4 updated_row(const Params& p, const unsigned ch
     while (mask) {
         const int a = __ffs((int)mask) - 1; mask &= mask - 1u;
         const unsigned n = n32 ? n32[a] : (unsigned)(w >> (16 * a)) & 0xFFFFu;
-        const float d = td_target<TSH>(p, s_q, reinterpret_cast<const float*>(st + L::ST_HALO), ic, a, mvb);
+        const float d = td_target<TSH>(p, s_q, reinterpret_cast<const float*>(st + L::ST_HALO), ic, a, mvb, tx0, ty0);
         float v = pick(row, a);
         for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(d, v), v);       // one application per environment
         row.x = a == 0 ? v : row.x; row.y = a == 1 ? v : row.y; row.z = a == 2 ? v : row.z; row.w = a == 3 ? v : row.w;
@@ -373,8 +374,9 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     if (stays) m = max4(lds_f4(sq + ((my << TSH) | mx) * 16u));
                     else m = lds_f32(shalo + 4u * ((int)my < 0 ? lx : my >= T ? T + lx : (int)mx < 0 ? 2u * T + ly : 3u * T + ly));
                     if (p.legacy_clamp && m < 0.0f) m = 0.0f;
-                    dd[q] = done ? 1.0f : __fmaf_rn(p.gamma, m, -0.01f);              // the TD target of (cell, a), from Q_t
-                    if (TRACE) { p.tr_a[rec.w] = a; p.tr_r[rec.w] = done ? 1.0f : -0.01f; p.tr_d[rec.w] = done ? 1 : 0; }
+                    const float r = (blocked && p.ntraps) ? blocked_step_reward(p, rec.x, rec.y, a) : -0.01f;     // a trap charges its penalty
+                    dd[q] = done ? 1.0f : __fmaf_rn(p.gamma, m, r);                  // the TD target of (cell, a), from Q_t
+                    if (TRACE) { p.tr_a[rec.w] = a; p.tr_r[rec.w] = done ? 1.0f : r; p.tr_d[rec.w] = done ? 1 : 0; }
                     const unsigned idx = ic * 4u + (unsigned)a, sh = 16u * ((unsigned)a & 1u);
                     const unsigned old = atoms_add(sn + (idx >> 1) * 4u, 1u << sh);
                     key[q] = ((((old >> sh) & 0xFFFFu) == 0u) ? 0x40000000u : 0u) | idx;
@@ -462,7 +464,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     const bool blocked = (mvb >> a) & 1u, done = (mvb >> (4 + a)) & 1u;
                     const int dx = blocked ? 0 : (a == 1) - (a == 3), dy = blocked ? 0 : (a == 2) - (a == 0);
                     nrec.x = rec.x + dx; nrec.y = rec.y + dy; nrec.z = rec.z + 1;
-                    if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = done ? 1.0f : -0.01f; p.tr_d[e] = done ? 1 : 0; }
+                    if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = done ? 1.0f : blocked ? blocked_step_reward(p, rec.x, rec.y, a) : -0.01f; p.tr_d[e] = done ? 1 : 0; }
                     // 32-bit shared-memory atomics are native; the 64-bit word of a cell is counted in its two halves
                     if (!crowded) atomicAdd(reinterpret_cast<unsigned*>(s_n) + 2u * ic + ((unsigned)a >> 1), 1u << (16u * ((unsigned)a & 1u)));
                     else if (gcnt) atomicAdd(&gcnt[ic * 4u + (unsigned)a], 1u);
@@ -509,7 +511,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 if (!tot) continue;
                 if (tot > 1u) conf += tot;
                 if (tot > CROWDED_CELL) { atomicAdd(&s_acc[3], 1u); atomicAdd(&s_acc[4], tot); }
-                const float4 row = updated_row<TSH>(p, st, ic, w, crowded ? n32 : nullptr);
+                const float4 row = updated_row<TSH>(p, st, ic, w, crowded ? n32 : nullptr, tx0, ty0);
                 const unsigned lx = ic & (T - 1u), ly = ic >> TSH;
                 p.Q[(size_t)(ty0 + (int)ly) * (size_t)p.W + (size_t)(tx0 + (int)lx)] = row;
                 const float mx = max4(row);

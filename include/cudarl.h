@@ -206,6 +206,17 @@ int cudarl_get_cells(cudarl_ctx* ctx, uint8_t* cells);
 /* EnvironmentBridge::addObstacle / setGoal (src/environment_bridge.cu:53-70; print-only there). */
 int cudarl_add_obstacle(cudarl_ctx* ctx, int32_t x, int32_t y);
 int cudarl_set_goal(cudarl_ctx* ctx, int32_t x, int32_t y);
+/* EnvironmentBridge::addTrap (src/environment_bridge.cu:72-78; print-only there) with the rule of
+ * step_environment_kernel (src/kernels.cu:29-36,61-63): the cell becomes an obstacle, and an agent that
+ * walks into it stays where it is and receives `penalty` instead of the step cost -- in cudarl_step_actions
+ * and in the fused train step alike (the TD target of that (state, action) uses the penalty as its reward).
+ * Only penalties in (-1, 0) make a trap, as in the reference; any other value leaves a plain obstacle.
+ * Kept on the device as a sparse table {cell, penalty} sorted by cell beside the cell classes.
+ * cudarl_stats.reward_sum is derived from the goal and step counters and does not include trap penalties. */
+int cudarl_add_trap(cudarl_ctx* ctx, int32_t x, int32_t y, float penalty);
+/* The traps set so far, ascending by cell (y*width + x): at most `capacity` entries are written, *count
+ * receives how many there are.  cells / penalties may be NULL. */
+int cudarl_get_traps(cudarl_ctx* ctx, int32_t capacity, int32_t* cells, float* penalties, int32_t* count);
 
 /* Switch the max(0, .) clamp of the flat reference kernel (src/kernels.cu:102-110) on or off. */
 int cudarl_set_legacy_clamp(cudarl_ctx* ctx, int on);

@@ -20,7 +20,7 @@ import types
 
 import numpy as np
 
-REF = os.environ.get("CUDARL_REFERENCE", "/root/reference")
+REF = os.environ.get("CUDARL_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 

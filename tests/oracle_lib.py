@@ -46,6 +46,7 @@ def lib():
         L.orc_get_cells.argtypes = [C.c_void_p] * 2
         L.orc_add_obstacle.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.orc_set_goal.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.orc_add_trap.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float]
         L.orc_get_stats.argtypes = [C.c_void_p, C.POINTER(pkg.Stats)]
         L.orc_average_replicas.argtypes = [C.POINTER(C.c_void_p), C.c_int]
         L.orc_philox.argtypes = [C.c_void_p] * 3
@@ -152,6 +153,9 @@ class Oracle:
 
     def set_goal(self, x, y):
         return self.L.orc_set_goal(self.h, x, y)
+
+    def add_trap(self, x, y, penalty=-0.5):
+        return self.L.orc_add_trap(self.h, x, y, penalty)
 
     def get_stats(self):
         s = pkg.Stats()

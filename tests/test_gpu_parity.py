@@ -145,10 +145,23 @@ def test_lockstep_c1(pkg, orc):
     assert s.episodes > 0
 
 
-def test_lockstep_c2(pkg, orc):
-    gpu, cpu = pair(pkg, orc, pkg.preset("C2"))
-    s = lockstep(gpu, cpu, 300, check_every=10, what="C2")
+@pytest.mark.parametrize("edge", [0, 8, 16])
+def test_lockstep_c2(pkg, orc, edge):
+    cfg = pkg.preset("C2")
+    cfg.tile_edge = edge                  # 0 = chosen from the population density; the results never depend on it
+    gpu, cpu = pair(pkg, orc, cfg)
+    s = lockstep(gpu, cpu, 300, check_every=10, what="C2 edge %d" % edge)
     assert s.conflicts > 0
+
+
+@pytest.mark.parametrize("edge", [8, 16])
+def test_lockstep_sparse_population_both_tile_edges(pkg, orc, edge):
+    """The benchmark's density (one environment per four cells, 30 % obstacles, several goals) on a grid whose sides are
+    not multiples of the tile edge: partial tiles at the right and bottom rims, most tiles on the register-held fast path."""
+    cfg = pkg.preset("C5", num_envs=9000)
+    cfg.width, cfg.height, cfg.num_goals, cfg.max_steps, cfg.tile_edge = 203, 181, 6, 50, edge
+    gpu, cpu = pair(pkg, orc, cfg)
+    lockstep(gpu, cpu, 160, check_every=8, what="sparse edge %d" % edge)
 
 
 def test_lockstep_c3_uniform_q_linear_eps(pkg, orc):
@@ -173,6 +186,62 @@ def test_lockstep_one_tile_beyond_16_bit_counts(pkg, orc):
     cfg = pkg.make_config(3, 2, 70000, start_mode=pkg.START_RANDOM, eps_kind=pkg.EPS_FIXED, eps0=0.3, max_steps=5, lr=0.2)
     gpu, cpu = pair(pkg, orc, cfg, threads=4)
     lockstep(gpu, cpu, 8, what="70000 on 3x2")
+
+
+def test_lockstep_with_traps(pkg, orc):
+    """Traps (src/kernels.cu:61-63 of the reference): obstacles that charge their penalty.  The fused step must use the
+    penalty as the reward of the blocked (state, action) in its TD target, the trace must show it, and caller-driven
+    steps must return it."""
+    cfg = pkg.make_config(20, 14, 2500, start_mode=pkg.START_RANDOM, goal_mode=pkg.GOAL_SEEDED, num_goals=2, obstacle_kind=pkg.OBST_BERNOULLI,
+                          obstacle_p=0.1, eps_kind=pkg.EPS_FIXED, eps0=0.5, max_steps=30, lr=0.2)
+    gpu, cpu = pair(pkg, orc, cfg)
+    rng = np.random.RandomState(11)
+    cells = gpu.get_cells()
+    placed = 0
+    for k in rng.permutation(20 * 14):
+        if cells[k] == 0 and placed < 25:
+            pen = float(np.float32(-rng.uniform(0.05, 0.95))) if placed % 5 else -2.0      # every fifth: outside (-1, 0) = a plain obstacle
+            gpu.add_trap(int(k % 20), int(k // 20), pen); cpu.add_trap(int(k % 20), int(k // 20), pen)
+            placed += 1
+    assert np.array_equal(gpu.get_cells(), cpu.get_cells())
+    tc, tp = gpu.get_traps()
+    assert len(tc) == 20 and np.all(np.diff(tc) > 0) and np.all((tp < 0) & (tp > -1))
+    gpu.reset_all(); cpu.reset_all()
+    lockstep(gpu, cpu, 60, check_every=5, what="traps")
+    gpu.set_trace(True); gpu.train_steps(1); cpu.train_steps(1)
+    assert np.array_equal(gpu.get_trace()[1], cpu.get_trace()[1])
+    assert (gpu.get_trace()[1] != np.float32(-0.01)).sum() > (gpu.get_trace()[1] == 1.0).sum()    # some penalties were charged
+    for _ in range(10):
+        a = rng.randint(0, 4, 2500)
+        (r1, d1), (r2, d2) = gpu.step_actions(a), cpu.step_actions(a)
+        assert np.array_equal(r1, r2) and np.array_equal(d1, d2)
+    # a goal or a plain obstacle put on a trap cell removes the trap
+    gpu.add_obstacle(int(tc[0] % 20), int(tc[0] // 20)); cpu.add_obstacle(int(tc[0] % 20), int(tc[0] // 20))
+    assert len(gpu.get_traps()[0]) == 19
+    gpu.train_steps(20); cpu.train_steps(20)
+    assert_same(gpu, cpu, "after removing a trap")
+
+
+def test_copy_wait_that_runs_out_is_reported_not_hung(pkg):
+    """The step kernel bounds every wait for a tile copy.  With the bound set to a single look at the barrier the wait runs out
+    before the copy can have landed: the warp records the failure, lets its copies land and leaves; the next call that waits
+    for the device returns CUDARL_ERR_DEVICE + CUDARL_DEVERR_COPY_TIMEOUT instead of handing out a half-updated table."""
+    cfg = pkg.preset("C3", num_envs=20000)
+    g = pkg.VecGridWorld(cfg)
+    g.train_steps(3); g.synchronize()
+    assert g.get_stats().device_error == 0
+    g.debug_set_copy_wait_polls(1)
+    g.train_steps(1)
+    with pytest.raises(pkg.CudarlError) as ei:
+        g.synchronize()
+    assert ei.value.code == 3000 + 32
+    g.debug_set_copy_wait_polls(0)
+    with pytest.raises(pkg.CudarlError):
+        g.get_q()                                            # the flag is sticky: this context's results are not to be trusted
+    g.close()
+    h = pkg.VecGridWorld(cfg)                                # the device itself is fine
+    h.train_steps(5); h.synchronize()
+    assert h.get_stats().device_error == 0
 
 
 def test_lockstep_legacy_clamp_and_walls(pkg, orc):
@@ -289,13 +358,25 @@ def test_determinism_run_twice(pkg):
 
 
 def test_full_size_c5_lockstep_and_properties(pkg, orc):
-    """The benchmark workload at full size: 4096x4096 cells, 4,194,304 environments.  A few steps against the
-    (multi-threaded) oracle, then invariants that do not need the oracle."""
+    """The benchmark workload at full size: 4096x4096 cells, 4,194,304 environments.  Steps against the (multi-threaded)
+    oracle that cross a re-sizing of the record regions, with one tile crowded beyond the 16-bit counters and a stream of
+    arrivals into one tile that overflows its arrival buffer into the spill list; then invariants that do not need the oracle."""
     cfg = pkg.preset("C5")
+    cfg.rebucket_every = 2
     gpu, cpu = pair(pkg, orc, cfg, threads=os.cpu_count() or 8)
     cpu.count_conflicts(False)
-    assert np.array_equal(gpu.get_cells(), cpu.get_cells())
-    for k in range(3):
+    cells = gpu.get_cells().reshape(4096, 4096)
+    assert np.array_equal(cells.ravel(), cpu.get_cells())
+    x, y, t = gpu.get_state()
+    # 70,000 environments on one free cell inside a tile (32-bit counters), 3,000 on a free cell in the top row of another tile
+    # whose upper neighbour is free too: with an all-zero table the greedy action is "up", so they all arrive in the tile above
+    # in one step -- far more than the 32 arrival slots.
+    ys, xs = np.nonzero(cells[1024:1040, 2048:2064] == 0)
+    x[:70000], y[:70000] = 2048 + xs[0], 1024 + ys[0]
+    cand = [(cx, cy) for cy in range(2064, 2400, 16) for cx in range(512, 528) if cells[cy, cx] == 0 and cells[cy - 1, cx] == 0]
+    x[70000:73000], y[70000:73000] = cand[0]
+    gpu.set_state(x, y, t); cpu.set_state(x, y, t)
+    for k in range(4):
         gpu.train_steps(1); cpu.train_steps(1)
     assert_same(gpu, cpu, "C5 full size")
     cpu.close()
@@ -306,7 +387,7 @@ def test_full_size_c5_lockstep_and_properties(pkg, orc):
     assert np.all(occ == 0)                                  # nobody stands on an obstacle or a goal
     assert t.max() < 16384 and t.min() >= 0
     s = gpu.get_stats()
-    assert s.device_error == 0 and s.steps == 63 and s.env_steps == 63 * (1 << 22)
+    assert s.device_error == 0 and s.steps == 64 and s.env_steps == 64 * (1 << 22)
     assert s.episodes == s.goals + s.timeouts
     q = gpu.get_q()
     assert np.isfinite(q).all() and q.max() <= 1.0 and q.min() >= -1.0

@@ -76,6 +76,38 @@ def test_obstacle_aware_step_kernel_of_the_reference(pkg, ref):
     assert checked > 300
 
 
+def test_trap_rule_of_the_reference_kernel(pkg, ref):
+    """src/kernels.cu:61-63: a grid value in (-1, 0) blocks like an obstacle and is charged as the reward.  Traps set with
+    cudarl_add_trap (the device trap table) against the reference's own step_environment_kernel on the float grid that
+    carries the same penalties; a value of -1 or below is a plain obstacle there and here."""
+    rng = np.random.RandomState(6)
+    checked = charged = 0
+    for trial in range(10):
+        w, h = int(rng.randint(5, 12)), int(rng.randint(5, 12))
+        cfg = pkg.make_config(w, h, 1, seed=2000 + trial, obstacle_kind=pkg.OBST_BERNOULLI, obstacle_p=0.1,
+                              goal_mode=pkg.GOAL_SEEDED, num_goals=1, start_mode=pkg.START_RANDOM)
+        e = pkg.VecGridWorld(cfg)
+        x, y, _ = e.get_state()
+        cells = e.get_cells()
+        grid = np.where(cells == 2, 1.0, np.where(cells == 1, -1.0, 0.0)).astype(np.float32)
+        free = [k for k in rng.permutation(w * h) if cells[k] == 0 and k != int(y[0]) * w + int(x[0])]
+        for j, k in enumerate(free[: max(3, len(free) // 4)]):
+            pen = np.float32(-rng.uniform(0.02, 0.98)) if j % 4 else np.float32(-1.5)
+            e.add_trap(int(k % w), int(k // w), float(pen))
+            grid[k] = pen
+        actions = rng.randint(0, 4, 250)
+        xs, ys, r, d = ref_walk(ref, 1, w, h, grid, int(x[0]), int(y[0]), actions)
+        for i, a in enumerate(actions):
+            rr, dd = e.step_actions([a])
+            xx, yy, _ = e.get_state()
+            assert (xx[0], yy[0], rr[0], dd[0]) == (xs[i], ys[i], r[i], d[i]), (trial, i)
+            checked += 1
+            charged += int(r[i] != np.float32(-0.01) and r[i] != 1.0)
+            if d[i]:
+                break
+    assert checked > 300 and charged > 20
+
+
 def race_free_batch(rng, w, h, n):
     """Unique (state, action) keys and no next-state that is also written: the reference kernels have no
     collision handling (plain read-modify-write, src/kernels.cu:99-114), so only such batches are defined."""
