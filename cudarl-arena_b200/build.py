@@ -138,8 +138,14 @@ def build_ref_demo(force=False):
     if not force and _newer(REF_DEMO, [src, os.path.join(CSRC, "facade.h"), LIB]):
         return REF_DEMO
     os.makedirs(REF_DIR, exist_ok=True)
-    _run([_nvcc(), "-O1", "-std=c++17"] + ARCH + ["-I" + os.path.join(CSRC, "compat"), "-o", REF_DEMO, src, "-L" + HERE, "-lcudarl",
-          "-Xlinker", "-rpath,$ORIGIN/../../cudarl-arena_b200"])
+    # `#include "environment.h"` looks beside the including file first, which would find the reference's own headers: the file
+    # is therefore compiled from a scratch directory outside this repository (byte-identical, removed afterwards).
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        scratch = os.path.join(tmp, "main.cu")
+        shutil.copyfile(src, scratch)
+        _run([_nvcc(), "-O1", "-std=c++17"] + ARCH + ["-I" + os.path.join(CSRC, "compat"), "-o", REF_DEMO, scratch, "-L" + HERE, "-lcudarl",
+              "-Xlinker", "-rpath,$ORIGIN/../../cudarl-arena_b200"])
     return REF_DEMO
 
 

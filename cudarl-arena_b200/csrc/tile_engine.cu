@@ -430,7 +430,18 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
 #pragma unroll
             for (unsigned kk = 0; kk < T2 / 32u; ++kk) sts_zero8(sn + (kk * 32u + lane) * 8u);
         } else {
-            const bool crowded = n_all > NMAX16;                    // warp-uniform
+            // How many records are really this tile's decides the counter width.  Records of the spill list belong to any tile, so a
+            // long list is counted first (one more pass over it) instead of sending every tile of the grid to the wide counters.
+            unsigned n_mine = n_all;
+            if (n_spill && n_all > NMAX16) {
+                n_mine = n_in;
+                for (unsigned base = 0; base < n_spill; base += 32u) {
+                    bool mine = false;
+                    if (base + lane < n_spill) { const int4 r = ovf_in[base + lane]; mine = tile_of(tp, r.x, r.y) == tile; }
+                    n_mine += __popc(__ballot_sync(FULL, mine));
+                }
+            }
+            const bool crowded = n_mine > NMAX16;                   // warp-uniform
             unsigned* gcnt = nullptr;
             if (crowded) {                                           // 4 x 32-bit counters per cell in global scratch
                 unsigned q = 0;

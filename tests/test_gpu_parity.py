@@ -371,8 +371,8 @@ def test_full_size_c5_lockstep_and_properties(pkg, orc):
     # 70,000 environments on one free cell inside a tile (32-bit counters), 3,000 on a free cell in the top row of another tile
     # whose upper neighbour is free too: with an all-zero table the greedy action is "up", so they all arrive in the tile above
     # in one step -- far more than the 32 arrival slots.
-    ys, xs = np.nonzero(cells[1024:1040, 2048:2064] == 0)
-    x[:70000], y[:70000] = 2048 + xs[0], 1024 + ys[0]
+    ys, xs = np.nonzero(cells[1030:1036, 2048:2064] == 0)      # rows 6..11 of the tile: four steps in any direction stay inside it
+    x[:70000], y[:70000] = 2048 + xs[0], 1030 + ys[0]
     cand = [(cx, cy) for cy in range(2064, 2400, 16) for cx in range(512, 528) if cells[cy, cx] == 0 and cells[cy - 1, cx] == 0]
     x[70000:73000], y[70000:73000] = cand[0]
     gpu.set_state(x, y, t); cpu.set_state(x, y, t)
