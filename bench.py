@@ -13,9 +13,14 @@ The line printed by rank 0 carries
   e2e        the same through the host-facing call: every window uploads its epsilon schedule from host
              memory and reads the run statistics back,
   roofline   algorithmic bytes (60 B per env-step) x envs per launch / mean duration of the step kernel
-             (k_tile_step, CUDA events around every launch), against the measured HBM copy bandwidth of
-             MEASURED_PEAKS.json,
-  cpu_baseline  the CPU oracle (a C++ port of the same semantics) timed on this box's cores.
+             (k_tile_step; one CUDA event pair around every uninterrupted run of launches), against the
+             measured HBM copy bandwidth of MEASURED_PEAKS.json,
+  eval       the greedy rollout of all environments that follows training in the workload (k_eval),
+  cpu_baseline  the CPU oracle (a C++ port of the same semantics) timed on this box's cores,
+  cpu_baseline_reference_python  the reference's own Python loop at its default configuration, where its
+             checkout is present,
+  multi_gpu_parity / replica_digests_equal  at N > 1: a small sharded run checked bit for bit against the
+             rank-ordered oracle replay before timing, and the replicas' tables compared after it.
 
 `--impl reference` times that CPU port with all host threads instead (the reference project itself
 only has one-thread-per-environment GPU kernels and a Python loop for this path).
@@ -32,8 +37,9 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 PKG_DIR = os.path.join(ROOT, "cudarl-arena_b200")
 ALGO_BYTES_TRAIN = 60      # 12 state in + 12 state out + 16 Q[s] row + 16 Q[s'] row + 4 Q[s,a] write
+ALGO_BYTES_EVAL = 40       # greedy rollout step: 24 state + 16 Q[s] row
 FALLBACK_HBM_GBS = 6650.0
-TRAFFIC_C5 = 655.5e6      # dram__bytes_read.sum + dram__bytes_write.sum of one k_tile_step launch on C5 (profiles/k_tile_step_C5.md)
+TRAFFIC_C5 = 512.6e6      # dram__bytes_read.sum + dram__bytes_write.sum of one k_tile_step launch on C5 (one ncu capture of one launch)
 
 
 def load_pkg():
@@ -136,7 +142,7 @@ def cpu_sample(pkg, cfg_name, nsteps, threads, num_envs=None):
     cfg = pkg.preset(cfg_name, num_envs=num_envs)
     o = oracle_lib.Oracle(cfg, threads=threads)
     o.count_conflicts(False)
-    o.train_steps(1)                       # touch memory once
+    o.train_steps(1)                       # touch memory once, start the worker threads
     t0 = time.perf_counter()
     o.train_steps(nsteps)
     dt = time.perf_counter() - t0
@@ -145,13 +151,60 @@ def cpu_sample(pkg, cfg_name, nsteps, threads, num_envs=None):
     return n * nsteps / dt, dt
 
 
+def reference_python_sample(episodes=300, max_steps=500):
+    """BASELINE configuration C1 on the reference's OWN CPU path: train() of src/train.py:171-259 driving MockEnvironment of
+    src/gui.py:84-137 with QTableAgent, one core (the Python interpreter).  Needs a checkout of the reference beside this
+    repository (or CUDARL_REFERENCE); its files are imported where they lie, never copied.  Returns None where it is absent."""
+    ref = os.environ.get("CUDARL_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+    if not os.path.isfile(os.path.join(ref, "src", "train.py")):
+        return {"unavailable": "no checkout of the reference project on this machine (its Python files are never copied; "
+                               "measured where the checkout exists: see BASELINE.md)"}
+    code = r"""
+import sys, os, types, time, tempfile, logging
+for n in ("matplotlib", "matplotlib.pyplot", "matplotlib.animation", "matplotlib.gridspec", "matplotlib.widgets"):
+    m = types.ModuleType(n); m.__path__ = []; sys.modules[n] = m
+sys.modules["matplotlib.animation"].FuncAnimation = object
+sys.modules["matplotlib.widgets"].Button = object; sys.modules["matplotlib.widgets"].Slider = object
+sys.modules["matplotlib"].pyplot = sys.modules["matplotlib.pyplot"]
+core = types.ModuleType("cudarl_core"); core.Environment = None; sys.modules["cudarl_core"] = core
+sys.path.insert(0, %r); os.chdir(tempfile.mkdtemp())
+import src.gui as gui, src.train as train
+logging.disable(logging.CRITICAL)
+env = gui.MockEnvironment(10, 10)
+agent = train.QTableAgent(10, 10)
+t0 = time.perf_counter()
+m = train.train(env, agent, num_episodes=%d, max_steps=%d)
+dt = time.perf_counter() - t0
+print("RESULT", sum(m["lengths"]), dt)
+""" % (ref, episodes, max_steps)
+    try:
+        r = subprocess.run([sys.executable, "-c", code], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, timeout=300)
+        steps, dt = [l for l in r.stdout.splitlines() if l.startswith("RESULT")][0].split()[1:]
+        return {"value": float(steps) / float(dt), "unit": "env-steps/s", "cores": 1, "kind": "reference_python",
+                "sample": "C1 (10x10, one environment): %d episodes x <= %d steps = %d steps of the reference's train() + MockEnvironment + QTableAgent, %.1f s"
+                          % (episodes, max_steps, int(float(steps)), float(dt))}
+    except Exception as e:           # noqa: BLE001
+        return {"unavailable": "running the reference's Python path failed: %r" % (e,)}
+
+
+METRIC = "env-steps/s (step+eps-greedy+TD update)"
+
+
+def bench_config(name, cfg, window, world):
+    return {"workload": workload_name(name, cfg), "window": window,
+            "l2": "inputs_exceed_l2" if cfg.width * cfg.height * 16 > 126e6 else "l2_resident",     # the table: 16 B per cell
+            "parallelism": "env-sharded x%d, Q replica per GPU, replicas averaged every %d steps" % (world, cfg.sync_every)}
+
+
 def run_reference(args):
-    """The reference arm: the CPU port of the path on all host threads; rank 0 only."""
+    """The reference arm: the CPU port of the path (persistent worker threads, all host threads) on the same workload;
+    rank 0 only.  One bench step times `--cpu-steps-per-sample` of the window's batched steps (a bounded sample)."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     pkg = load_pkg()
     threads = os.cpu_count() or 1
-    cfg = pkg.preset(args.config)
+    cfg = pkg.preset(args.config, num_envs=args.envs or None)
+    window = args.window or (cfg.sync_every if cfg.sync_every > 0 else 256)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib
     o = oracle_lib.Oracle(cfg, threads=threads)
@@ -165,12 +218,13 @@ def run_reference(args):
     dt = time.perf_counter() - t0
     n = int(cfg.num_envs)
     value = n * per * args.steps / dt
-    sample = "%d batched step(s) of %s (%d envs) per bench step, %d threads" % (per, args.config, n, threads)
+    sample = ("each bench step times %d of the %d batched steps of a window of %s (%d environments; at N GPUs the job is N such shards, "
+              "which a CPU steps one after the other at this same rate), %d threads" % (per, window, args.config, n, threads))
     print(json.dumps({
-        "impl": "reference", "metric": "env-steps/s (step+eps-greedy+TD update)", "value": value, "unit": "env-steps/s",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "env-steps/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.config, cfg), "window": per},
+        "config": bench_config(args.config, cfg, window, max(args.gpus, 1)),
         "cpu_baseline": {"value": value, "unit": "env-steps/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "env-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -178,6 +232,44 @@ def run_reference(args):
 
 def workload_name(name, cfg):
     return "%s: %dx%d grid, %d envs/GPU, fused step+eps-greedy+TD update" % (name, cfg.width, cfg.height, cfg.num_envs)
+
+
+def table_digest(q):
+    """Two 64-bit numbers of the table's bits: xor and wrapping sum of its 8-byte words."""
+    import numpy as np
+    w = np.ascontiguousarray(q).view(np.uint64)
+    return int(np.bitwise_xor.reduce(w)), int(np.add.reduce(w, dtype=np.uint64))
+
+
+def multi_gpu_parity(pkg, dist, rank, world, local):
+    """Before anything is timed at N > 1: every rank trains a small shard (C2: 64x64, 4096 environments per rank) for 24 steps
+    with the replicas averaged every 4, and replays ALL shards on the CPU oracle with the sum taken in rank order.  State and
+    table of the own shard must match bit for bit.  The oracle is the checker here, nothing of it is timed."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    n = 4096
+    def shard(r, device):
+        c = pkg.preset("C2", num_envs=n, device=device)
+        c.env_offset, c.sync_every = r * n, 4
+        return c
+    env = pkg.VecGridWorld(shard(rank, local))
+    ids = [pkg.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    env.comm_init(ids[0], rank, world)
+    env.train_steps(24)
+    cpus = [oracle_lib.Oracle(shard(r, 0)) for r in range(world)]
+    for _ in range(6):
+        for o in cpus:
+            o.train_steps(4)
+        oracle_lib.average_replicas(cpus)
+    ok = bool(np.array_equal(env.get_q(), cpus[rank].get_q()) and all(np.array_equal(a, b) for a, b in zip(env.get_state(), cpus[rank].get_state())))
+    env.close()
+    for o in cpus:
+        o.close()
+    flags = [None] * world
+    dist.all_gather_object(flags, ok)
+    return all(flags)
 
 
 def main():
@@ -189,15 +281,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--window", type=int, default=0, help="fused steps per bench step (default: averaging period, else 256)")
     ap.add_argument("--envs", type=int, default=0, help="override environments per GPU")
-    ap.add_argument("--cpu-steps", type=int, default=4, help="oracle steps timed for cpu_baseline (0 = skip)")
+    ap.add_argument("--cpu-steps", type=int, default=24, help="oracle steps timed for cpu_baseline (0 = skip)")
     ap.add_argument("--cpu-steps-per-sample", type=int, default=1)
+    ap.add_argument("--eval-steps", type=int, default=1000, help="step cap of the greedy evaluation rollout (0 = skip); 1000 as in src/train.py:282 of the reference")
     ap.add_argument("--profile-steps", type=int, default=0, help="run only this many fused steps and exit (for ncu)")
+    ap.add_argument("--profile-eval", type=int, default=0, help="with --profile-steps: then one greedy rollout with this step cap")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
 
+    import numpy as np
     pkg = load_pkg()
     dist, rank, world = dist_setup(args.gpus)
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -205,22 +300,26 @@ def main():
     n_local = int(cfg.num_envs)
     cfg.env_offset = rank * n_local
     window = args.window or (cfg.sync_every if cfg.sync_every > 0 else 256)
-    env = pkg.VecGridWorld(cfg)
-    launches_per_step = 1      # k_tile_step (+ 5 kernels that re-size the tile regions every 128th step)
 
     if args.profile_steps:                      # small fixed run for profilers: no timing, no JSON
+        env = pkg.VecGridWorld(cfg)
         env.train_steps(args.profile_steps)
         env.synchronize()
+        if args.profile_eval:
+            env.eval_rollout(args.profile_eval)
         print("ran %d fused steps" % args.profile_steps)
         return
 
+    parity = None
+    if world > 1:
+        parity = multi_gpu_parity(pkg, dist, rank, world, local)
+        if not parity:
+            raise SystemExit("multi-GPU parity check failed: a rank's shard differs from the rank-ordered oracle replay")
+    env = pkg.VecGridWorld(cfg)
     if world > 1:
         ids = [pkg.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         env.comm_init(ids[0], rank, world)
-        launches_per_step_window_extra = (cfg.width * cfg.height + (1 << 20) - 1) >> 20     # one averaging kernel per all-gather round of 2^20 cells
-    else:
-        launches_per_step_window_extra = 0
 
     # ---- device-resident arm -------------------------------------------------------------------
     for _ in range(args.warmup):
@@ -239,8 +338,16 @@ def main():
     total_env_steps = float(n_local) * world * window * args.steps
     value = total_env_steps / (ms * 1e-3)
 
+    # every window ends with an average: all replicas must now hold the same bits
+    digests_equal = None
+    if world > 1:
+        d = [None] * world
+        dist.all_gather_object(d, table_digest(env.get_q()))
+        digests_equal = all(x == d[0] for x in d)
+        if not digests_equal:
+            raise SystemExit("replicas differ after an averaging step: %r" % (d,))
+
     # ---- end-to-end arm: host-facing call, per-window host epsilon array in, statistics out -------
-    import numpy as np
     eps_host = np.full(window, float(cfg.eps0), np.float32)
     for _ in range(2):
         env.train_steps_eps(eps_host); env.get_stats()
@@ -248,23 +355,43 @@ def main():
     t0 = time.perf_counter()
     for _ in range(args.steps):
         env.train_steps_eps(eps_host)
-        st = env.get_stats()                     # synchronising device->host read of the result
+        env.get_stats()                          # synchronising device->host read of the result
     e2e_s = time.perf_counter() - t0
     barrier(dist)
     e2e_s = reduce_max(dist, e2e_s)
     e2e_value = total_env_steps / e2e_s
 
-    # ---- roofline of the dominant kernel: mean main-kernel duration from events around each launch -
+    # ---- roofline of the dominant kernel: one event pair around every uninterrupted run of step-kernel launches ------------
     env.kernel_timing(True)
-    env.train_steps(min(window, 128))
-    main_ms, nl = env.kernel_time_ms(); fix_ms = 0.0
+    env.train_steps(window)
+    step_ms, nl = env.kernel_time_ms()
     env.kernel_timing(False)
     peak, peak_kind = hbm_peak()
-    main_avg_s = main_ms * 1e-3 / max(nl, 1)
-    fix_avg_s = fix_ms * 1e-3 / max(nl, 1)
-    achieved = ALGO_BYTES_TRAIN * n_local / main_avg_s / 1e9
+    step_s = step_ms * 1e-3 / max(nl, 1)
+    achieved = ALGO_BYTES_TRAIN * n_local / step_s / 1e9
     stats = env.get_stats()
-    assert stats.device_error == 0, "device error flag set: %d" % stats.device_error
+
+    # ---- the greedy evaluation rollout of all environments that follows training in the workload ---------------------------
+    ev = None
+    if args.eval_steps > 0:
+        env.eval_rollout(8)                       # warm-up
+        env.synchronize(); barrier(dist)
+        env.timer_start()
+        es = env.eval_rollout(args.eval_steps)
+        ev_ms = reduce_max(dist, env.timer_stop_ms())
+        tot = [None] * world
+        if dist is not None:
+            dist.all_gather_object(tot, (int(es.total_steps), int(es.reached)))
+        else:
+            tot = [(int(es.total_steps), int(es.reached))]
+        ev_steps, ev_reached = sum(t[0] for t in tot), sum(t[1] for t in tot)
+        ev_rate = ev_steps / (ev_ms * 1e-3)
+        ev = {"value": ev_rate, "unit": "env-steps/s", "ms": ev_ms, "step_cap": args.eval_steps, "env_steps": ev_steps,
+              "reached_fraction": ev_reached / float(n_local * world),
+              "roofline": {"bound": "hbm", "kernel": "k_eval", "algorithmic_bytes_per_env_step": ALGO_BYTES_EVAL,
+                           "achieved": ALGO_BYTES_EVAL * ev_rate / world / 1e9, "peak": peak, "unit": "GB/s",
+                           "frac": ALGO_BYTES_EVAL * ev_rate / world / 1e9 / peak, "peak_kind": peak_kind,
+                           "note": "includes the host call and its synchronising read of the result"}}
 
     if rank != 0:
         return
@@ -274,23 +401,28 @@ def main():
         v, dt = cpu_sample(pkg, args.config, args.cpu_steps, threads, num_envs=args.envs or None)
         cpu = {"value": v, "unit": "env-steps/s", "cores": threads, "kind": "port",
                "sample": "%d batched steps of the full %s workload (%d envs) on the CPU oracle, %.1f s" % (args.cpu_steps, args.config, n_local, dt)}
+    averaging_kernels = 2 if world > 1 else 0          # per window: the ordered sum of the own slice, the border array rebuilt
     line = {
-        "metric": "env-steps/s (step+eps-greedy+TD update)", "value": value, "unit": "env-steps/s",
+        "metric": METRIC, "value": value, "unit": "env-steps/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.config, cfg), "window": window, "l2": "inputs_exceed_l2" if cfg.width * cfg.height * 32 > 126e6 else "l2_resident",   # two dense tables of 16 B per cell
-                   "parallelism": "env-sharded x%d, Q replica per GPU, NCCL average every %d steps" % (world, cfg.sync_every)},
+        "config": bench_config(args.config, cfg, window, world),
         "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": int(window * 4), "d2h_bytes_per_step": 128},
-        "gpu_launches": int(args.steps * (window * launches_per_step + (window // 128) * 5 + launches_per_step_window_extra)),
+        # k_tile_step once per fused step, 5 kernels that re-size the record regions every 128th step, the averaging kernels
+        "gpu_launches": int(args.steps * (window + (window // 128) * 5 + averaging_kernels)),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one k_tile_step launch on this workload, from the ncu
-                     # capture summarised in profiles/k_tile_step_C5.md (not measured by this run)
+                     # dram__bytes_read.sum + dram__bytes_write.sum of ONE k_tile_step launch on this workload, from an ncu capture
+                     # of one launch (not measured by this run)
                      "traffic": TRAFFIC_C5 if (args.config == "C5" and not args.envs) else None,
                      "peak_kind": peak_kind, "kernel": "k_tile_step", "algorithmic_bytes_per_env_step": ALGO_BYTES_TRAIN,
-                     "main_kernel_us": main_avg_s * 1e6, "other_kernels_us": fix_avg_s * 1e6,
+                     "main_kernel_us": step_s * 1e6, "launches_timed": int(nl),
                      "whole_step_frac": ALGO_BYTES_TRAIN * n_local / (ms * 1e-3 / (args.steps * window)) / 1e9 / peak},
+        "eval": ev,
         "cpu_baseline": cpu,
+        "cpu_baseline_reference_python": reference_python_sample(),
+        "multi_gpu_parity": None if parity is None else "ok",
+        "replica_digests_equal": digests_equal,
         "run_stats": {"steps": stats.steps, "goals": stats.goals, "timeouts": stats.timeouts,
                       "conflict_fraction": stats.conflicts / max(stats.env_steps, 1), "chained_fraction": stats.chained / max(stats.env_steps, 1),
                       "long_chains": stats.long_chains},

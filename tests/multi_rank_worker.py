@@ -21,10 +21,15 @@ from conftest import load_package  # noqa: E402
 import oracle_lib  # noqa: E402
 
 
+SIZE = [0, 0]      # --width / --height: a grid other than the preset's 64x64
+
+
 def shard_config(pkg, rank, n_local, k):
     cfg = pkg.preset("C2", num_envs=n_local)
     cfg.env_offset = rank * n_local
     cfg.sync_every = k
+    if SIZE[0]:
+        cfg.width, cfg.height = SIZE
     return cfg
 
 
@@ -34,7 +39,10 @@ def main():
     ap.add_argument("--steps", type=int, default=24)
     ap.add_argument("--k", type=int, default=4)
     ap.add_argument("--envs", type=int, default=1024)
+    ap.add_argument("--width", type=int, default=0)
+    ap.add_argument("--height", type=int, default=0)
     a = ap.parse_args()
+    SIZE[:] = [a.width, a.height]
     pkg = load_package()
     dist.init_process_group(backend="gloo")
     rank, world = dist.get_rank(), dist.get_world_size()

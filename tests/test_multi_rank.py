@@ -46,5 +46,8 @@ def test_gpu_ranks_nccl():
     if n < 2:
         pytest.skip("needs at least two GPUs")
     run_ranks(2, "gpu", ["--steps", "24", "--k", "4", "--envs", "4096"])
+    # 999,999 cells: the table does not split into equal slices, the last slice of the averaging runs into the table's padding
+    run_ranks(2, "gpu", ["--steps", "12", "--k", "4", "--envs", "8192", "--width", "1001", "--height", "999"])
     if n >= 4:
         run_ranks(4, "gpu", ["--steps", "16", "--k", "4", "--envs", "2048"])
+        run_ranks(3, "gpu", ["--steps", "8", "--k", "4", "--envs", "4096", "--width", "1001", "--height", "999"])
