@@ -74,7 +74,8 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned coun
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+    // relaxed: the barrier only tells this warp that its tensor copy has landed; no write of the arriving lane is published by it
+    asm volatile("mbarrier.arrive.expect_tx.relaxed.cta.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // One look at the barrier, no waiting.
 __device__ __forceinline__ bool mbar_test_wait(unsigned long long* bar, unsigned parity) {
@@ -157,7 +158,8 @@ template <unsigned TSH> struct WarpSmem {
     static constexpr unsigned OFF_N = STAGE, OFF_BM = OFF_N + T2 * 8u, OFF_LIST = OFF_BM + 4u * T * 4u;
     static constexpr unsigned LIST_BYTES = T2 * 2u > 512u ? T2 * 2u : 512u;
     static constexpr unsigned BYTES = (OFF_LIST + LIST_BYTES + 127u) / 128u * 128u;
-    static constexpr unsigned TX_BYTES = T2 * 16u + CLS + 4u * T * 4u;      // what the three copies of a tile deliver
+    static constexpr unsigned TX_BYTES = T2 * 16u;                   // what the tensor copy of a tile delivers
+    static constexpr unsigned HALO_LANES = T, MV_LANES = T2 / 16u;   // lanes that fetch 16 bytes each of the border values / move bytes
 };
 
 // Everything the per-environment step needs about the tile being processed.
@@ -276,14 +278,16 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     unsigned roff = 0, fcap = 0, n_front = 0, n_in = 0;
     int4 pre[PRE];
     unsigned long long* const bar = &s_bar[warp];
+    uint4 side = make_uint4(0u, 0u, 0u, 0u);      // this lane's 16 bytes of the tile's border values or move bytes, on their way to shared memory
     auto issue = [&](unsigned tile, unsigned txi, unsigned tyi, const uint2 hw) {
         roff = __shfl_sync(FULL, hw.x, 0); fcap = __shfl_sync(FULL, hw.y, 0);
         n_front = min(__shfl_sync(FULL, hw.x, 1), fcap); n_in = n_front + min(__shfl_sync(FULL, hw.y, 1), ARR_CAP);
         if (lane == 0u) mbar_arrive_expect_tx(bar, L::TX_BYTES);
         __syncwarp();
         if (lane == 0u) tensor_g2s_2d(wb, &tp.tmq, (int)(txi << TSH) * 4, (int)(tyi << TSH), bar);
-        else if (lane == 1u) bulk_g2s(wb + L::ST_MV, tp.tcls + (size_t)tile * L::CLS, L::CLS, bar);
-        else if (lane == 2u) bulk_g2s(wb + L::ST_HALO, halo_in + (size_t)tile * (4u * T), 4u * T * 4u, bar);
+        // the small pieces (border values 16 T bytes, move bytes T*T) come as one 16-byte load per lane, stored after the wait
+        if (lane < L::HALO_LANES) side = *reinterpret_cast<const uint4*>(halo_in + (size_t)tile * (4u * T) + lane * 4u);
+        else if (lane < L::HALO_LANES + L::MV_LANES) side = *reinterpret_cast<const uint4*>(tp.tcls + (size_t)tile * L::CLS + (lane - L::HALO_LANES) * 16u);
 #pragma unroll
         for (unsigned q = 0; q < PRE; ++q) {
             const unsigned j = q * 32u + lane;
@@ -321,6 +325,10 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             break;
         }
         phase ^= 1u;
+        if (lane < L::HALO_LANES + L::MV_LANES)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" :: "r"(lane < L::HALO_LANES ? shalo + lane * 16u : smv + (lane - L::HALO_LANES) * 16u),
+                         "r"(side.x), "r"(side.y), "r"(side.z), "r"(side.w) : "memory");
+        __syncwarp();
 
         // stays: position in the tile's own region from a ballot.  Gives back whether the record still has to go somewhere else.
         unsigned nstay = 0;

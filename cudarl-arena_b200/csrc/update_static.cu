@@ -28,6 +28,7 @@
 // Transitions whose state, next state or action is out of range are skipped.
 #include "../../include/cudarl.h"
 #include <cuda_runtime.h>
+#include <cstdint>
 #include <mutex>
 
 namespace {
@@ -81,15 +82,12 @@ __global__ void ks_main(unsigned char* base, const float4* q, int W, int H, unsi
         (unsigned)nx[i] >= (unsigned)W || (unsigned)ny[i] >= (unsigned)H) { atomicOr(s.ctl + 1, 4u); return; }
     unsigned cell = (unsigned)sy[i] * (unsigned)W + (unsigned)sx[i];
     unsigned a = (unsigned)act[i];
-    float4 row = q[cell];
-    float cur = a == 0 ? row.x : a == 1 ? row.y : a == 2 ? row.z : row.w;
     float m = 0.0f;
     if (!dn[i]) {
         float4 r2 = q[(unsigned)ny[i] * (unsigned)W + (unsigned)nx[i]];
         m = r2.x; m = r2.y > m ? r2.y : m; m = r2.z > m ? r2.z : m; m = r2.w > m ? r2.w : m;
         if (clamp && m < 0.0f) m = 0.0f;
     }
-    (void)cur;
     float d = __fmaf_rn(gamma, m, rew[i]);               // TD target from the untouched table
     unsigned prev = atomicExch(s.head + slot_of(cell), i + 1u);
     s.ent[i] = make_uint4((cell << 2) | a, i, __float_as_uint(d), prev);
@@ -166,6 +164,10 @@ extern "C" int cudarl_update_batch_static(float* d_q, int32_t width, int32_t hei
     if (n > (int64_t)MAXB) return -5;                   // larger than the static scratch: refuse, launch nothing
     if (n == 0) return 0;
     if (!d_q || !d_sx || !d_sy || !d_actions || !d_rewards || !d_nx || !d_ny || !d_dones) return -1;
+    // the kernels read the table as 16-byte rows and the other arrays as 4-byte words: a misaligned pointer would be a device fault
+    if ((reinterpret_cast<uintptr_t>(d_q) & 15u) || ((reinterpret_cast<uintptr_t>(d_sx) | reinterpret_cast<uintptr_t>(d_sy) |
+         reinterpret_cast<uintptr_t>(d_actions) | reinterpret_cast<uintptr_t>(d_rewards) | reinterpret_cast<uintptr_t>(d_nx) |
+         reinterpret_cast<uintptr_t>(d_ny)) & 3u)) return -1;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return 1000 + (int)e;

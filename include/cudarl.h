@@ -181,7 +181,9 @@ int cudarl_update_batch(cudarl_ctx* ctx, int64_t n,
  * CUDARL_STATIC_MAX_BATCH (larger n returns -5 and launches nothing).  Every call on a GPU shares
  * that array: calls that could overlap on the GPU must be serialised by the caller.  The first call
  * on each device looks up the array's device address; make that call outside stream capture.
- * Asynchronous on `stream` (a cudaStream_t, NULL = default stream); out-of-range transitions are skipped. */
+ * Asynchronous on `stream` (a cudaStream_t, NULL = default stream).  A transition whose state, next state or action is
+ * out of range is skipped without a report; a table pointer that is not 16-byte aligned, or an int32 / float array that
+ * is not 4-byte aligned, returns -1 and launches nothing. */
 #define CUDARL_STATIC_MAX_BATCH 65536
 int cudarl_update_batch_static(float* d_q, int32_t width, int32_t height, int64_t n,
                                const int32_t* d_state_x, const int32_t* d_state_y, const int32_t* d_actions,
