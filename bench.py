@@ -286,6 +286,7 @@ def main():
     ap.add_argument("--eval-steps", type=int, default=1000, help="step cap of the greedy evaluation rollout (0 = skip); 1000 as in src/train.py:282 of the reference")
     ap.add_argument("--profile-steps", type=int, default=0, help="run only this many fused steps and exit (for ncu)")
     ap.add_argument("--profile-eval", type=int, default=0, help="with --profile-steps: then one greedy rollout with this step cap")
+    ap.add_argument("--profile-aux", type=int, default=0, help="with --profile-steps: then one caller-driven step of all environments and one update_batch of this many transitions")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
@@ -307,6 +308,12 @@ def main():
         env.synchronize()
         if args.profile_eval:
             env.eval_rollout(args.profile_eval)
+        if args.profile_aux:                    # the caller-driven step and the ordered update_batch, once each at this size
+            rng = np.random.RandomState(1)
+            env.step_actions(rng.randint(0, 4, n_local).astype(np.int32))
+            nb = args.profile_aux
+            sx, sy = rng.randint(0, cfg.width, nb).astype(np.int32), rng.randint(0, cfg.height, nb).astype(np.int32)
+            env.update_batch(sx, sy, rng.randint(0, 4, nb), np.full(nb, -0.01, np.float32), np.clip(sx + 1, 0, cfg.width - 1), sy, np.zeros(nb, np.uint8))
         print("ran %d fused steps" % args.profile_steps)
         return
 
