@@ -686,6 +686,7 @@ int cudarl_eval_rollout(cudarl_ctx* c, int32_t max_steps, cudarl_eval_stats* out
     if (!c || !out || max_steps < 0) return fail(c, -1, "bad argument");
     CK(cudaSetDevice(c->cfg.device));
     { int rl = leave_tiles(c); if (rl) return rl; }
+    if (c->cls_dirty) { launch_tile_classes(c->p, c->st); c->cls_dirty = false; }       // the rollout reads the per-tile move bytes
     k_ctl_eval_clear<<<1, 1, 0, c->st>>>(c->p.ctl);
     launch_eval(c->p, max_steps, (unsigned long long)c->eval_calls, c->st);
     CK(cudaGetLastError());

@@ -378,27 +378,45 @@ __global__ void k_step_actions(Params p, const int* actions, float* rewards, uns
     if (dones) dones[e] = dn;
 }
 
-// Greedy rollout of every environment from a fresh start cell; positions stay in registers, the
-// table is read-only, so the whole rollout is one launch.
+// Greedy rollout of every environment from a fresh start cell; positions stay in registers, the table is read-only, so
+// the whole rollout is one launch.  A step is ONE round trip to memory: the cell's row (for the argmax) and its move
+// byte (which of the four moves are blocked / end on a goal, the per-tile array of the train step) are loaded side by side.
+// Every thread walks two environments, so that two such chains overlap.
 __global__ void __launch_bounds__(BLOCK) k_eval(Params p, int max_steps, unsigned long long nonce) {
     __shared__ unsigned s_reached; __shared__ unsigned long long s_steps;
     if (threadIdx.x == 0) { s_reached = 0; s_steps = 0; }
     __syncthreads();
-    unsigned i = blockIdx.x * BLOCK + threadIdx.x;
-    if (i < p.N) {
-        unsigned s = sample_start(p, p.env_offset + i, nonce, TAG_EVAL);
-        unsigned cs = cw_load(p.cw, s);
-        unsigned steps = 0; bool reached = false;
-        for (int k = 0; k < max_steps; ++k) {
-            float4 row = __ldg(p.Q + s);
-            int a = argmax4(row);
-            int x = (int)(s % (unsigned)p.W), y = (int)(s / (unsigned)p.W);
-            unsigned c2; unsigned s2 = move_cell(p, x, y, s, cs, a, c2);
-            ++steps; s = s2; cs = c2;
-            if (c2 & CW_GOAL) { reached = true; break; }
+    const TileP& tp = p.tp;
+    const unsigned half = (p.N + 1u) / 2u;
+    const unsigned i0 = blockIdx.x * BLOCK + threadIdx.x;
+    if (i0 < half) {
+        int x[2], y[2]; bool live[2]; unsigned steps[2] = {0u, 0u}; unsigned reached = 0;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const unsigned i = i0 + (unsigned)k * half;
+            live[k] = i < p.N;
+            const unsigned s = live[k] ? sample_start(p, p.env_offset + i, nonce, TAG_EVAL) : 0u;
+            y[k] = (int)(s / (unsigned)p.W); x[k] = (int)(s - (unsigned)y[k] * (unsigned)p.W);
         }
-        if (reached) atomicAdd(&s_reached, 1u);
-        atomicAdd(&s_steps, (unsigned long long)steps);
+        for (int it = 0; it < max_steps && (live[0] || live[1]); ++it) {
+            float4 row[2]; unsigned mvb[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const unsigned tile = ((unsigned)y[k] >> tp.tshift) * tp.tiles_x + ((unsigned)x[k] >> tp.tshift);
+                row[k] = __ldg(p.Q + (size_t)y[k] * (size_t)p.W + (size_t)x[k]);
+                mvb[k] = __ldg(tp.tcls + (size_t)tile * tp.cls_stride + ((((unsigned)y[k] & (tp.T - 1u)) << tp.tshift) | ((unsigned)x[k] & (tp.T - 1u))));
+            }
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                if (!live[k]) continue;
+                const int a = argmax4(row[k]);
+                if (!((mvb[k] >> a) & 1u)) { x[k] += (a == 1) - (a == 3); y[k] += (a == 2) - (a == 0); }
+                ++steps[k];
+                if ((mvb[k] >> (4 + a)) & 1u) { ++reached; live[k] = false; }
+            }
+        }
+        if (reached) atomicAdd(&s_reached, reached);
+        atomicAdd(&s_steps, (unsigned long long)(steps[0] + steps[1]));
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -481,7 +499,7 @@ void launch_step_actions(const Params& p, const int* a, float* r, unsigned char*
     if (p.N) k_step_actions<<<nblk(p.N), BLOCK, 0, st>>>(p, a, r, d);
 }
 void launch_eval(const Params& p, int max_steps, unsigned long long nonce, cudaStream_t st) {
-    if (p.N) k_eval<<<nblk(p.N), BLOCK, 0, st>>>(p, max_steps, nonce);
+    if (p.N) k_eval<<<nblk((p.N + 1u) / 2u), BLOCK, 0, st>>>(p, max_steps, nonce);
 }
 void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* sy, const int* a, const float* r,
                          const int* nx, const int* ny, const unsigned char* dn, cudaStream_t st) {
