@@ -281,6 +281,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--window", type=int, default=0, help="fused steps per bench step (default: averaging period, else 256)")
     ap.add_argument("--envs", type=int, default=0, help="override environments per GPU")
+    ap.add_argument("--tile-edge", type=int, default=0, help="tile edge of the step kernel, 8 or 16 (0 = chosen from the density)")
     ap.add_argument("--cpu-steps", type=int, default=24, help="oracle steps timed for cpu_baseline (0 = skip)")
     ap.add_argument("--cpu-steps-per-sample", type=int, default=1)
     ap.add_argument("--eval-steps", type=int, default=1000, help="step cap of the greedy evaluation rollout (0 = skip); 1000 as in src/train.py:282 of the reference")
@@ -300,6 +301,7 @@ def main():
     cfg = pkg.preset(args.config, num_envs=args.envs or None, device=local)
     n_local = int(cfg.num_envs)
     cfg.env_offset = rank * n_local
+    cfg.tile_edge = args.tile_edge
     window = args.window or (cfg.sync_every if cfg.sync_every > 0 else 256)
 
     if args.profile_steps:                      # small fixed run for profilers: no timing, no JSON

@@ -466,12 +466,19 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             }
 
             // ---- the step: every environment acts, moves and counts itself in its cell's histogram ----------
+            // record j of this tile's input: its region, its arrival buffer, then the spill list (filtered by tile in the loop)
+            auto fetch = [&](unsigned j) -> int4 {
+                if (j >= n_all) return make_int4(0, 0, 0, 0);
+                return j < n_front ? in[roff + j] : j < n_in ? arr_in[(size_t)tile * ARR_CAP + (j - n_front)] : ovf_in[j - n_in];
+            };
+            int4 ahead = fetch(PRE * 32u + lane);                     // one round ahead of the loop: its latency hides behind a round of work
             for (unsigned it = 0; it * 32u < n_all; ++it) {
                 const unsigned j = it * 32u + lane;
                 bool act = j < n_all;
                 int4 rec = it == 0u ? pre[0] : it == 1u ? pre[1] : pre[2];
-                if (act && j >= n_in) { rec = ovf_in[j - n_in]; act = tile_of(tp, rec.x, rec.y) == tile; }
-                else if (act && it >= PRE) rec = j < n_front ? in[roff + j] : arr_in[(size_t)tile * ARR_CAP + (j - n_front)];
+                if (it >= PRE) { rec = ahead; ahead = fetch(j + 32u); }
+                else if (act && j >= n_in) rec = ovf_in[j - n_in];     // a spill list next to a small tile: the first rounds read it directly
+                if (act && j >= n_in) act = tile_of(tp, rec.x, rec.y) == tile;
                 const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
                 if (act && (lx | ly) >= T) { s_acc[5] = 1u; act = false; }
                 int4 nrec = rec; bool stays = false;
