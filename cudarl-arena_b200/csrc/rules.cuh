@@ -41,6 +41,7 @@ __device__ __forceinline__ unsigned cw_load(const unsigned short* cw, unsigned c
 // RANDOM: first free non-goal cell among 64 seeded candidates, else the precomputed fallback cell.
 __device__ __forceinline__ unsigned sample_start(const Params& p, unsigned gi, unsigned long long nonce, unsigned tag) {
     if (p.start_mode != 2) return p.start_cell;
+#pragma unroll 1            // restarts are rare: keep the inlined copies of this loop small (the step kernel's hot loop must fit the instruction cache)
     for (unsigned k = 0; k < 16; ++k) {
         U4 w = philox4x32_10(gi, k, (unsigned)nonce, (unsigned)(nonce >> 32), p.k0, p.k1 ^ tag);
         unsigned c;

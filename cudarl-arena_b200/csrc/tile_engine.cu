@@ -38,7 +38,7 @@ namespace cudarl {
 constexpr unsigned CROWDED_CELL = 24;   // a cell with more environments than this counts as "crowded" in the run statistics
 constexpr unsigned NMAX16 = 65535u;     // records of a tile the 16-bit counters can hold
 constexpr unsigned WPB = 4;             // warps per block; every warp works on its own
-constexpr unsigned PRE = 3;             // records per lane fetched before the warp waits for its copies
+constexpr unsigned FAST_MAX = 96;       // records of a tile the fast path stages in shared memory
 
 __device__ __forceinline__ unsigned tile_of(const TileP& tp, int x, int y) {
     return ((unsigned)y >> tp.tshift) * tp.tiles_x + ((unsigned)x >> tp.tshift);
@@ -146,19 +146,22 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 //   s_mv   T*T  u8       per cell: bit a = a move in direction a is blocked (grid edge or obstacle), bit 4+a = the
 //                        cell an environment stands on after choosing a (the next cell, or its own when blocked) is a goal
 //   s_halo 4T   float    max_a Q_t of the cells beyond the north / south / west / east edge (from the border array)
-// and one work area:
+//   s_rec  96   int4     fast path: the tile's records (bulk copies); a record that leaves the tile is written back here
+// and the work area:
 //   s_n    T*T  u64      per cell: how many environments chose action a, 16 bits per action; zero between tiles
-//   s_bm   4T   float    max_a Q_{t+1} of the tile's own north / south / west / east border cells (general path only)
-//   s_list               general path: T*T u16, the occupied cells; fast path: up to 32 records that leave the tile
+//   s_kd   96   u32+f32  fast path: per record its key (cell, action, owner flag) and TD target, from the step to the owner pass
+//   s_que  96   u8       fast path: the slots of the records that leave the tile
+//   s_bm   4T   float    general path: max_a Q_{t+1} of the tile's own north / south / west / east border cells
+//   s_list T*T  u16      general path: the occupied cells (shares the bytes of s_rec)
 // A tile with more than 65,535 records counts in 32-bit counters in global scratch instead.
 template <unsigned TSH> struct WarpSmem {
     static constexpr unsigned T = 1u << TSH, T2 = T * T;
     static constexpr unsigned CLS = T2;                              // a multiple of 16 for T = 8 and 16
-    static constexpr unsigned ST_MV = T2 * 16u, ST_HALO = ST_MV + CLS, STAGE = (ST_HALO + 4u * T * 4u + 127u) / 128u * 128u;
-    static constexpr unsigned OFF_N = STAGE, OFF_BM = OFF_N + T2 * 8u, OFF_LIST = OFF_BM + 4u * T * 4u;
-    static constexpr unsigned LIST_BYTES = T2 * 2u > 512u ? T2 * 2u : 512u;
-    static constexpr unsigned BYTES = (OFF_LIST + LIST_BYTES + 127u) / 128u * 128u;
-    static constexpr unsigned TX_BYTES = T2 * 16u;                   // what the tensor copy of a tile delivers
+    static constexpr unsigned ST_MV = T2 * 16u, ST_HALO = ST_MV + CLS, ST_REC = ST_HALO + 4u * T * 4u;
+    static constexpr unsigned REC_BYTES = FAST_MAX * 16u > T2 * 2u ? FAST_MAX * 16u : T2 * 2u;
+    static constexpr unsigned OFF_N = ST_REC + REC_BYTES, OFF_KD = OFF_N + T2 * 8u, OFF_QUE = OFF_KD + FAST_MAX * 8u,
+                              OFF_BM = OFF_QUE + FAST_MAX;
+    static constexpr unsigned BYTES = (OFF_BM + 4u * T * 4u + 127u) / 128u * 128u;
     static constexpr unsigned HALO_LANES = T, MV_LANES = T2 / 16u;   // lanes that fetch 16 bytes each of the border values / move bytes
 };
 
@@ -224,8 +227,8 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     unsigned char* wb = smem + warp * L::BYTES;
     unsigned long long* s_n = reinterpret_cast<unsigned long long*>(wb + L::OFF_N);
     float* s_bm = reinterpret_cast<float*>(wb + L::OFF_BM);
-    unsigned short* s_list = reinterpret_cast<unsigned short*>(wb + L::OFF_LIST);
-    const unsigned sbase = smem_u32(wb), sn = sbase + L::OFF_N, sleave = sbase + L::OFF_LIST;
+    unsigned short* s_list = reinterpret_cast<unsigned short*>(wb + L::ST_REC);
+    const unsigned sbase = smem_u32(wb), sn = sbase + L::OFF_N, srec = sbase + L::ST_REC, skd = sbase + L::OFF_KD, sque = sbase + L::OFF_QUE;
 
     const unsigned long long g = p.step;
     const unsigned par = (unsigned)(g & 1ull);
@@ -257,17 +260,21 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     // Border cells a lane reports at the end of a tile: entry k = lane + 32 r of the ring (north row, south row, west column,
     // east column): its cell inside the tile, and where it goes in the neighbour's block of the border array -- my north row is
     // the south halo (slot 1) of the tile above, my south row the north halo (0) of the tile below, west -> east (3), east -> west (2).
+    // Per lane these never change: packed once (cell: 8 bits per entry; edge: 2 bits per entry; offsets: one int per entry).
     constexpr unsigned BR = (4u * T + 31u) / 32u;
     auto ring_cell = [&](unsigned k) -> unsigned {
         const unsigned e = k >> TSH, i = k & (T - 1u);
         return e == 0u ? i : e == 1u ? ((T - 1u) << TSH) + i : e == 2u ? (i << TSH) : (i << TSH) + T - 1u;
     };
-    auto ring_dst = [&](unsigned k) -> int {
-        const unsigned e = k >> TSH, i = k & (T - 1u);
+    unsigned b_pack = 0u; int b_dst[BR];
+#pragma unroll
+    for (unsigned r = 0; r < BR; ++r) {
+        const unsigned k = lane + 32u * r, e = k >> TSH, i = k & (T - 1u);
         const int dtile = e == 0u ? -(int)tp.tiles_x : e == 1u ? (int)tp.tiles_x : e == 2u ? -1 : 1;
         const unsigned slot = e == 0u ? 1u : e == 1u ? 0u : e == 2u ? 3u : 2u;
-        return (dtile * 4 + (int)slot) * (int)T + (int)i;
-    };
+        b_dst[r] = (dtile * 4 + (int)slot) * (int)T + (int)i;
+        b_pack |= (ring_cell(k) | (e << 8)) << (16u * r);
+    }
 
     // Header of a tile: lane 0 loads {region start, capacity}, lane 1 {records in the region, arrivals}; the words
     // are only exchanged when the tile's copies are issued, one tile after the loads.
@@ -276,23 +283,22 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     // Issue the copies of a tile and fetch its first records into registers.  (One stage: a second one, with the next tile's
     // copies in flight during the work, cost more in registers and resident warps than it hid: 176 us against 127 us per step.)
     unsigned roff = 0, fcap = 0, n_front = 0, n_in = 0;
-    int4 pre[PRE];
     unsigned long long* const bar = &s_bar[warp];
     uint4 side = make_uint4(0u, 0u, 0u, 0u);      // this lane's 16 bytes of the tile's border values or move bytes, on their way to shared memory
+    // Issue the copies of a tile: the table box (tensor copy) and, when the tile is small enough for the fast path, its records
+    // (region and arrival buffer, one bulk copy each), all completing on the warp's barrier.
     auto issue = [&](unsigned tile, unsigned txi, unsigned tyi, const uint2 hw) {
         roff = __shfl_sync(FULL, hw.x, 0); fcap = __shfl_sync(FULL, hw.y, 0);
         n_front = min(__shfl_sync(FULL, hw.x, 1), fcap); n_in = n_front + min(__shfl_sync(FULL, hw.y, 1), ARR_CAP);
-        if (lane == 0u) mbar_arrive_expect_tx(bar, L::TX_BYTES);
+        const bool stage_records = n_in <= FAST_MAX && n_spill == 0u;
+        if (lane == 0u) mbar_arrive_expect_tx(bar, T2 * 16u + (stage_records ? n_in * 16u : 0u));
         __syncwarp();
         if (lane == 0u) tensor_g2s_2d(wb, &tp.tmq, (int)(txi << TSH) * 4, (int)(tyi << TSH), bar);
+        else if (lane == 1u && stage_records && n_front) bulk_g2s(wb + L::ST_REC, in + roff, n_front * 16u, bar);
+        else if (lane == 2u && stage_records && n_in > n_front) bulk_g2s(wb + L::ST_REC + n_front * 16u, arr_in + (size_t)tile * ARR_CAP, (n_in - n_front) * 16u, bar);
         // the small pieces (border values 16 T bytes, move bytes T*T) come as one 16-byte load per lane, stored after the wait
         if (lane < L::HALO_LANES) side = *reinterpret_cast<const uint4*>(halo_in + (size_t)tile * (4u * T) + lane * 4u);
         else if (lane < L::HALO_LANES + L::MV_LANES) side = *reinterpret_cast<const uint4*>(tp.tcls + (size_t)tile * L::CLS + (lane - L::HALO_LANES) * 16u);
-#pragma unroll
-        for (unsigned q = 0; q < PRE; ++q) {
-            const unsigned j = q * 32u + lane;
-            pre[q] = j < n_front ? in[roff + j] : j < n_in ? arr_in[(size_t)tile * ARR_CAP + (j - n_front)] : make_int4(0, 0, 0, 0);
-        }
     };
     // A record that leaves its tile: one atomic on the new tile's arrival counter, then the store.  The fast path issues the
     // atomic at the end of a tile and stores a tile later, when the counter value has long arrived.
@@ -341,38 +347,32 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             return act && !placed;
         };
 
-        const bool fast = n_all <= PRE * 32u && n_spill == 0u;  // warp-uniform: every record of the tile is already in registers
+        const bool fast = n_in <= FAST_MAX && n_spill == 0u;     // warp-uniform: the tile's records are in shared memory
         if (fast) {
-            // ---- few records: one pass, everything an update needs stays in registers ---------------------------
+            // ---- few records: everything an update needs passes through shared memory once ------------------------
             // Each environment computes the TD target of its own (cell, action) -- it has the next cell at hand -- and
             // counts itself; the FIRST to count on a (cell, action) owns it and, once every count is in, applies the
             // map that many times to the one table entry: a 4-byte store into the table, and into the tile in shared
-            // memory, which thereby becomes Q_{t+1} for the border values.
-            unsigned key[PRE]; float dd[PRE];
-            unsigned draws = 0u;                                 // per record 3 bits: explore, random action
-#pragma unroll
-            for (unsigned q = 0; q < PRE; ++q) {                 // the random draws first: independent chains the scheduler can interleave
-                key[q] = 0u; dd[q] = 0.0f;
-                if (q * 32u < n_all) {
-                    const U4 w = philox4x32_10(p.env_offset + (unsigned)pre[q].w, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
-                    draws |= ((((w.x >> 8) < c.eps_thr) ? 4u : 0u) | (w.y & 3u)) << (3u * q);
-                }
-            }
+            // memory, which thereby becomes Q_{t+1} for the border values.  The loops are rolled on purpose: the tile
+            // loop has to stay inside the instruction cache.
+            const unsigned rounds = (n_in + 31u) >> 5;
             unsigned nleave = 0;
-#pragma unroll
-            for (unsigned q = 0; q < PRE; ++q) {
-                if (q * 32u >= n_all) break;
-                const int4 rec = pre[q];
+#pragma unroll 1
+            for (unsigned it = 0; it < rounds; ++it) {
+                const unsigned j = it * 32u + lane;
+                bool act = j < n_in;
+                int4 rec = make_int4(0, 0, 0, 0);
+                if (act) asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(rec.x), "=r"(rec.y), "=r"(rec.z), "=r"(rec.w) : "r"(srec + j * 16u) : "memory");
                 const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
-                bool act = q * 32u + lane < n_all;
                 if (act && (lx | ly) >= T) { s_acc[5] = 1u; act = false; }             // never seen: the record does not lie in this tile
-                int4 nrec = rec; bool stays = false;
+                int4 nrec = rec; bool stays = false; unsigned key = 0u; float dd = 0.0f;
                 if (act) {
+                    const U4 w = philox4x32_10(p.env_offset + (unsigned)rec.w, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
                     const unsigned ic = (ly << TSH) | lx;
                     const float4 row = lds_f4(sq + ic * 16u);
                     const unsigned mvb = lds_u8(smv + ic);
                     int a = argmax4(row);
-                    if ((draws >> (3u * q)) & 4u) a = (int)((draws >> (3u * q)) & 3u);
+                    if ((w.x >> 8) < c.eps_thr) a = (int)(w.y & 3u);
                     const bool blocked = (mvb >> a) & 1u, done = (mvb >> (a + 4)) & 1u;
                     // per action: dx = {0, 1, 0, -1}, dy = {-1, 0, 1, 0}, one signed byte each
                     const int dx = blocked ? 0 : (int)(signed char)(0xFF000100u >> (8 * a)), dy = blocked ? 0 : (int)(signed char)(0x000100FFu >> (8 * a));
@@ -383,37 +383,36 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     else m = lds_f32(shalo + 4u * ((int)my < 0 ? lx : my >= T ? T + lx : (int)mx < 0 ? 2u * T + ly : 3u * T + ly));
                     if (p.legacy_clamp && m < 0.0f) m = 0.0f;
                     const float r = (blocked && p.ntraps) ? blocked_step_reward(p, rec.x, rec.y, a) : -0.01f;     // a trap charges its penalty
-                    dd[q] = done ? 1.0f : __fmaf_rn(p.gamma, m, r);                  // the TD target of (cell, a), from Q_t
+                    dd = done ? 1.0f : __fmaf_rn(p.gamma, m, r);                     // the TD target of (cell, a), from Q_t
                     if (TRACE) { p.tr_a[rec.w] = a; p.tr_r[rec.w] = done ? 1.0f : r; p.tr_d[rec.w] = done ? 1 : 0; }
                     const unsigned idx = ic * 4u + (unsigned)a, sh = 16u * ((unsigned)a & 1u);
                     const unsigned old = atoms_add(sn + (idx >> 1) * 4u, 1u << sh);
-                    key[q] = ((((old >> sh) & 0xFFFFu) == 0u) ? 0x40000000u : 0u) | idx;
+                    key = ((((old >> sh) & 0xFFFFu) == 0u) ? 0x40000000u : 0u) | idx;
                     nrec.x = rec.x + dx; nrec.y = rec.y + dy; nrec.z = rec.z + 1;
-                    if (done || nrec.z >= c.tmax) {
-                        const unsigned sn2 = sample_start(p, p.env_offset + (unsigned)rec.w, g + 1ull, TAG_START);
-                        nrec.y = (int)(sn2 / (unsigned)p.W); nrec.x = (int)(sn2 - (unsigned)nrec.y * (unsigned)p.W); nrec.z = 0;
-                        stays = (((unsigned)(nrec.x - tx0)) | ((unsigned)(nrec.y - ty0))) < T;
+                    if (done || nrec.z >= c.tmax) {        // the episode ends: the start cell of the next one is drawn when the record is sent (below)
+                        nrec.z = -1; stays = false;
                         atomicAdd(&s_acc[done ? 0 : 1], 1u);
                     }
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" :: "r"(skd + j * 8u), "r"(key), "r"(__float_as_uint(dd)) : "memory");
                 }
-                // a record that leaves is queued in shared memory; its atomic goes out when the tile is done
+                // a record that leaves goes back into its slot and the slot's number into the queue; it is sent when the tile is done
                 const bool leaves = put_stay(act, stays, nrec);
                 const unsigned lm = __ballot_sync(FULL, leaves);
-                if (lm) {
-                    const unsigned qpos = nleave + __popc(lm & lt);
-                    nleave += __popc(lm);
-                    if (leaves) {
-                        if (qpos < 32u) asm volatile("st.shared.v4.s32 [%0], {%1, %2, %3, %4};" :: "r"(sleave + qpos * 16u), "r"(nrec.x), "r"(nrec.y), "r"(nrec.z), "r"(nrec.w) : "memory");
-                        else { const unsigned dt = tile_of(tp, nrec.x, nrec.y); store_arrival(nrec, dt, atomicAdd(&cnt_next[dt].y, 1u)); }
-                    }
+                if (leaves) {
+                    asm volatile("st.shared.v4.s32 [%0], {%1, %2, %3, %4};" :: "r"(srec + j * 16u), "r"(nrec.x), "r"(nrec.y), "r"(nrec.z), "r"(nrec.w) : "memory");
+                    asm volatile("st.shared.u8 [%0], %1;" :: "r"(sque + nleave + __popc(lm & lt)), "r"(j) : "memory");
                 }
+                nleave += __popc(lm);
             }
             __syncwarp();
             float* const qtile = reinterpret_cast<float*>(p.Q + ((size_t)ty0 * (size_t)p.W + (size_t)tx0));
-#pragma unroll
-            for (unsigned q = 0; q < PRE; ++q) {
-                if (!(key[q] & 0x40000000u)) continue;
-                const unsigned idx = key[q] & 0xFFFFu, ic = idx >> 2, a = idx & 3u;
+#pragma unroll 1
+            for (unsigned it = 0; it < rounds; ++it) {
+                const unsigned j = it * 32u + lane;
+                if (j >= n_in) continue;
+                const uint2 kd = lds_u32x2(skd + j * 8u);
+                if (!(kd.x & 0x40000000u)) continue;
+                const unsigned idx = kd.x & 0xFFFFu, ic = idx >> 2, a = idx & 3u;
                 const unsigned n = lds_u16(sn + idx * 2u);
                 const uint2 w = lds_u32x2(sn + ic * 8u);
                 const unsigned s2 = w.x + w.y, tot = (s2 & 0xFFFFu) + (s2 >> 16);       // at most 96 per tile: no carry between the fields
@@ -422,18 +421,28 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     const unsigned long long ww = ((unsigned long long)w.y << 32) | w.x;
                     if ((ww & ((1ull << (16u * a)) - 1ull)) == 0ull) { atomicAdd(&s_acc[3], 1u); atomicAdd(&s_acc[4], tot); }
                 }
+                const float d = __uint_as_float(kd.y);
                 float v = lds_f32(sq + idx * 4u);
-                for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(dd[q], v), v);      // one application per environment
+                for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(d, v), v);          // one application per environment
                 sts_f32(sq + idx * 4u, v);
                 qtile[((ic >> TSH) * (unsigned)p.W + (ic & (T - 1u))) * 4u + a] = v;    // (row inside the tile) * W + column < cells < 2^28
             }
-            // the tile's leavers: one atomic each now, the store after the border values (the counter value is on its way meanwhile)
-            pend = lane < min(nleave, 32u);
             __syncwarp();
-            if (pend) {
-                asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(pend_rec.x), "=r"(pend_rec.y), "=r"(pend_rec.z), "=r"(pend_rec.w) : "r"(sleave + lane * 16u) : "memory");
-                pend_dt = tile_of(tp, pend_rec.x, pend_rec.y);
-                pend_pos = atomicAdd(&cnt_next[pend_dt].y, 1u);
+            // the tile's leavers, one lane each: draw the start cell of a new episode where one ended, one atomic on the new tile's
+            // arrival counter; the first 32 are stored after the border values (the counter value is on its way meanwhile)
+            for (unsigned base = 0; base < nleave; base += 32u) {
+                if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
+                pend = base + lane < nleave;
+                if (pend) {
+                    const unsigned slot = lds_u8(sque + base + lane);
+                    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(pend_rec.x), "=r"(pend_rec.y), "=r"(pend_rec.z), "=r"(pend_rec.w) : "r"(srec + slot * 16u) : "memory");
+                    if (pend_rec.z < 0) {
+                        const unsigned sn2 = sample_start(p, p.env_offset + (unsigned)pend_rec.w, g + 1ull, TAG_START);
+                        pend_rec.y = (int)(sn2 / (unsigned)p.W); pend_rec.x = (int)(sn2 - (unsigned)pend_rec.y * (unsigned)p.W); pend_rec.z = 0;
+                    }
+                    pend_dt = tile_of(tp, pend_rec.x, pend_rec.y);
+                    pend_pos = atomicAdd(&cnt_next[pend_dt].y, 1u);
+                }
             }
 #pragma unroll
             for (unsigned kk = 0; kk < T2 / 32u; ++kk) sts_zero8(sn + (kk * 32u + lane) * 8u);
@@ -471,13 +480,12 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 if (j >= n_all) return make_int4(0, 0, 0, 0);
                 return j < n_front ? in[roff + j] : j < n_in ? arr_in[(size_t)tile * ARR_CAP + (j - n_front)] : ovf_in[j - n_in];
             };
-            int4 ahead = fetch(PRE * 32u + lane);                     // one round ahead of the loop: its latency hides behind a round of work
+            int4 ahead = fetch(lane);                                 // one round ahead of the loop: its latency hides behind a round of work
             for (unsigned it = 0; it * 32u < n_all; ++it) {
                 const unsigned j = it * 32u + lane;
                 bool act = j < n_all;
-                int4 rec = it == 0u ? pre[0] : it == 1u ? pre[1] : pre[2];
-                if (it >= PRE) { rec = ahead; ahead = fetch(j + 32u); }
-                else if (act && j >= n_in) rec = ovf_in[j - n_in];     // a spill list next to a small tile: the first rounds read it directly
+                const int4 rec = ahead;
+                ahead = fetch(j + 32u);
                 if (act && j >= n_in) act = tile_of(tp, rec.x, rec.y) == tile;
                 const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
                 if (act && (lx | ly) >= T) { s_acc[5] = 1u; act = false; }
@@ -518,7 +526,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 }
             } else nocc = gcnt ? T2 : 0u;
 #pragma unroll
-            for (unsigned r = 0; r < BR; ++r) if (lane + 32u * r < 4u * T) s_bm[lane + 32u * r] = max4(s_q[ring_cell(lane + 32u * r)]);
+            for (unsigned r = 0; r < BR; ++r) if (lane + 32u * r < 4u * T) s_bm[lane + 32u * r] = max4(s_q[(b_pack >> (16u * r)) & 0xFFu]);
             __syncwarp();
 
             // ---- Q_{t+1} of the occupied cells, from Q_t in shared memory straight into the table -----------------
@@ -554,11 +562,12 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
         // ---- border values out: max_a Q_{t+1} of my border ring into the neighbours' blocks of the other parity ----------
         {
             float* const hbase = halo_out + (size_t)tile * (4u * T);
+            // which of the four neighbours exist: bit e = north, south, west, east
+            const unsigned have = (tyi > 0u ? 1u : 0u) | (tyi + 1u < tp.tiles_y ? 2u : 0u) | (txi > 0u ? 4u : 0u) | (txi + 1u < tp.tiles_x ? 8u : 0u);
 #pragma unroll
             for (unsigned r = 0; r < BR; ++r) {
-                const unsigned kk = lane + 32u * r, e = kk >> TSH;
-                const bool there = kk < 4u * T && (e == 0u ? tyi > 0u : e == 1u ? tyi + 1u < tp.tiles_y : e == 2u ? txi > 0u : txi + 1u < tp.tiles_x);
-                if (there) hbase[ring_dst(kk)] = fast ? max4(lds_f4(sq + ring_cell(kk) * 16u)) : s_bm[kk];
+                const unsigned kk = lane + 32u * r, ent = b_pack >> (16u * r);
+                if (kk < 4u * T && ((have >> ((ent >> 8) & 3u)) & 1u)) hbase[b_dst[r]] = fast ? max4(lds_f4(sq + (ent & 0xFFu) * 16u)) : s_bm[kk];
             }
         }
         if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
@@ -719,7 +728,7 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const 
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 static inline unsigned capped_blocks(size_t n) { const size_t b = (n + BLOCK - 1) / BLOCK; return (unsigned)(b < 1 ? 1 : (b > 2368 ? 2368 : b)); }
 
-constexpr unsigned MINB16 = 5, MINB8 = 5;     // resident blocks per SM the register budget is cut for: the most that compiles without spills
+constexpr unsigned MINB16 = 6, MINB8 = 6;     // resident blocks per SM the register budget is cut for: the most that compiles without spills
 size_t tile_step_smem(const Params& p) { return (size_t)WPB * (p.tp.tshift == 4u ? WarpSmem<4>::BYTES : WarpSmem<3>::BYTES); }
 unsigned tile_cls_stride(unsigned tshift) { return tshift == 4u ? WarpSmem<4>::CLS : WarpSmem<3>::CLS; }
 
