@@ -318,6 +318,9 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     for (unsigned tile = gw; tile < tp.ntiles; tile += nw) {
         issue(tile, txi, tyi, hw);
         hw = fetch_hdr(tile + nw);                              // in flight while this tile is worked on
+        // the previous tile's leavers: their arrival counters were bumped before its border values went out; the stores go
+        // out now, while this tile's copies are in flight
+        if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
         const unsigned n_all = n_in + n_spill;
         const int tx0 = (int)(txi << TSH), ty0 = (int)(tyi << TSH);
         const unsigned char* st = wb;
@@ -429,7 +432,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             }
             __syncwarp();
             // the tile's leavers, one lane each: draw the start cell of a new episode where one ended, one atomic on the new tile's
-            // arrival counter; the first 32 are stored after the border values (the counter value is on its way meanwhile)
+            // arrival counter; the last 32 (normally all) are stored when the next tile's copies have been issued
             for (unsigned base = 0; base < nleave; base += 32u) {
                 if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
                 pend = base + lane < nleave;
@@ -570,12 +573,13 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 if (kk < 4u * T && ((have >> ((ent >> 8) & 3u)) & 1u)) hbase[b_dst[r]] = fast ? max4(lds_f4(sq + (ent & 0xFFu) * 16u)) : s_bm[kk];
             }
         }
-        if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
         fence_async_smem();                                      // this lane's reads of the stage come before the copies that will refill it
         __syncwarp();                                            // every lane is done with the tile
         txi += dtx; tyi += dty;
         if (txi >= tp.tiles_x) { txi -= tp.tiles_x; ++tyi; }
     }
+
+    if (pend) store_arrival(pend_rec, pend_dt, pend_pos);
 
     // ---- run statistics: warp -> block -> one atomic per counter and block ----------------------------------
     for (int o = 16; o; o >>= 1) conf += __shfl_xor_sync(FULL, conf, o);
