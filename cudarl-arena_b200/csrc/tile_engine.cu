@@ -6,24 +6,30 @@
 //   * the grid is cut into T x T tiles (16 x 16 cells, or 8 x 8 on densely populated grids); the environments
 //     are kept bucketed by tile (records {x,y,t,id});
 //   * a warp owns a tile for the whole step and needs no block-wide barrier: it fetches the tile of Q_t with
-//     ONE tensor copy (cp.async.bulk.tensor, a T x T box of float4 out of the row-major table), plus the
-//     tile's class bytes and its border values, completion on the warp's own mbarrier; while the copies are
-//     in flight it already holds the tile's first records in registers and the next tile's header;
+//     ONE tensor copy (cp.async.bulk.tensor, a T x T box of float4 out of the row-major table) and the tile's
+//     records with two bulk copies, completion on the warp's own mbarrier; the tile's move bytes and border
+//     values (16 bytes per lane) and the next tile's header are loaded while the copies are in flight;
 //   * every environment of the tile is stepped against shared memory: epsilon-greedy from the Philox
 //     stream keyed by (seed, global env, step), move with obstacle / goal lookup, auto-reset;
 //   * the TD updates of a cell are applied from a histogram of (cell, action) counts: inside one step the
 //     target of an update depends on (cell, action) only, so n environments on one (cell, action) mean the
 //     same map applied n times -- the same bits as the oracle's sequential order, without sorting anything
 //     and without float atomics;
-//   * the table is updated IN PLACE: only the rows of occupied cells are stored (16 bytes each, straight from
+//   * the table is updated IN PLACE: only the entries that were updated are stored (4 bytes each, straight from
 //     registers), and no other warp reads this tile's cells in this step.  The one thing a neighbour needs
 //     from a tile -- max_a Q of the cell just beyond the shared edge, for the TD target of a move across the
 //     edge -- travels through a border array: at the end of its step a tile stores the max of every cell of
 //     its border ring (taken from Q_{t+1}) into its four neighbours' slots of the OTHER parity;
 //   * an environment that stays in the tile is appended to the tile's region of the other record array
-//     (positions from a warp ballot, no atomics); one that leaves (a walk across the edge, a restart anywhere)
-//     is appended to its new tile's arrival buffer with one atomic; a full arrival buffer spills to a global
-//     list that every warp filters.  Regions are re-sized from the actual populations every few steps.
+//     (positions from a warp ballot, no atomics); one that leaves (a walk across the edge, the end of an episode:
+//     the next one starts on a seeded cell anywhere) is appended to its new tile's arrival buffer with one atomic;
+//     a full arrival buffer spills to a global list that every warp filters.  Regions are re-sized from the actual
+//     populations every few steps.
+//
+// What bounds the kernel (B200, 4096 x 4096 cells, 4,194,304 environments): the memory time of its 513 MB per step and the
+// issue time of its ~1,100 instructions per tile add up with little overlap inside a warp; resident warps (24 per SM: 78
+// registers, 9.1 KB of shared memory each) hide the rest.  The tile loop is rolled and reads its records from shared
+// memory on purpose: unrolled over register-held records it outgrew the instruction cache.
 //
 // Reference semantics (paths relative to the CudaRL-Arena project root):
 //   step        src/environment.cu:17-48, obstacle test src/kernels.cu:29-44, goal src/kernels.cu:56-59
