@@ -360,8 +360,12 @@ int alloc_tiles(cudarl_ctx* c) {
     tp.cls_stride = tile_cls_stride(tsh);
     CK(cudaMalloc(&c->dtcls, nt * tp.cls_stride));
     tp.tcls = (unsigned char*)c->dtcls;
-    CK(cudaMalloc(&c->dtscratch, (N > 65536 ? N : 65536) * sizeof(uint2)));
-    tp.scratch = (uint2*)c->dtscratch;
+    // 16 bytes per cell of every tile that counts in global memory: on 16 x 16 tiles that is every tile the general path takes
+    // (in the worst case -- a step with a spill list -- all of them), on 8 x 8 tiles only tiles with more than 65,535 records
+    size_t scratch_cap = N > 65536 ? N : 65536;
+    if (tsh >= 4 && nt * tp.T * tp.T * 2 > scratch_cap) scratch_cap = nt * tp.T * tp.T * 2;
+    CK(cudaMalloc(&c->dtscratch, scratch_cap * sizeof(uint2)));
+    tp.scratch = (uint2*)c->dtscratch; tp.scratch_cap = (unsigned)scratch_cap;
     tp.wait_polls = 0;
     { int rm = make_table_map(c); if (rm) return rm; }
     if (tile_engine_configure(p, c->cfg.device) != 0) { cudaGetLastError(); return fail(c, -5, "tile step: shared memory request refused"); }
@@ -895,7 +899,7 @@ int cudarl_kernel_timing(cudarl_ctx* c, int on) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));
     if (on && c->kev.empty()) {
-        c->kev.resize(2 * 256);
+        c->kev.resize(2 * 2048);
         for (auto& e : c->kev) CK(cudaEventCreate(&e));
     }
     if (!on) { int rc = drain_kernel_events(c); if (rc) return rc; }

@@ -62,7 +62,8 @@ struct TileP {
     unsigned char* tcls;       // ntiles x cls_stride: one move byte per cell, tile by tile (which of the four moves are blocked / end on a goal)
     unsigned cls_stride;
     float* bmax[2];            // ntiles x 4T: max_a Q of the cells just outside the tile's north / south / west / east edge; [step & 1] is current
-    uint2* scratch;            // N x 8 bytes: 32-bit (cell, action) counters of tiles with more than 65,535 records
+    uint2* scratch;            // scratch_cap x 8 bytes: 32-bit (cell, action) counters of the tiles the general path counts in global memory
+    unsigned scratch_cap;
     CUtensorMap tmq;           // the table as a 2-D tensor of floats (4W x H), box 4T x T: one copy instruction per tile
 };
 

@@ -44,7 +44,7 @@ namespace cudarl {
 constexpr unsigned CROWDED_CELL = 24;   // a cell with more environments than this counts as "crowded" in the run statistics
 constexpr unsigned NMAX16 = 65535u;     // records of a tile the 16-bit counters can hold
 constexpr unsigned WPB = 4;             // warps per block; every warp works on its own
-constexpr unsigned FAST_MAX = 96;       // records of a tile the fast path stages in shared memory
+constexpr unsigned FAST_MAX = 128;      // records of a tile the fast path stages in shared memory (a multiple of 32, below 256)
 
 __device__ __forceinline__ unsigned tile_of(const TileP& tp, int x, int y) {
     return ((unsigned)y >> tp.tshift) * tp.tiles_x + ((unsigned)x >> tp.tshift);
@@ -109,6 +109,7 @@ __device__ __forceinline__ void tensor_g2s_2d(void* dst, const CUtensorMap* map,
 __device__ __forceinline__ float4 lds_f4(unsigned a) { float4 v; asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ float lds_f32(unsigned a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ unsigned lds_u8(unsigned a) { unsigned v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ unsigned lds_u32(unsigned a) { unsigned v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ unsigned lds_u16(unsigned a) { unsigned v; asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ uint2 lds_u32x2(unsigned a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ void sts_f32(unsigned a, float v) { asm volatile("st.shared.f32 [%0], %1;" :: "r"(a), "f"(v) : "memory"); }
@@ -152,12 +153,14 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 //   s_mv   T*T  u8       per cell: bit a = a move in direction a is blocked (grid edge or obstacle), bit 4+a = the
 //                        cell an environment stands on after choosing a (the next cell, or its own when blocked) is a goal
 //   s_halo 4T   float    max_a Q_t of the cells beyond the north / south / west / east edge (from the border array)
-//   s_rec  96   int4     fast path: the tile's records (bulk copies); a record that leaves the tile is written back here
+//   s_rec  128  int4     fast path: the tile's records (bulk copies); a record that leaves the tile is written back here
 // and the work area:
-//   s_n    T*T  u64      per cell: how many environments chose action a, 16 bits per action; zero between tiles
-//   s_kd   96   u32+f32  fast path: per record its key (cell, action, owner flag) and TD target, from the step to the owner pass
-//   s_que  96   u8       fast path: the slots of the records that leave the tile
-//   s_bm   4T   float    general path: max_a Q_{t+1} of the tile's own north / south / west / east border cells
+//   s_n    T*T  words    per cell: how many environments chose action a; zero between tiles.  8-byte words with 16 bits per action on
+//                        8 x 8 tiles; on 16 x 16 tiles 4-byte words with 8 bits per action (the fast path counts at most 128 records,
+//                        the general path counts in global scratch there): the kilobyte saved pays for 128 instead of 96 staged records
+//   s_kd   128  u32+f32  fast path: per record its key (cell, action, owner flag) and TD target, from the step to the owner pass
+//   s_que  128  u8       fast path: the slots of the records that leave the tile
+//   s_bm   4T   float    general path: max_a Q_{t+1} of the tile's own north / south / west / east border cells (shares the bytes of s_kd)
 //   s_list T*T  u16      general path: the occupied cells (shares the bytes of s_rec)
 // A tile with more than 65,535 records counts in 32-bit counters in global scratch instead.
 template <unsigned TSH> struct WarpSmem {
@@ -165,9 +168,13 @@ template <unsigned TSH> struct WarpSmem {
     static constexpr unsigned CLS = T2;                              // a multiple of 16 for T = 8 and 16
     static constexpr unsigned ST_MV = T2 * 16u, ST_HALO = ST_MV + CLS, ST_REC = ST_HALO + 4u * T * 4u;
     static constexpr unsigned REC_BYTES = FAST_MAX * 16u > T2 * 2u ? FAST_MAX * 16u : T2 * 2u;
-    static constexpr unsigned OFF_N = ST_REC + REC_BYTES, OFF_KD = OFF_N + T2 * 8u, OFF_QUE = OFF_KD + FAST_MAX * 8u,
-                              OFF_BM = OFF_QUE + FAST_MAX;
-    static constexpr unsigned BYTES = (OFF_BM + 4u * T * 4u + 127u) / 128u * 128u;
+    static constexpr bool NARROW = TSH >= 4u;                        // 8-bit counters in shared memory; the general path then counts in global scratch
+    static constexpr unsigned CELL_BYTES = NARROW ? 4u : 8u;
+    static constexpr unsigned OFF_N = ST_REC + REC_BYTES, OFF_KD = OFF_N + T2 * CELL_BYTES, OFF_QUE = OFF_KD + FAST_MAX * 8u,
+                              OFF_BM = OFF_KD;
+    static constexpr unsigned BYTES = (OFF_QUE + FAST_MAX + 127u) / 128u * 128u;
+    static_assert(4u * T * 4u <= FAST_MAX * 8u, "s_bm must fit into the bytes of s_kd");
+    static_assert(FAST_MAX < 256u && FAST_MAX % 32u == 0u, "8-bit counters and whole rounds");
     static constexpr unsigned HALO_LANES = T, MV_LANES = T2 / 16u;   // lanes that fetch 16 bytes each of the border values / move bytes
 };
 
@@ -252,7 +259,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
 
     if (threadIdx.x < 6u) s_acc[threadIdx.x] = 0u;
     if (lane == 0) mbar_init(&s_bar[warp], 1u);
-    for (unsigned q = lane; q < T2; q += 32u) s_n[q] = 0ull;
+    for (unsigned q = lane; q < T2 * L::CELL_BYTES / 4u; q += 32u) reinterpret_cast<unsigned*>(s_n)[q] = 0u;
     if (gw == 0u && lane == 0u) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
     __syncthreads();
 
@@ -296,7 +303,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     auto issue = [&](unsigned tile, unsigned txi, unsigned tyi, const uint2 hw) {
         roff = __shfl_sync(FULL, hw.x, 0); fcap = __shfl_sync(FULL, hw.y, 0);
         n_front = min(__shfl_sync(FULL, hw.x, 1), fcap); n_in = n_front + min(__shfl_sync(FULL, hw.y, 1), ARR_CAP);
-        const bool stage_records = n_in <= FAST_MAX && n_spill == 0u;
+        const bool stage_records = n_in + n_spill <= FAST_MAX;        // room even if every spilled record were this tile's
         if (lane == 0u) mbar_arrive_expect_tx(bar, T2 * 16u + (stage_records ? n_in * 16u : 0u));
         __syncwarp();
         if (lane == 0u) tensor_g2s_2d(wb, &tp.tmq, (int)(txi << TSH) * 4, (int)(tyi << TSH), bar);
@@ -356,20 +363,31 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             return act && !placed;
         };
 
-        const bool fast = n_in <= FAST_MAX && n_spill == 0u;     // warp-uniform: the tile's records are in shared memory
+        const bool fast = n_in + n_spill <= FAST_MAX;            // warp-uniform: the tile's records are in shared memory
         if (fast) {
+            // A short spill list (records that found an arrival buffer full in the last step) is filtered here: what belongs to this
+            // tile joins the staged records.  Only a long list sends a tile to the general path.
+            unsigned n_tot = n_in;
+            for (unsigned base = 0; base < n_spill; base += 32u) {
+                int4 r = make_int4(0, 0, 0, 0); bool mine = false;
+                if (base + lane < n_spill) { r = ovf_in[base + lane]; mine = tile_of(tp, r.x, r.y) == tile; }
+                const unsigned mm = __ballot_sync(FULL, mine);
+                if (mine) asm volatile("st.shared.v4.s32 [%0], {%1, %2, %3, %4};" :: "r"(srec + (n_tot + __popc(mm & lt)) * 16u), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+                n_tot += __popc(mm);
+            }
+            if (n_spill) __syncwarp();
             // ---- few records: everything an update needs passes through shared memory once ------------------------
             // Each environment computes the TD target of its own (cell, action) -- it has the next cell at hand -- and
             // counts itself; the FIRST to count on a (cell, action) owns it and, once every count is in, applies the
             // map that many times to the one table entry: a 4-byte store into the table, and into the tile in shared
             // memory, which thereby becomes Q_{t+1} for the border values.  The loops are rolled on purpose: the tile
             // loop has to stay inside the instruction cache.
-            const unsigned rounds = (n_in + 31u) >> 5;
+            const unsigned rounds = (n_tot + 31u) >> 5;
             unsigned nleave = 0;
 #pragma unroll 1
             for (unsigned it = 0; it < rounds; ++it) {
                 const unsigned j = it * 32u + lane;
-                bool act = j < n_in;
+                bool act = j < n_tot;
                 int4 rec = make_int4(0, 0, 0, 0);
                 if (act) asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(rec.x), "=r"(rec.y), "=r"(rec.z), "=r"(rec.w) : "r"(srec + j * 16u) : "memory");
                 const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
@@ -394,9 +412,11 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     const float r = (blocked && p.ntraps) ? blocked_step_reward(p, rec.x, rec.y, a) : -0.01f;     // a trap charges its penalty
                     dd = done ? 1.0f : __fmaf_rn(p.gamma, m, r);                     // the TD target of (cell, a), from Q_t
                     if (TRACE) { p.tr_a[rec.w] = a; p.tr_r[rec.w] = done ? 1.0f : r; p.tr_d[rec.w] = done ? 1 : 0; }
-                    const unsigned idx = ic * 4u + (unsigned)a, sh = 16u * ((unsigned)a & 1u);
-                    const unsigned old = atoms_add(sn + (idx >> 1) * 4u, 1u << sh);
-                    key = ((((old >> sh) & 0xFFFFu) == 0u) ? 0x40000000u : 0u) | idx;
+                    const unsigned idx = ic * 4u + (unsigned)a;
+                    bool first;
+                    if (L::NARROW) { const unsigned old = atoms_add(sn + ic * 4u, 1u << (8u * (unsigned)a)); first = ((old >> (8u * (unsigned)a)) & 0xFFu) == 0u; }
+                    else { const unsigned sh = 16u * ((unsigned)a & 1u), old = atoms_add(sn + (idx >> 1) * 4u, 1u << sh); first = ((old >> sh) & 0xFFFFu) == 0u; }
+                    key = (first ? 0x40000000u : 0u) | idx;
                     nrec.x = rec.x + dx; nrec.y = rec.y + dy; nrec.z = rec.z + 1;
                     if (done || nrec.z >= c.tmax) {        // the episode ends: the start cell of the next one is drawn when the record is sent (below)
                         nrec.z = -1; stays = false;
@@ -418,18 +438,23 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
 #pragma unroll 1
             for (unsigned it = 0; it < rounds; ++it) {
                 const unsigned j = it * 32u + lane;
-                if (j >= n_in) continue;
+                if (j >= n_tot) continue;
                 const uint2 kd = lds_u32x2(skd + j * 8u);
                 if (!(kd.x & 0x40000000u)) continue;
                 const unsigned idx = kd.x & 0xFFFFu, ic = idx >> 2, a = idx & 3u;
-                const unsigned n = lds_u16(sn + idx * 2u);
-                const uint2 w = lds_u32x2(sn + ic * 8u);
-                const unsigned s2 = w.x + w.y, tot = (s2 & 0xFFFFu) + (s2 >> 16);       // at most 96 per tile: no carry between the fields
-                if (tot > 1u) conf += n;
-                if (tot > CROWDED_CELL) {                                              // the lowest chosen action speaks for the cell
-                    const unsigned long long ww = ((unsigned long long)w.y << 32) | w.x;
-                    if ((ww & ((1ull << (16u * a)) - 1ull)) == 0ull) { atomicAdd(&s_acc[3], 1u); atomicAdd(&s_acc[4], tot); }
+                unsigned n, tot; bool lowest;                                          // count of (cell, a), of the cell; no lower action was chosen
+                if (L::NARROW) {
+                    const unsigned w = lds_u32(sn + ic * 4u);
+                    n = (w >> (8u * a)) & 0xFFu; tot = __dp4a(w, 0x01010101u, 0u); lowest = (w & ((1u << (8u * a)) - 1u)) == 0u;
+                } else {
+                    n = lds_u16(sn + idx * 2u);
+                    const uint2 w = lds_u32x2(sn + ic * 8u);
+                    const unsigned s2 = w.x + w.y;                                     // at most 128 per tile: no carry between the fields
+                    tot = (s2 & 0xFFFFu) + (s2 >> 16);
+                    lowest = ((((unsigned long long)w.y << 32) | w.x) & ((1ull << (16u * a)) - 1ull)) == 0ull;
                 }
+                if (tot > 1u) conf += n;
+                if (tot > CROWDED_CELL && lowest) { atomicAdd(&s_acc[3], 1u); atomicAdd(&s_acc[4], tot); }      // the lowest chosen action speaks for the cell
                 const float d = __uint_as_float(kd.y);
                 float v = lds_f32(sq + idx * 4u);
                 for (unsigned i = 0; i < n; ++i) v = __fmaf_rn(p.lr, __fsub_rn(d, v), v);          // one application per environment
@@ -454,7 +479,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 }
             }
 #pragma unroll
-            for (unsigned kk = 0; kk < T2 / 32u; ++kk) sts_zero8(sn + (kk * 32u + lane) * 8u);
+            for (unsigned kk = 0; kk < T2 * L::CELL_BYTES / 256u; ++kk) sts_zero8(sn + (kk * 32u + lane) * 8u);
         } else {
             // How many records are really this tile's decides the counter width.  Records of the spill list belong to any tile, so a
             // long list is counted first (one more pass over it) instead of sending every tile of the grid to the wide counters.
@@ -467,13 +492,13 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     n_mine += __popc(__ballot_sync(FULL, mine));
                 }
             }
-            const bool crowded = n_mine > NMAX16;                   // warp-uniform
+            const bool crowded = L::NARROW || n_mine > NMAX16;      // warp-uniform
             unsigned* gcnt = nullptr;
             if (crowded) {                                           // 4 x 32-bit counters per cell in global scratch
                 unsigned q = 0;
                 if (lane == 0u) {
                     q = atomicAdd(&tp.tctl[3u + par], T2 * 2u);
-                    if (q + T2 * 2u > p.N) { q = 0xFFFFFFFFu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
+                    if (q + T2 * 2u > tp.scratch_cap) { q = 0xFFFFFFFFu; atomicOr(&p.ctl->error, ERR_SCRATCH_OVERFLOW); }
                 }
                 q = __shfl_sync(FULL, q, 0);
                 if (q != 0xFFFFFFFFu) {
