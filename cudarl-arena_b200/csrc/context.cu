@@ -327,8 +327,9 @@ int make_table_map(cudarl_ctx* c) {
     return 0;
 }
 
-// Tile edge: 16 cells where a 16 x 16 tile holds at most ~128 environments on average, else 8 (a warp steps a
-// tile's environments 32 at a time; measured on B200, about 64 per tile keeps the warps short and even).
+// Tile edge: 16 cells while a 16 x 16 tile holds few enough environments for most tiles to stay on the step kernel's fast
+// path (at most 128 staged records), else 8.  Measured on B200, 4096 x 4096 cells, us per step with edge 16 / edge 8:
+// 64 per tile 124 / 250, 96 per tile 182 / 271, 128 per tile 731 / 323 -- the crossover lies near 110.
 int alloc_tiles(cudarl_ctx* c) {
     Params& p = c->p; TileP& tp = p.tp;
     const size_t S = p.S, N = p.N ? p.N : 1;
@@ -336,7 +337,7 @@ int alloc_tiles(cudarl_ctx* c) {
     CK(cudaMemsetAsync(c->dQ, 0, (S + 64) * sizeof(float4), c->st));
     p.Q = (float4*)c->dQ;
     const size_t nt16 = (((size_t)p.W + 15) >> 4) * (((size_t)p.H + 15) >> 4);
-    unsigned tsh = (N / nt16 <= 128) ? 4u : 3u;
+    unsigned tsh = (N / nt16 <= 104) ? 4u : 3u;
     if (c->cfg.tile_edge == 8) tsh = 3u; else if (c->cfg.tile_edge == 16) tsh = 4u;
     tp.tshift = tsh; tp.T = 1u << tsh;
     tp.tiles_x = (unsigned)((p.W + (int)tp.T - 1) >> tsh); tp.tiles_y = (unsigned)((p.H + (int)tp.T - 1) >> tsh);
