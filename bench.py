@@ -396,10 +396,12 @@ def main():
         ev_rate = ev_steps / (ev_ms * 1e-3)
         ev = {"value": ev_rate, "unit": "env-steps/s", "ms": ev_ms, "step_cap": args.eval_steps, "env_steps": ev_steps,
               "reached_fraction": ev_reached / float(n_local * world),
-              "roofline": {"bound": "hbm", "kernel": "k_eval", "algorithmic_bytes_per_env_step": ALGO_BYTES_EVAL,
+              "roofline": {"bound": "hbm", "kernel": "k_eval_policy + k_eval", "algorithmic_bytes_per_env_step": ALGO_BYTES_EVAL,
                            "achieved": ALGO_BYTES_EVAL * ev_rate / world / 1e9, "peak": peak, "unit": "GB/s",
                            "frac": ALGO_BYTES_EVAL * ev_rate / world / 1e9 / peak, "peak_kind": peak_kind,
-                           "note": "includes the host call and its synchronising read of the result"}}
+                           "note": "includes the host call and its synchronising read of the result; the rollout folds the table into a "
+                                   "one-byte-per-cell policy map once (k_eval_policy) and then reads one byte per environment-step, so "
+                                   "against the 40 B per env-step of a rollout that reads Q[s] every step frac can exceed 1"}}
 
     if rank != 0:
         return

@@ -83,6 +83,7 @@ struct cudarl_ctx {
     std::vector<uint8_t> cells;           // host copy of the cell classes
     std::map<uint32_t, float> traps;      // cell -> penalty; mirrored on the device as a table sorted by cell
     void* dtraps = nullptr; size_t traps_cap = 0;
+    void* dpolicy = nullptr;                // greedy policy map of the evaluation rollout (one byte per cell), allocated on first use
     // device buffers
     void *dci = nullptr, *dreward = nullptr, *ddone = nullptr;
     void *dstate[2] = {nullptr, nullptr};   // int4 {x,y,t,id} per environment, and a scratch copy of the same size
@@ -462,7 +463,7 @@ void free_all(cudarl_ctx* c) {
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->dgather, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6],
                     c->dQ, c->drec[0], c->drec[1], c->darr[0], c->darr[1], c->dovf[0], c->dovf[1], c->dbmax[0], c->dbmax[1],
-                    c->dtmeta, c->dtscratch, c->dtcls, c->dtraps};
+                    c->dtmeta, c->dtscratch, c->dtcls, c->dtraps, c->dpolicy};
     for (void* b : bufs) if (b) cudaFree(b);
     if (c->h_eps) cudaFreeHost(c->h_eps);
     for (auto e : c->kev) cudaEventDestroy(e);
@@ -693,7 +694,8 @@ int cudarl_eval_rollout(cudarl_ctx* c, int32_t max_steps, cudarl_eval_stats* out
     { int rl = leave_tiles(c); if (rl) return rl; }
     if (c->cls_dirty) { launch_tile_classes(c->p, c->st); c->cls_dirty = false; }       // the rollout reads the per-tile move bytes
     k_ctl_eval_clear<<<1, 1, 0, c->st>>>(c->p.ctl);
-    launch_eval(c->p, max_steps, (unsigned long long)c->eval_calls, c->st);
+    if (!c->dpolicy) CK(cudaMalloc(&c->dpolicy, c->p.S));                                // one byte per cell, kept until the context goes
+    launch_eval(c->p, (unsigned char*)c->dpolicy, max_steps, (unsigned long long)c->eval_calls, c->st);
     CK(cudaGetLastError());
     Ctl h; CK(cudaMemcpyAsync(&h, c->dctl, sizeof(Ctl), cudaMemcpyDeviceToHost, c->st));
     CK(cudaStreamSynchronize(c->st));

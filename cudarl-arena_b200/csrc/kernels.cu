@@ -378,45 +378,53 @@ __global__ void k_step_actions(Params p, const int* actions, float* rewards, uns
     if (dones) dones[e] = dn;
 }
 
-// Greedy rollout of every environment from a fresh start cell; positions stay in registers, the table is read-only, so
-// the whole rollout is one launch.  A step is ONE round trip to memory: the cell's row (for the argmax) and its move
-// byte (which of the four moves are blocked / end on a goal, the per-tile array of the train step) are loaded side by side.
-// Every thread walks two environments, so that two such chains overlap.
-__global__ void __launch_bounds__(BLOCK) k_eval(Params p, int max_steps, unsigned long long nonce) {
+// Greedy rollout of every environment from a fresh start cell.  The table does not change during a rollout, so the greedy
+// policy is folded into one byte per cell first (k_eval_policy: bits 0-1 the first-max action, bit 2 "that move is blocked",
+// bit 3 "it ends on a goal") -- one pass over the table -- and the rollout itself walks that map: one byte per step instead
+// of a 16-byte row and a move byte, and the map (one byte per cell) stays in L2.  Positions stay in registers, so the whole
+// rollout is one launch; every thread walks four environments, so that four dependent chains of loads overlap.
+__global__ void __launch_bounds__(BLOCK) k_eval_policy(Params p, unsigned char* __restrict__ pol) {
+    const TileP& tp = p.tp;
+    for (unsigned s = blockIdx.x * BLOCK + threadIdx.x; s < p.S; s += gridDim.x * BLOCK) {
+        const unsigned y = s / (unsigned)p.W, x = s - y * (unsigned)p.W;
+        const unsigned tile = (y >> tp.tshift) * tp.tiles_x + (x >> tp.tshift);
+        const float4 row = __ldcs(p.Q + s);
+        const unsigned mvb = __ldg(tp.tcls + (size_t)tile * tp.cls_stride + (((y & (tp.T - 1u)) << tp.tshift) | (x & (tp.T - 1u))));
+        const int a = argmax4(row);
+        pol[s] = (unsigned char)((unsigned)a | (((mvb >> a) & 1u) << 2) | (((mvb >> (4 + a)) & 1u) << 3));
+    }
+}
+constexpr int EVAL_EPT = 4;     // environments per thread
+__global__ void __launch_bounds__(BLOCK) k_eval(Params p, const unsigned char* __restrict__ pol, int max_steps, unsigned long long nonce) {
     __shared__ unsigned s_reached; __shared__ unsigned long long s_steps;
     if (threadIdx.x == 0) { s_reached = 0; s_steps = 0; }
     __syncthreads();
-    const TileP& tp = p.tp;
-    const unsigned half = (p.N + 1u) / 2u;
+    const unsigned part = (p.N + (unsigned)EVAL_EPT - 1u) / (unsigned)EVAL_EPT;
     const unsigned i0 = blockIdx.x * BLOCK + threadIdx.x;
-    if (i0 < half) {
-        int x[2], y[2]; bool live[2]; unsigned steps[2] = {0u, 0u}; unsigned reached = 0;
+    if (i0 < part) {
+        unsigned pos[EVAL_EPT]; unsigned live = 0u, reached = 0u, steps = 0u;
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const unsigned i = i0 + (unsigned)k * half;
-            live[k] = i < p.N;
-            const unsigned s = live[k] ? sample_start(p, p.env_offset + i, nonce, TAG_EVAL) : 0u;
-            y[k] = (int)(s / (unsigned)p.W); x[k] = (int)(s - (unsigned)y[k] * (unsigned)p.W);
+        for (int k = 0; k < EVAL_EPT; ++k) {
+            const unsigned i = i0 + (unsigned)k * part;
+            if (i < p.N) live |= 1u << k;
+            pos[k] = i < p.N ? sample_start(p, p.env_offset + i, nonce, TAG_EVAL) : 0u;
         }
-        for (int it = 0; it < max_steps && (live[0] || live[1]); ++it) {
-            float4 row[2]; unsigned mvb[2];
+        for (int it = 0; it < max_steps && live; ++it) {
+            unsigned b[EVAL_EPT];
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                const unsigned tile = ((unsigned)y[k] >> tp.tshift) * tp.tiles_x + ((unsigned)x[k] >> tp.tshift);
-                row[k] = __ldg(p.Q + (size_t)y[k] * (size_t)p.W + (size_t)x[k]);
-                mvb[k] = __ldg(tp.tcls + (size_t)tile * tp.cls_stride + ((((unsigned)y[k] & (tp.T - 1u)) << tp.tshift) | ((unsigned)x[k] & (tp.T - 1u))));
-            }
+            for (int k = 0; k < EVAL_EPT; ++k) b[k] = __ldg(pol + pos[k]);
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                if (!live[k]) continue;
-                const int a = argmax4(row[k]);
-                if (!((mvb[k] >> a) & 1u)) { x[k] += (a == 1) - (a == 3); y[k] += (a == 2) - (a == 0); }
-                ++steps[k];
-                if ((mvb[k] >> (4 + a)) & 1u) { ++reached; live[k] = false; }
+            for (int k = 0; k < EVAL_EPT; ++k) {
+                if (!((live >> k) & 1u)) continue;
+                const unsigned a = b[k] & 3u;
+                // per action the step in cells: up -W, right +1, down +W, left -1; none when the move is blocked
+                if (!(b[k] & 4u)) pos[k] += a == 0u ? 0u - (unsigned)p.W : a == 1u ? 1u : a == 2u ? (unsigned)p.W : 0u - 1u;
+                ++steps;
+                if (b[k] & 8u) { ++reached; live &= ~(1u << k); }
             }
         }
         if (reached) atomicAdd(&s_reached, reached);
-        atomicAdd(&s_steps, (unsigned long long)(steps[0] + steps[1]));
+        atomicAdd(&s_steps, (unsigned long long)steps);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -498,8 +506,10 @@ void launch_reset_all(const Params& p, cudaStream_t st) {
 void launch_step_actions(const Params& p, const int* a, float* r, unsigned char* d, cudaStream_t st) {
     if (p.N) k_step_actions<<<nblk(p.N), BLOCK, 0, st>>>(p, a, r, d);
 }
-void launch_eval(const Params& p, int max_steps, unsigned long long nonce, cudaStream_t st) {
-    if (p.N) k_eval<<<nblk((p.N + 1u) / 2u), BLOCK, 0, st>>>(p, max_steps, nonce);
+void launch_eval(const Params& p, unsigned char* policy, int max_steps, unsigned long long nonce, cudaStream_t st) {
+    if (!p.N) return;
+    k_eval_policy<<<nblk(p.S) < 4736u ? nblk(p.S) : 4736u, BLOCK, 0, st>>>(p, policy);
+    k_eval<<<nblk((p.N + (unsigned)EVAL_EPT - 1u) / (unsigned)EVAL_EPT), BLOCK, 0, st>>>(p, policy, max_steps, nonce);
 }
 void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* sy, const int* a, const float* r,
                          const int* nx, const int* ny, const unsigned char* dn, cudaStream_t st) {

@@ -115,7 +115,7 @@ void launch_export_state(const Params& p, cudaStream_t st);       // st2 viewed 
 void launch_import_state(const Params& p, const int* x, const int* y, const int* t, cudaStream_t st);
 void launch_reset_all(const Params& p, cudaStream_t st);
 void launch_step_actions(const Params& p, const int* d_actions, float* d_rewards, unsigned char* d_dones, cudaStream_t st);
-void launch_eval(const Params& p, int max_steps, unsigned long long nonce, cudaStream_t st);
+void launch_eval(const Params& p, unsigned char* policy, int max_steps, unsigned long long nonce, cudaStream_t st);   // policy: one byte per cell, scratch
 void launch_update_batch(const Params& p, unsigned n, const int* sx, const int* sy, const int* a, const float* r,
                          const int* nx, const int* ny, const unsigned char* dn, cudaStream_t st);
 void launch_q_init(const Params& p, int kind, float scale, cudaStream_t st);
