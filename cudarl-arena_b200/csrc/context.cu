@@ -50,6 +50,7 @@ struct NcclApi {
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;   // optional
     bool load(std::string& err) {
         if (h) return true;
         h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
@@ -62,6 +63,7 @@ struct NcclApi {
         Send = (decltype(Send))dlsym(h, "ncclSend"); Recv = (decltype(Recv))dlsym(h, "ncclRecv");
         GroupStart = (decltype(GroupStart))dlsym(h, "ncclGroupStart"); GroupEnd = (decltype(GroupEnd))dlsym(h, "ncclGroupEnd");
         GetErrorString = (decltype(GetErrorString))dlsym(h, "ncclGetErrorString");
+        CommGetAsyncError = (decltype(CommGetAsyncError))dlsym(h, "ncclCommGetAsyncError");
         if (!GetUniqueId || !CommInitRank || !CommDestroy || !AllReduce || !AllGather || !Send || !Recv || !GroupStart || !GroupEnd) { err = "NCCL symbols missing"; h = nullptr; return false; }
         return true;
     }
@@ -301,6 +303,12 @@ int check_device_error(cudarl_ctx* c) {
                          ((err & ERR_COPY_TIMEOUT) ? " (a tile copy did not land within its wait bound)" : "") +
                          ((err & ERR_SCRATCH_OVERFLOW) ? " (scratch area full)" : "") + ((err & ERR_BAD_STATE) ? " (a record outside its tile or the grid)" : "") +
                          ((err & ERR_CHAIN_CYCLE) ? " (update_batch chain longer than the batch)" : ""));
+    if (c->comm && g_nccl.CommGetAsyncError) {               // a collective that failed after it was enqueued (a peer that went away)
+        ncclResult_t ar = ncclSuccess;
+        const ncclResult_t qr = g_nccl.CommGetAsyncError(c->comm, &ar);
+        if (qr == ncclSuccess && ar != ncclSuccess && ar != ncclInProgress)
+            return fail(c, 2000 + (int)ar, std::string("replica averaging failed asynchronously: ") + (g_nccl.GetErrorString ? g_nccl.GetErrorString(ar) : "nccl error"));
+    }
     return 0;
 }
 
