@@ -158,7 +158,7 @@ def reference_python_sample(episodes=300, max_steps=500):
     ref = os.environ.get("CUDARL_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
     if not os.path.isfile(os.path.join(ref, "src", "train.py")):
         return {"unavailable": "no checkout of the reference project on this machine (its Python files are never copied; "
-                               "measured where the checkout exists: see BASELINE.md)"}
+                               "measured where the checkout exists: 42-49 k env-steps/s on one 2.7 GHz Xeon core)"}
     code = r"""
 import sys, os, types, time, tempfile, logging
 for n in ("matplotlib", "matplotlib.pyplot", "matplotlib.animation", "matplotlib.gridspec", "matplotlib.widgets"):

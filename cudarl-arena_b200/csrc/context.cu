@@ -108,6 +108,7 @@ struct cudarl_ctx {
     float eps_fixed_cached = -1.0f; bool eps_fixed_valid = false;
     // host mirror of schedule state
     int64_t h_step = 0;
+    int64_t epoch_step = 0;                 // the step at which every environment last started an episode together (creation, reset_all)
     int eps_mode = 0;                     // 0 one fixed value, 1 table indexed by step of the call, 2 per-episode (device index)
     float eps_used = 0.0f;
     double eps_running = 1.0;
@@ -446,6 +447,11 @@ int run_steps(cudarl_ctx* c, int64_t n) {
     { int re = enter_tiles(c); if (re) return re; }
     for (int64_t k = 0; k < n; ++k) {
         if (c->bucket_every > 0 && c->since_bucket >= c->bucket_every) { int rs = rebucket_tiles(c); if (rs) return rs; }
+        // Environments that started together and never reached a goal hit the step cap together: the step before this one sent
+        // them all to fresh start cells, far more arrivals than the tiles' arrival buffers hold, and the rest sits in the spill
+        // list that every tile would have to filter.  Re-bucketing now puts them into regions instead (same results either way).
+        if (c->bucket_every > 0 && c->cfg.max_steps > 0 && c->since_bucket > 0 && c->h_step > c->epoch_step &&
+            (c->h_step - c->epoch_step) % c->cfg.max_steps == 0) { int rs = rebucket_tiles(c); if (rs) return rs; }
         if (c->ktiming && !c->kseg_open) {
             if (c->kev_used + 2 > c->kev.size()) { int rc = drain_kernel_events(c); if (rc) return rc; }
             CK(cudaEventRecord(c->kev[c->kev_used], c->st));
@@ -585,6 +591,7 @@ int cudarl_reset_all(cudarl_ctx* c) {
     c->p.step = (unsigned long long)c->h_step;
     launch_reset_all(c->p, c->st);
     CK(cudaGetLastError());
+    c->epoch_step = c->h_step;
     return 0;
 }
 

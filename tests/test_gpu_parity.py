@@ -414,6 +414,31 @@ def test_region_resizing_never_changes_results(pkg, orc):
         g.close()
 
 
+def test_synchronised_step_cap_mass_restart(pkg, orc):
+    """Environments that started together and never reach a goal hit the step cap in the same step: nearly all of them draw a
+    fresh start cell at once, far more arrivals per tile than an arrival buffer holds, so the spill list carries most of the
+    population.  With the re-bucketing that the library schedules right after such a step, and without any re-bucketing
+    (every tile then filters the whole spill list), the results are the oracle's."""
+    base = pkg.preset("C5", num_envs=60000)
+    base.width, base.height, base.num_goals, base.max_steps = 500, 490, 2, 20
+    ref = orc.Oracle(base, threads=min(8, os.cpu_count() or 1))
+    ref.train_steps(45)
+    want_state, want_q, ws = ref.get_state(), ref.get_q(), ref.get_stats()
+    assert ws.timeouts > 2 * 50000                      # two mass restarts happened
+    for period in (0, -1):
+        cfg = base.copy()
+        cfg.rebucket_every = period
+        g = pkg.VecGridWorld(cfg)
+        for n in (19, 1, 1, 24):
+            g.train_steps(n)
+        for a, b in zip(g.get_state(), want_state):
+            assert np.array_equal(a, b), "period %d" % period
+        assert np.array_equal(g.get_q(), want_q), "period %d" % period
+        gs = g.get_stats()
+        assert gs.device_error == 0 and (gs.timeouts, gs.goals) == (ws.timeouts, ws.goals)
+        g.close()
+
+
 def test_odd_sizes_and_tiny_populations(pkg, orc):
     for w, h, n in [(1, 7, 5), (7, 1, 33), (13, 11, 1), (31, 3, 257), (5, 5, 0)]:
         cfg = pkg.make_config(w, h, n, start_mode=pkg.START_RANDOM, goal_mode=pkg.GOAL_SEEDED, num_goals=1,
