@@ -354,12 +354,12 @@ int alloc_tiles(cudarl_ctx* c) {
     tp.ntiles = tp.tiles_x * tp.tiles_y;
     const size_t nt = tp.ntiles;
     for (int k = 0; k < 2; ++k) {
-        CK(cudaMalloc(&c->drec[k], (N + N / 4 + 32 * nt + 64) * sizeof(int4)));
-        CK(cudaMalloc(&c->darr[k], nt * ARR_CAP * sizeof(int4)));
+        CK(cudaMalloc(&c->drec[k], (N + N / 4 + 34 * nt + 64) * sizeof(uint2)));
+        CK(cudaMalloc(&c->darr[k], nt * ARR_CAP * sizeof(uint2)));
         CK(cudaMalloc(&c->dovf[k], N * sizeof(int4)));
         CK(cudaMalloc(&c->dbmax[k], nt * 4 * tp.T * sizeof(float)));
         CK(cudaMemsetAsync(c->dbmax[k], 0, nt * 4 * tp.T * sizeof(float), c->st));
-        tp.rec[k] = (int4*)c->drec[k]; tp.arr[k] = (int4*)c->darr[k]; tp.ovf[k] = (int4*)c->dovf[k]; tp.bmax[k] = (float*)c->dbmax[k];
+        tp.rec[k] = (uint2*)c->drec[k]; tp.arr[k] = (uint2*)c->darr[k]; tp.ovf[k] = (int4*)c->dovf[k]; tp.bmax[k] = (float*)c->dbmax[k];
     }
     const size_t meta = 2 * (nt + 1) + 4 * nt + 8;          // reg (uint2 x (nt+1)), cnt[2] (uint2 x nt each), tctl
     CK(cudaMalloc(&c->dtmeta, meta * sizeof(unsigned)));
@@ -515,6 +515,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
     if (f->num_envs < 0 || f->num_envs >= (1ll << 26)) return fail(nullptr, -1, "num_envs out of range (at most 2^26 - 1 per context)");
     if (f->env_offset < 0 || f->env_offset + f->num_envs >= (1ll << 32)) return fail(nullptr, -1, "env_offset out of range");
     if (f->max_steps < 0) return fail(nullptr, -1, "max_steps negative");
+    if (f->max_steps > 0xFFFFFE) return fail(nullptr, -1, "max_steps above 16,777,214 (the records keep 24 bits of an episode's step count; 0 = no cap)");
     if (f->eps_kind < 0 || f->eps_kind > 3) return fail(nullptr, -1, "bad eps_kind");
     if (f->tile_edge != 0 && f->tile_edge != 8 && f->tile_edge != 16) return fail(nullptr, -1, "tile_edge must be 0 (automatic), 8 or 16");
     cudarl_ctx* c = new (std::nothrow) cudarl_ctx();

@@ -53,11 +53,11 @@ struct TileP {
     unsigned tiles_x, tiles_y, ntiles;
     unsigned grid;             // blocks of the persistent step kernel (SMs x resident blocks per SM)
     unsigned wait_polls;       // 0: copy waits are bounded by time (seconds); > 0: by this many polls (tests only)
-    int4* rec[2];              // records {x, y, t, id} of the environments that stayed; [step & 1] is current
+    uint2* rec[2];             // 8-byte records {id, t << 8 | row in tile << 4 | column in tile} of the environments that stayed; [step & 1] is current
     uint2* reg;                // ntiles + 1: {start of the tile's region, its capacity}
     uint2* cnt[2];             // ntiles: {records in the region, records in the arrival buffer}
-    int4* arr[2];              // ntiles x ARR_CAP arrival slots
-    int4* ovf[2];              // records that found their tile's arrival buffer full, any tile, N slots
+    uint2* arr[2];             // ntiles x ARR_CAP arrival slots, same 8-byte records
+    int4* ovf[2];              // records {x, y, t, id} that found their tile's arrival buffer full, any tile, N slots
     unsigned* tctl;            // [0..2] spill counts (read step%3, append (step+1)%3, clear (step+2)%3); [3..4] scratch cursors by parity
     unsigned char* tcls;       // ntiles x cls_stride: one move byte per cell, tile by tile (which of the four moves are blocked / end on a goal)
     unsigned cls_stride;

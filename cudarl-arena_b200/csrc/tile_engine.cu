@@ -49,6 +49,16 @@ constexpr unsigned FAST_MAX = 128;      // records of a tile the fast path stage
 __device__ __forceinline__ unsigned tile_of(const TileP& tp, int x, int y) {
     return ((unsigned)y >> tp.tshift) * tp.tiles_x + ((unsigned)x >> tp.tshift);
 }
+// A record inside a tile's region or arrival buffer, 8 bytes: .x = environment, .y = steps of the episode << 8 | row inside the
+// tile << 4 | column inside the tile (the tile is known from where the record lies).  The step counter saturates at 2^24 - 2 (step caps beyond that are refused).
+constexpr unsigned T_SAT = 0xFFFFFEu;     // (T_SAT << 8 | 0xFF) stays clear of the all-ones word that marks a restart inside the step kernel
+__device__ __forceinline__ uint2 pack_rec(const TileP& tp, const int4 r) {
+    const unsigned m = tp.T - 1u, t = (unsigned)r.z < T_SAT ? (unsigned)r.z : T_SAT;
+    return make_uint2((unsigned)r.w, (t << 8) | (((unsigned)r.y & m) << 4) | ((unsigned)r.x & m));
+}
+__device__ __forceinline__ int4 unpack_rec(const uint2 q, int tx0, int ty0) {
+    return make_int4(tx0 + (int)(q.y & 15u), ty0 + (int)((q.y >> 4) & 15u), (int)(q.y >> 8), (int)q.x);
+}
 
 // Exclusive prefix of v over the block (any block size up to 1024); *total receives the block sum.
 __device__ __forceinline__ unsigned block_scan_excl(unsigned v, unsigned* s_warp, unsigned* total) {
@@ -153,7 +163,8 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 //   s_mv   T*T  u8       per cell: bit a = a move in direction a is blocked (grid edge or obstacle), bit 4+a = the
 //                        cell an environment stands on after choosing a (the next cell, or its own when blocked) is a goal
 //   s_halo 4T   float    max_a Q_t of the cells beyond the north / south / west / east edge (from the border array)
-//   s_rec  128  int4     fast path: the tile's records (bulk copies); a record that leaves the tile is written back here
+//   s_rec  130  8 bytes  fast path: the tile's records (bulk copies: arrivals, a pad slot when their number is odd, then the region);
+//                        a record that leaves the tile is written back here
 // and the work area:
 //   s_n    T*T  words    per cell: how many environments chose action a; zero between tiles.  8-byte words with 16 bits per action on
 //                        8 x 8 tiles; on 16 x 16 tiles 4-byte words with 8 bits per action (the fast path counts at most 128 records,
@@ -167,7 +178,7 @@ template <unsigned TSH> struct WarpSmem {
     static constexpr unsigned T = 1u << TSH, T2 = T * T;
     static constexpr unsigned CLS = T2;                              // a multiple of 16 for T = 8 and 16
     static constexpr unsigned ST_MV = T2 * 16u, ST_HALO = ST_MV + CLS, ST_REC = ST_HALO + 4u * T * 4u;
-    static constexpr unsigned REC_BYTES = FAST_MAX * 16u > T2 * 2u ? FAST_MAX * 16u : T2 * 2u;
+    static constexpr unsigned REC_BYTES = (FAST_MAX + 2u) * 8u > T2 * 2u ? (FAST_MAX + 2u) * 8u : T2 * 2u;   // + a pad slot and the copy's round-up
     static constexpr bool NARROW = TSH >= 4u;                        // 8-bit counters in shared memory; the general path then counts in global scratch
     static constexpr unsigned CELL_BYTES = NARROW ? 4u : 8u;
     static constexpr unsigned OFF_N = ST_REC + REC_BYTES, OFF_KD = OFF_N + T2 * CELL_BYTES, OFF_QUE = OFF_KD + FAST_MAX * 8u,
@@ -245,11 +256,11 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
 
     const unsigned long long g = p.step;
     const unsigned par = (unsigned)(g & 1ull);
-    const int4* __restrict__ in = tp.rec[par];
-    const int4* __restrict__ arr_in = tp.arr[par];
+    const uint2* __restrict__ in = tp.rec[par];
+    const uint2* __restrict__ arr_in = tp.arr[par];
     const int4* __restrict__ ovf_in = tp.ovf[par];
-    int4* __restrict__ out = tp.rec[par ^ 1u];
-    int4* __restrict__ arr_out = tp.arr[par ^ 1u];
+    uint2* __restrict__ out = tp.rec[par ^ 1u];
+    uint2* __restrict__ arr_out = tp.arr[par ^ 1u];
     int4* __restrict__ ovf_out = tp.ovf[par ^ 1u];
     uint2* __restrict__ cnt_next = tp.cnt[par ^ 1u];
     unsigned* ovf_cnt_next = tp.tctl + (unsigned)((g + 1ull) % 3ull);
@@ -295,20 +306,24 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     auto fetch_hdr = [&](unsigned tile) -> uint2 { return (tile < tp.ntiles && lane < 2u) ? hdr_src[tile] : make_uint2(0u, 0u); };
     // Issue the copies of a tile and fetch its first records into registers.  (One stage: a second one, with the next tile's
     // copies in flight during the work, cost more in registers and resident warps than it hid: 176 us against 127 us per step.)
-    unsigned roff = 0, fcap = 0, n_front = 0, n_in = 0;
+    unsigned roff = 0, fcap = 0, n_front = 0, n_arr = 0, n_in = 0, n_slots = 0;
     unsigned long long* const bar = &s_bar[warp];
     uint4 side = make_uint4(0u, 0u, 0u, 0u);      // this lane's 16 bytes of the tile's border values or move bytes, on their way to shared memory
     // Issue the copies of a tile: the table box (tensor copy) and, when the tile is small enough for the fast path, its records
     // (region and arrival buffer, one bulk copy each), all completing on the warp's barrier.
     auto issue = [&](unsigned tile, unsigned txi, unsigned tyi, const uint2 hw) {
         roff = __shfl_sync(FULL, hw.x, 0); fcap = __shfl_sync(FULL, hw.y, 0);
-        n_front = min(__shfl_sync(FULL, hw.x, 1), fcap); n_in = n_front + min(__shfl_sync(FULL, hw.y, 1), ARR_CAP);
-        const bool stage_records = n_in + n_spill <= FAST_MAX;        // room even if every spilled record were this tile's
-        if (lane == 0u) mbar_arrive_expect_tx(bar, T2 * 16u + (stage_records ? n_in * 16u : 0u));
+        n_front = min(__shfl_sync(FULL, hw.x, 1), fcap); n_arr = min(__shfl_sync(FULL, hw.y, 1), ARR_CAP); n_in = n_front + n_arr;
+        // Staged records: the arrivals first, then the region, each copy rounded up to 16 bytes (regions start on even records and
+        // have even capacities, so the round-up stays inside them); an odd number of arrivals leaves one pad slot behind them.
+        const unsigned a2 = (n_arr + 1u) & ~1u, f2 = (n_front + 1u) & ~1u;
+        n_slots = a2 + n_front;
+        const bool stage_records = n_slots + n_spill <= FAST_MAX;     // room even if every spilled record were this tile's
+        if (lane == 0u) mbar_arrive_expect_tx(bar, T2 * 16u + (stage_records ? (a2 + f2) * 8u : 0u));
         __syncwarp();
         if (lane == 0u) tensor_g2s_2d(wb, &tp.tmq, (int)(txi << TSH) * 4, (int)(tyi << TSH), bar);
-        else if (lane == 1u && stage_records && n_front) bulk_g2s(wb + L::ST_REC, in + roff, n_front * 16u, bar);
-        else if (lane == 2u && stage_records && n_in > n_front) bulk_g2s(wb + L::ST_REC + n_front * 16u, arr_in + (size_t)tile * ARR_CAP, (n_in - n_front) * 16u, bar);
+        else if (lane == 1u && stage_records && n_front) bulk_g2s(wb + L::ST_REC + a2 * 8u, in + roff, f2 * 8u, bar);
+        else if (lane == 2u && stage_records && n_arr) bulk_g2s(wb + L::ST_REC, arr_in + (size_t)tile * ARR_CAP, a2 * 8u, bar);
         // the small pieces (border values 16 T bytes, move bytes T*T) come as one 16-byte load per lane, stored after the wait
         if (lane < L::HALO_LANES) side = *reinterpret_cast<const uint4*>(halo_in + (size_t)tile * (4u * T) + lane * 4u);
         else if (lane < L::HALO_LANES + L::MV_LANES) side = *reinterpret_cast<const uint4*>(tp.tcls + (size_t)tile * L::CLS + (lane - L::HALO_LANES) * 16u);
@@ -316,7 +331,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     // A record that leaves its tile: one atomic on the new tile's arrival counter, then the store.  The fast path issues the
     // atomic at the end of a tile and stores a tile later, when the counter value has long arrived.
     auto store_arrival = [&](const int4 r, unsigned dt, unsigned apos) {
-        if (apos < ARR_CAP) arr_out[(size_t)dt * ARR_CAP + apos] = r;
+        if (apos < ARR_CAP) arr_out[(size_t)dt * ARR_CAP + apos] = pack_rec(tp, r);
         else {
             const unsigned qq = atomicAdd(ovf_cnt_next, 1u);
             if (qq < p.N) ovf_out[qq] = r; else s_acc[5] = 1u;
@@ -335,6 +350,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
         // out now, while this tile's copies are in flight
         if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
         const unsigned n_all = n_in + n_spill;
+        const unsigned pad_slot = (n_arr & 1u) ? n_arr : 0xFFFFFFFFu;
         const int tx0 = (int)(txi << TSH), ty0 = (int)(tyi << TSH);
         const unsigned char* st = wb;
         const float4* s_q = reinterpret_cast<const float4*>(st);
@@ -354,7 +370,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
 
         // stays: position in the tile's own region from a ballot.  Gives back whether the record still has to go somewhere else.
         unsigned nstay = 0;
-        auto put_stay = [&](bool act, bool stays, const int4 nrec) -> bool {
+        auto put_stay = [&](bool act, bool stays, const uint2 nrec) -> bool {
             const unsigned sm = __ballot_sync(FULL, act && stays);
             const unsigned pos = nstay + __popc(sm & lt);
             nstay += __popc(sm);
@@ -363,16 +379,16 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             return act && !placed;
         };
 
-        const bool fast = n_in + n_spill <= FAST_MAX;            // warp-uniform: the tile's records are in shared memory
+        const bool fast = n_slots + n_spill <= FAST_MAX;         // warp-uniform: the tile's records are in shared memory
         if (fast) {
             // A short spill list (records that found an arrival buffer full in the last step) is filtered here: what belongs to this
             // tile joins the staged records.  Only a long list sends a tile to the general path.
-            unsigned n_tot = n_in;
+            unsigned n_tot = n_slots;
             for (unsigned base = 0; base < n_spill; base += 32u) {
                 int4 r = make_int4(0, 0, 0, 0); bool mine = false;
                 if (base + lane < n_spill) { r = ovf_in[base + lane]; mine = tile_of(tp, r.x, r.y) == tile; }
                 const unsigned mm = __ballot_sync(FULL, mine);
-                if (mine) asm volatile("st.shared.v4.s32 [%0], {%1, %2, %3, %4};" :: "r"(srec + (n_tot + __popc(mm & lt)) * 16u), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+                if (mine) { const uint2 q = pack_rec(tp, r); asm volatile("st.shared.v2.u32 [%0], {%1, %2};" :: "r"(srec + (n_tot + __popc(mm & lt)) * 8u), "r"(q.x), "r"(q.y) : "memory"); }
                 n_tot += __popc(mm);
             }
             if (n_spill) __syncwarp();
@@ -387,14 +403,14 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
 #pragma unroll 1
             for (unsigned it = 0; it < rounds; ++it) {
                 const unsigned j = it * 32u + lane;
-                bool act = j < n_tot;
-                int4 rec = make_int4(0, 0, 0, 0);
-                if (act) asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(rec.x), "=r"(rec.y), "=r"(rec.z), "=r"(rec.w) : "r"(srec + j * 16u) : "memory");
-                const unsigned lx = (unsigned)(rec.x - tx0), ly = (unsigned)(rec.y - ty0);
+                bool act = j < n_tot && j != pad_slot;
+                unsigned id = 0u, w1 = 0u;
+                if (act) asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(id), "=r"(w1) : "r"(srec + j * 8u) : "memory");
+                const unsigned lx = w1 & 15u, ly = (w1 >> 4) & 15u;
                 if (act && (lx | ly) >= T) { s_acc[5] = 1u; act = false; }             // never seen: the record does not lie in this tile
-                int4 nrec = rec; bool stays = false; unsigned key = 0u; float dd = 0.0f;
+                uint2 nrec = make_uint2(id, 0u); bool stays = false; unsigned key = 0u; float dd = 0.0f;
                 if (act) {
-                    const U4 w = philox4x32_10(p.env_offset + (unsigned)rec.w, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
+                    const U4 w = philox4x32_10(p.env_offset + id, 0u, (unsigned)g, (unsigned)(g >> 32), p.k0, p.k1 ^ TAG_POLICY);
                     const unsigned ic = (ly << TSH) | lx;
                     const float4 row = lds_f4(sq + ic * 16u);
                     const unsigned mvb = lds_u8(smv + ic);
@@ -409,26 +425,29 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     if (stays) m = max4(lds_f4(sq + ((my << TSH) | mx) * 16u));
                     else m = lds_f32(shalo + 4u * ((int)my < 0 ? lx : my >= T ? T + lx : (int)mx < 0 ? 2u * T + ly : 3u * T + ly));
                     if (p.legacy_clamp && m < 0.0f) m = 0.0f;
-                    const float r = (blocked && p.ntraps) ? blocked_step_reward(p, rec.x, rec.y, a) : -0.01f;     // a trap charges its penalty
+                    const float r = (blocked && p.ntraps) ? blocked_step_reward(p, tx0 + (int)lx, ty0 + (int)ly, a) : -0.01f;     // a trap charges its penalty
                     dd = done ? 1.0f : __fmaf_rn(p.gamma, m, r);                     // the TD target of (cell, a), from Q_t
-                    if (TRACE) { p.tr_a[rec.w] = a; p.tr_r[rec.w] = done ? 1.0f : r; p.tr_d[rec.w] = done ? 1 : 0; }
+                    if (TRACE) { p.tr_a[id] = a; p.tr_r[id] = done ? 1.0f : r; p.tr_d[id] = done ? 1 : 0; }
                     const unsigned idx = ic * 4u + (unsigned)a;
                     bool first;
                     if (L::NARROW) { const unsigned old = atoms_add(sn + ic * 4u, 1u << (8u * (unsigned)a)); first = ((old >> (8u * (unsigned)a)) & 0xFFu) == 0u; }
                     else { const unsigned sh = 16u * ((unsigned)a & 1u), old = atoms_add(sn + (idx >> 1) * 4u, 1u << sh); first = ((old >> sh) & 0xFFFFu) == 0u; }
                     key = (first ? 0x40000000u : 0u) | idx;
-                    nrec.x = rec.x + dx; nrec.y = rec.y + dy; nrec.z = rec.z + 1;
-                    if (done || nrec.z >= c.tmax) {        // the episode ends: the start cell of the next one is drawn when the record is sent (below)
-                        nrec.z = -1; stays = false;
+                    const unsigned t1 = min((w1 >> 8) + 1u, T_SAT);
+                    nrec.y = (t1 << 8) | ((my & 15u) << 4) | (mx & 15u);             // meaningful when the record stays
+                    if (done || t1 >= (unsigned)c.tmax) {  // the episode ends: the start cell of the next one is drawn when the record is sent (below)
+                        nrec.y = 0xFFFFFFFFu; stays = false;
                         atomicAdd(&s_acc[done ? 0 : 1], 1u);
                     }
-                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" :: "r"(skd + j * 8u), "r"(key), "r"(__float_as_uint(dd)) : "memory");
                 }
-                // a record that leaves goes back into its slot and the slot's number into the queue; it is sent when the tile is done
+                // every slot gets its key (0 = owns nothing: the pad slot, a rejected record) and target for the owner pass
+                if (j < n_tot) asm volatile("st.shared.v2.u32 [%0], {%1, %2};" :: "r"(skd + j * 8u), "r"(key), "r"(__float_as_uint(dd)) : "memory");
+                // a record that leaves goes back into its slot (environment and new step count, or the restart mark; where it goes
+                // follows from its key) and the slot's number into the queue; it is sent when the tile is done
                 const bool leaves = put_stay(act, stays, nrec);
                 const unsigned lm = __ballot_sync(FULL, leaves);
                 if (leaves) {
-                    asm volatile("st.shared.v4.s32 [%0], {%1, %2, %3, %4};" :: "r"(srec + j * 16u), "r"(nrec.x), "r"(nrec.y), "r"(nrec.z), "r"(nrec.w) : "memory");
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" :: "r"(srec + j * 8u), "r"(nrec.x), "r"(nrec.y) : "memory");
                     asm volatile("st.shared.u8 [%0], %1;" :: "r"(sque + nleave + __popc(lm & lt)), "r"(j) : "memory");
                 }
                 nleave += __popc(lm);
@@ -469,10 +488,19 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                 pend = base + lane < nleave;
                 if (pend) {
                     const unsigned slot = lds_u8(sque + base + lane);
-                    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(pend_rec.x), "=r"(pend_rec.y), "=r"(pend_rec.z), "=r"(pend_rec.w) : "r"(srec + slot * 16u) : "memory");
-                    if (pend_rec.z < 0) {
-                        const unsigned sn2 = sample_start(p, p.env_offset + (unsigned)pend_rec.w, g + 1ull, TAG_START);
+                    unsigned id, w1;
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(id), "=r"(w1) : "r"(srec + slot * 8u) : "memory");
+                    pend_rec.w = (int)id;
+                    if (w1 == 0xFFFFFFFFu) {
+                        const unsigned sn2 = sample_start(p, p.env_offset + id, g + 1ull, TAG_START);
                         pend_rec.y = (int)(sn2 / (unsigned)p.W); pend_rec.x = (int)(sn2 - (unsigned)pend_rec.y * (unsigned)p.W); pend_rec.z = 0;
+                    } else {
+                        // where it went: its cell and action are in its key; a blocked move (a record that stayed but found its
+                        // tile's region full) keeps the cell
+                        const unsigned idx = lds_u32(skd + slot * 8u) & 0xFFFFu, ic = idx >> 2, a = idx & 3u;
+                        const bool blocked = (lds_u8(smv + ic) >> a) & 1u;
+                        const int dx = blocked ? 0 : (int)(signed char)(0xFF000100u >> (8 * a)), dy = blocked ? 0 : (int)(signed char)(0x000100FFu >> (8 * a));
+                        pend_rec.x = tx0 + (int)(ic & (T - 1u)) + dx; pend_rec.y = ty0 + (int)(ic >> TSH) + dy; pend_rec.z = (int)(w1 >> 8);
                     }
                     pend_dt = tile_of(tp, pend_rec.x, pend_rec.y);
                     pend_pos = atomicAdd(&cnt_next[pend_dt].y, 1u);
@@ -512,7 +540,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
             // record j of this tile's input: its region, its arrival buffer, then the spill list (filtered by tile in the loop)
             auto fetch = [&](unsigned j) -> int4 {
                 if (j >= n_all) return make_int4(0, 0, 0, 0);
-                return j < n_front ? in[roff + j] : j < n_in ? arr_in[(size_t)tile * ARR_CAP + (j - n_front)] : ovf_in[j - n_in];
+                return j < n_front ? unpack_rec(in[roff + j], tx0, ty0) : j < n_in ? unpack_rec(arr_in[(size_t)tile * ARR_CAP + (j - n_front)], tx0, ty0) : ovf_in[j - n_in];
             };
             int4 ahead = fetch(lane);                                 // one round ahead of the loop: its latency hides behind a round of work
             for (unsigned it = 0; it * 32u < n_all; ++it) {
@@ -531,7 +559,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     const int a = ((w.x >> 8) < c.eps_thr) ? (int)(w.y & 3u) : argmax4(s_q[ic]);
                     const bool blocked = (mvb >> a) & 1u, done = (mvb >> (4 + a)) & 1u;
                     const int dx = blocked ? 0 : (a == 1) - (a == 3), dy = blocked ? 0 : (a == 2) - (a == 0);
-                    nrec.x = rec.x + dx; nrec.y = rec.y + dy; nrec.z = rec.z + 1;
+                    nrec.x = rec.x + dx; nrec.y = rec.y + dy; nrec.z = (int)min((unsigned)rec.z + 1u, T_SAT);
                     if (TRACE) { p.tr_a[e] = a; p.tr_r[e] = done ? 1.0f : blocked ? blocked_step_reward(p, rec.x, rec.y, a) : -0.01f; p.tr_d[e] = done ? 1 : 0; }
                     // 32-bit shared-memory atomics are native; the 64-bit word of a cell is counted in its two halves
                     if (!crowded) atomicAdd(reinterpret_cast<unsigned*>(s_n) + 2u * ic + ((unsigned)a >> 1), 1u << (16u * ((unsigned)a & 1u)));
@@ -543,7 +571,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     }
                     stays = (((unsigned)(nrec.x - tx0)) | ((unsigned)(nrec.y - ty0))) < T;
                 }
-                if (put_stay(act, stays, nrec)) { const unsigned dt = tile_of(tp, nrec.x, nrec.y); store_arrival(nrec, dt, atomicAdd(&cnt_next[dt].y, 1u)); }
+                if (put_stay(act, stays, pack_rec(tp, nrec))) { const unsigned dt = tile_of(tp, nrec.x, nrec.y); store_arrival(nrec, dt, atomicAdd(&cnt_next[dt].y, 1u)); }
             }
             __syncwarp();
 
@@ -655,7 +683,7 @@ __global__ void __launch_bounds__(1024) k_te_layout(Params p) {
     for (unsigned base = 0; base < tp.ntiles; base += 1024u) {
         const unsigned k = base + threadIdx.x;
         const unsigned cnt = k < tp.ntiles ? tp.cnt[par][k].x : 0u;
-        const unsigned F = cnt + cnt / 4u + 32u;
+        const unsigned F = (cnt + cnt / 4u + 33u) & ~1u;        // even: a region starts and ends on a 16-byte boundary
         unsigned total = 0;
         const unsigned ex = block_scan_excl(k < tp.ntiles ? F : 0u, s_warp, &total);
         const unsigned carry = s_carry;
@@ -677,7 +705,7 @@ __global__ void k_te_scatter(Params p) {
     const int4 r = p.st[i];
     const unsigned tile = tile_of(tp, r.x, r.y);
     const unsigned pos = atomicAdd(&tp.cnt[par][tile].x, 1u);
-    tp.rec[par][tp.reg[tile].x + pos] = r;
+    tp.rec[par][tp.reg[tile].x + pos] = pack_rec(tp, r);
 }
 // The move byte of every cell, tile by tile as the step kernel copies them: bit a = a move in direction a is blocked (grid
 // edge or obstacle, src/kernels.cu:29-44 of the reference), bit 4+a = the cell an environment stands on after choosing a is a
@@ -730,10 +758,11 @@ __global__ void __launch_bounds__(BLOCK) k_te_export(Params p) {
         const uint2 rg = tp.reg[tile];
         const uint2 cn = tp.cnt[par][tile];
         const unsigned n_front = min(cn.x, rg.y), n_arr = min(cn.y, ARR_CAP);
-        const int4* in = tp.rec[par] + rg.x;
-        const int4* ain = tp.arr[par] + (size_t)tile * ARR_CAP;
-        for (unsigned j = threadIdx.x; j < n_front; j += BLOCK) { const int4 r = in[j]; if ((unsigned)r.w < p.N) p.st[r.w] = r; }
-        for (unsigned j = threadIdx.x; j < n_arr; j += BLOCK) { const int4 r = ain[j]; if ((unsigned)r.w < p.N) p.st[r.w] = r; }
+        const uint2* in = tp.rec[par] + rg.x;
+        const uint2* ain = tp.arr[par] + (size_t)tile * ARR_CAP;
+        const int tx0 = (int)((tile % tp.tiles_x) << tp.tshift), ty0 = (int)((tile / tp.tiles_x) << tp.tshift);
+        for (unsigned j = threadIdx.x; j < n_front; j += BLOCK) { const int4 r = unpack_rec(in[j], tx0, ty0); if ((unsigned)r.w < p.N) p.st[r.w] = r; }
+        for (unsigned j = threadIdx.x; j < n_arr; j += BLOCK) { const int4 r = unpack_rec(ain[j], tx0, ty0); if ((unsigned)r.w < p.N) p.st[r.w] = r; }
     }
 }
 __global__ void k_te_export_ovf(Params p) {
@@ -763,7 +792,7 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const 
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 static inline unsigned capped_blocks(size_t n) { const size_t b = (n + BLOCK - 1) / BLOCK; return (unsigned)(b < 1 ? 1 : (b > 2368 ? 2368 : b)); }
 
-constexpr unsigned MINB16 = 6, MINB8 = 6;     // resident blocks per SM the register budget is cut for: the most that compiles without spills
+constexpr unsigned MINB16 = 7, MINB8 = 6;     // resident blocks per SM the register budget is cut for: the most that compiles without spills
 size_t tile_step_smem(const Params& p) { return (size_t)WPB * (p.tp.tshift == 4u ? WarpSmem<4>::BYTES : WarpSmem<3>::BYTES); }
 unsigned tile_cls_stride(unsigned tshift) { return tshift == 4u ? WarpSmem<4>::CLS : WarpSmem<3>::CLS; }
 

@@ -72,7 +72,7 @@ typedef struct cudarl_config {
     int32_t  goal_xy[2 * CUDARL_MAX_GOALS]; /* LIST: x0,y0,x1,y1,... */
     int32_t  start_mode;
     int32_t  start_x, start_y;
-    int32_t  max_steps;     /* episode cap (auto-reset after this many steps); 0 = none */
+    int32_t  max_steps;     /* episode cap (auto-reset after this many steps); 0 = none; at most 16,777,214 -- an episode's step count is kept in 24 bits and saturates there when there is no cap */
     float    lr, gamma;
     int32_t  eps_kind;
     int32_t  reserved0;
