@@ -4,7 +4,7 @@
 // every step, so the step is organised around the TABLE, not around the environments:
 //
 //   * the grid is cut into T x T tiles (16 x 16 cells, or 8 x 8 on densely populated grids); the environments
-//     are kept bucketed by tile (records {x,y,t,id});
+//     are kept bucketed by tile (8-byte records: environment, step count, cell inside the tile);
 //   * a warp owns a tile for the whole step and needs no block-wide barrier: it fetches the tile of Q_t with
 //     ONE tensor copy (cp.async.bulk.tensor, a T x T box of float4 out of the row-major table) and the tile's
 //     records with two bulk copies, completion on the warp's own mbarrier; the tile's move bytes and border
@@ -26,10 +26,10 @@
 //     a full arrival buffer spills to a global list that every warp filters.  Regions are re-sized from the actual
 //     populations every few steps.
 //
-// What bounds the kernel (B200, 4096 x 4096 cells, 4,194,304 environments): the memory time of its 513 MB per step and the
-// issue time of its ~1,100 instructions per tile add up with little overlap inside a warp; resident warps (24 per SM: 78
-// registers, 9.1 KB of shared memory each) hide the rest.  The tile loop is rolled and reads its records from shared
-// memory on purpose: unrolled over register-held records it outgrew the instruction cache.
+// What bounds the kernel (B200, 4096 x 4096 cells, 4,194,304 environments): a tile is ~1,100 dependent instructions at ~10
+// cycles each for its warp; the 451 MB a step moves are hidden behind the other resident warps (28 per SM: 72 registers,
+// 7.75 KB of shared memory each).  The tile loop is rolled and reads its records from shared memory on purpose: unrolled
+// over register-held records it outgrew the instruction cache.
 //
 // Reference semantics (paths relative to the CudaRL-Arena project root):
 //   step        src/environment.cu:17-48, obstacle test src/kernels.cu:29-44, goal src/kernels.cu:56-59
@@ -792,7 +792,7 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const 
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 static inline unsigned capped_blocks(size_t n) { const size_t b = (n + BLOCK - 1) / BLOCK; return (unsigned)(b < 1 ? 1 : (b > 2368 ? 2368 : b)); }
 
-constexpr unsigned MINB16 = 7, MINB8 = 6;     // resident blocks per SM the register budget is cut for: the most that compiles without spills
+constexpr unsigned MINB16 = 7, MINB8 = 6;     // resident blocks per SM the register budget is cut for (16 x 16 tiles: no spills at 72 registers; 8 x 8 tiles: 8 bytes at 80, faster than 5 blocks at 94)
 size_t tile_step_smem(const Params& p) { return (size_t)WPB * (p.tp.tshift == 4u ? WarpSmem<4>::BYTES : WarpSmem<3>::BYTES); }
 unsigned tile_cls_stride(unsigned tshift) { return tshift == 4u ? WarpSmem<4>::CLS : WarpSmem<3>::CLS; }
 
