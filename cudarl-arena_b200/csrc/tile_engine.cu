@@ -304,8 +304,8 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     // are only exchanged when the tile's copies are issued, one tile after the loads.
     const uint2* hdr_src = lane == 0u ? tp.reg : tp.cnt[par];
     auto fetch_hdr = [&](unsigned tile) -> uint2 { return (tile < tp.ntiles && lane < 2u) ? hdr_src[tile] : make_uint2(0u, 0u); };
-    // Issue the copies of a tile and fetch its first records into registers.  (One stage: a second one, with the next tile's
-    // copies in flight during the work, cost more in registers and resident warps than it hid: 176 us against 127 us per step.)
+    // One copy stage per warp.  (A second one, with the next tile's copies in flight during the work, costs more in shared
+    // memory and resident warps than it hides: 134.8 us per step at 16 warps per SM against 121.6 us at 24 single-stage warps.)
     unsigned roff = 0, fcap = 0, n_front = 0, n_arr = 0, n_in = 0, n_slots = 0;
     unsigned long long* const bar = &s_bar[warp];
     uint4 side = make_uint4(0u, 0u, 0u, 0u);      // this lane's 16 bytes of the tile's border values or move bytes, on their way to shared memory
