@@ -339,13 +339,18 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     };
 
     const unsigned dty = nw / tp.tiles_x, dtx = nw - dty * tp.tiles_x;
-    unsigned tyi = gw / tp.tiles_x, txi = gw - tyi * tp.tiles_x, phase = 0;
-    uint2 hw = fetch_hdr(gw);
+    // Odd steps walk the tiles in descending order: what the last step touched last (table lines, records, border values
+    // of the final part of the grid) is what this step touches first, while it is still in L2.
+    const bool flip = (g & 1ull) != 0ull;
+    const unsigned first = flip ? tp.ntiles - 1u - gw : gw;           // meaningful when gw < ntiles
+    unsigned tyi = first / tp.tiles_x, txi = first - tyi * tp.tiles_x, phase = 0;
+    uint2 hw = fetch_hdr(gw < tp.ntiles ? first : tp.ntiles);
     bool pend = false; int4 pend_rec = make_int4(0, 0, 0, 0); unsigned pend_dt = 0, pend_pos = 0;
 
-    for (unsigned tile = gw; tile < tp.ntiles; tile += nw) {
+    for (unsigned seq = gw; seq < tp.ntiles; seq += nw) {
+        const unsigned tile = flip ? tp.ntiles - 1u - seq : seq;
         issue(tile, txi, tyi, hw);
-        hw = fetch_hdr(tile + nw);                              // in flight while this tile is worked on
+        hw = fetch_hdr(seq + nw < tp.ntiles ? (flip ? tile - nw : tile + nw) : tp.ntiles);      // in flight while this tile is worked on
         // the previous tile's leavers: their arrival counters were bumped before its border values went out; the stores go
         // out now, while this tile's copies are in flight
         if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
@@ -634,8 +639,8 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
         }
         fence_async_smem();                                      // this lane's reads of the stage come before the copies that will refill it
         __syncwarp();                                            // every lane is done with the tile
-        txi += dtx; tyi += dty;
-        if (txi >= tp.tiles_x) { txi -= tp.tiles_x; ++tyi; }
+        if (!flip) { txi += dtx; tyi += dty; if (txi >= tp.tiles_x) { txi -= tp.tiles_x; ++tyi; } }
+        else { txi -= dtx; tyi -= dty; if (txi >= tp.tiles_x) { txi += tp.tiles_x; --tyi; } }           // txi wrapped below zero
     }
 
     if (pend) store_arrival(pend_rec, pend_dt, pend_pos);
