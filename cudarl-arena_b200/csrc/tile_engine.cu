@@ -38,6 +38,7 @@
 //   episode     src/train.py:191-222
 #include "kernels.cuh"
 #include "rules.cuh"
+#include <cstring>
 
 namespace cudarl {
 
@@ -271,8 +272,11 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     if (threadIdx.x < 6u) s_acc[threadIdx.x] = 0u;
     if (lane == 0) mbar_init(&s_bar[warp], 1u);
     for (unsigned q = lane; q < T2 * L::CELL_BYTES / 4u; q += 32u) reinterpret_cast<unsigned*>(s_n)[q] = 0u;
-    if (gw == 0u && lane == 0u) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
     __syncthreads();
+    // The step is launched with programmatic stream serialisation: its blocks may become resident, and run everything above, while
+    // the previous kernel's last blocks are still at work.  From here on that kernel is complete and its writes are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (gw == 0u && lane == 0u) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
 
     StepCtx c;
     c.eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx];
@@ -644,6 +648,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     }
 
     if (pend) store_arrival(pend_rec, pend_dt, pend_pos);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the next kernel's blocks may take the slots that free up
 
     // ---- run statistics: warp -> block -> one atomic per counter and block ----------------------------------
     for (int o = 16; o; o >>= 1) conf += __shfl_xor_sync(FULL, conf, o);
@@ -848,8 +853,13 @@ void launch_tile_export(const Params& p, cudaStream_t st) {
 static unsigned tile_step_grid(const Params& p) { const unsigned need = (p.tp.ntiles + WPB - 1u) / WPB; return need < p.tp.grid ? need : p.tp.grid; }
 template <unsigned TSH, unsigned MINB>
 static void launch_step_one(const Params& p, bool trace, unsigned grid, size_t smem, cudaStream_t st) {
-    if (trace) k_tile_step<true, TSH, MINB><<<grid, WPB * 32u, smem, st>>>(p);
-    else       k_tile_step<false, TSH, MINB><<<grid, WPB * 32u, smem, st>>>(p);
+    cudaLaunchConfig_t cfg; memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(WPB * 32u); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (trace) cudaLaunchKernelEx(&cfg, k_tile_step<true, TSH, MINB>, p);
+    else       cudaLaunchKernelEx(&cfg, k_tile_step<false, TSH, MINB>, p);
 }
 void launch_tile_step(const Params& p, bool trace, cudaStream_t st) {
     const size_t smem = tile_step_smem(p);
