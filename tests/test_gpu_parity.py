@@ -439,6 +439,18 @@ def test_synchronised_step_cap_mass_restart(pkg, orc):
         g.close()
 
 
+def test_step_cap_beyond_the_record_format_is_refused(pkg):
+    """A tile record keeps 24 bits of an episode's step count: a larger cap is refused at creation, the largest one is accepted."""
+    cfg = pkg.make_config(8, 8, 16, start_mode=pkg.START_RANDOM, eps_kind=pkg.EPS_FIXED, eps0=0.5, max_steps=0xFFFFFF)
+    with pytest.raises(pkg.CudarlError):
+        pkg.VecGridWorld(cfg)
+    cfg.max_steps = 0xFFFFFE
+    g = pkg.VecGridWorld(cfg)
+    g.train_steps(3)
+    assert g.get_stats().device_error == 0
+    g.close()
+
+
 def test_odd_sizes_and_tiny_populations(pkg, orc):
     for w, h, n in [(1, 7, 5), (7, 1, 33), (13, 11, 1), (31, 3, 257), (5, 5, 0)]:
         cfg = pkg.make_config(w, h, n, start_mode=pkg.START_RANDOM, goal_mode=pkg.GOAL_SEEDED, num_goals=1,
