@@ -85,6 +85,7 @@ struct cudarl_ctx {
     std::vector<uint8_t> cells;           // host copy of the cell classes
     std::map<uint32_t, float> traps;      // cell -> penalty; mirrored on the device as a table sorted by cell
     void* dtraps = nullptr; size_t traps_cap = 0;
+    void* dtq = nullptr;                    // ticket counters of the step kernel's tile queues
     void* dpolicy = nullptr;                // greedy policy map of the evaluation rollout (one byte per cell), allocated on first use
     // device buffers
     void *dci = nullptr, *dreward = nullptr, *ddone = nullptr;
@@ -378,6 +379,10 @@ int alloc_tiles(cudarl_ctx* c) {
     CK(cudaMalloc(&c->dtscratch, scratch_cap * sizeof(uint2)));
     tp.scratch = (uint2*)c->dtscratch; tp.scratch_cap = (unsigned)scratch_cap;
     tp.wait_polls = 0;
+    { int sms = 0; CK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->cfg.device)); tp.nq = (unsigned)(sms > 0 ? sms : 1); }
+    CK(cudaMalloc(&c->dtq, 3 * (size_t)tp.nq * sizeof(unsigned)));
+    CK(cudaMemsetAsync(c->dtq, 0, 3 * (size_t)tp.nq * sizeof(unsigned), c->st));
+    tp.tq = (unsigned*)c->dtq;
     { int rm = make_table_map(c); if (rm) return rm; }
     if (tile_engine_configure(p, c->cfg.device) != 0) { cudaGetLastError(); return fail(c, -5, "tile step: shared memory request refused"); }
     return 0;
@@ -477,7 +482,7 @@ void free_all(cudarl_ctx* c) {
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->dgather, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6],
                     c->dQ, c->drec[0], c->drec[1], c->darr[0], c->darr[1], c->dovf[0], c->dovf[1], c->dbmax[0], c->dbmax[1],
-                    c->dtmeta, c->dtscratch, c->dtcls, c->dtraps, c->dpolicy};
+                    c->dtmeta, c->dtscratch, c->dtcls, c->dtraps, c->dpolicy, c->dtq};
     for (void* b : bufs) if (b) cudaFree(b);
     if (c->h_eps) cudaFreeHost(c->h_eps);
     for (auto e : c->kev) cudaEventDestroy(e);

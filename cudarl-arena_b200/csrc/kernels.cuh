@@ -52,7 +52,7 @@ struct TileP {
     unsigned tshift, T;        // tile edge = 1 << tshift cells
     unsigned tiles_x, tiles_y, ntiles;
     unsigned grid;             // blocks of the persistent step kernel (SMs x resident blocks per SM)
-    unsigned wait_polls;       // 0: copy waits are bounded by time (seconds); > 0: by this many polls (tests only)
+    unsigned wait_polls;       // 0: copy waits are bounded by time (seconds); > 0 (tests only): a wait of this many polls before the copies are issued, which must run out
     uint2* rec[2];             // 8-byte records {id, t << 8 | row in tile << 4 | column in tile} of the environments that stayed; [step & 1] is current
     uint2* reg;                // ntiles + 1: {start of the tile's region, its capacity}
     uint2* cnt[2];             // ntiles: {records in the region, records in the arrival buffer}
@@ -64,6 +64,8 @@ struct TileP {
     float* bmax[2];            // ntiles x 4T: max_a Q of the cells just outside the tile's north / south / west / east edge; [step & 1] is current
     uint2* scratch;            // scratch_cap x 8 bytes: 32-bit (cell, action) counters of the tiles the general path counts in global memory
     unsigned scratch_cap;
+    unsigned nq;               // tile queues of the step kernel: one per SM
+    unsigned* tq;              // 3 x nq ticket counters: [step % 3] in use, [(step + 2) % 3] cleared
     CUtensorMap tmq;           // the table as a 2-D tensor of floats (4W x H), box 4T x T: one copy instruction per tile
 };
 

@@ -132,7 +132,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 constexpr unsigned long long WAIT_NS = 2000000000ull;   // a copy that has not landed after two seconds never will
 
-// Wait for the phase with the given parity.  Bounded: by `polls` tries when polls > 0 (tests make the wait run
+// Wait for the phase with the given parity.  Bounded: by `polls` tries when polls > 0 (tests make a wait run
 // out that way), else by WAIT_NS of wall time.  false = gave up.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, unsigned polls) {
     if (polls) {
@@ -238,7 +238,7 @@ __device__ __forceinline__ float4 updated_row(const Params& p, const unsigned ch
     return row;
 }
 
-template <bool TRACE, unsigned TSH, unsigned MINB>
+template <bool TRACE, unsigned TSH, unsigned MINB, bool PROBE>
 __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_constant__ Params p) {
     using L = WarpSmem<TSH>;
     constexpr unsigned T = L::T, T2 = L::T2;
@@ -276,6 +276,14 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     // The step is launched with programmatic stream serialisation: its blocks may become resident, and run everything above, while
     // the previous kernel's last blocks are still at work.  From here on that kernel is complete and its writes are visible.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Tests only (an instantiation of its own, launched when a poll bound is set): a wait bounded by a number of looks at the
+    // barrier, taken before any copy has been issued, so that it must run out; the warp then does what it does when a copy never
+    // arrives: it records the failure and leaves (nothing is in flight yet).
+    bool gave_up = false;
+    if (PROBE) {
+        gave_up = !__all_sync(FULL, mbar_wait(&s_bar[threadIdx.x >> 5], 0u, p.tp.wait_polls ? p.tp.wait_polls : 1u));
+        if (gave_up && (threadIdx.x & 31u) == 0u) atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT);
+    }
     if (gw == 0u && lane == 0u) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
 
     StepCtx c;
@@ -342,19 +350,30 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
         }
     };
 
-    const unsigned dty = nw / tp.tiles_x, dtx = nw - dty * tp.tiles_x;
     // Odd steps walk the tiles in descending order: what the last step touched last (table lines, records, border values
     // of the final part of the grid) is what this step touches first, while it is still in L2.
     const bool flip = (g & 1ull) != 0ull;
-    const unsigned first = flip ? tp.ntiles - 1u - gw : gw;           // meaningful when gw < ntiles
-    unsigned tyi = first / tp.tiles_x, txi = first - tyi * tp.tiles_x, phase = 0;
-    uint2 hw = fetch_hdr(gw < tp.ntiles ? first : tp.ntiles);
     bool pend = false; int4 pend_rec = make_int4(0, 0, 0, 0); unsigned pend_dt = 0, pend_pos = 0;
-
-    for (unsigned seq = gw; seq < tp.ntiles; seq += nw) {
-        const unsigned tile = flip ? tp.ntiles - 1u - seq : seq;
+    // Tiles are handed out by queue, so that a warp that got light tiles takes more of them: queue q holds the tiles q, q + nq,
+    // q + 2 nq, ... and is served by the blocks q, q + nq, ... of this launch (nq = the number of SMs, or of blocks when there are
+    // fewer: every queue has a block, and blocks launched nq apart normally share an SM).  A warp draws its tickets with one atomic
+    // per tile, two tiles ahead of the work, so that neither the ticket nor the tile's header is waited for.
+    const unsigned QN = min(tp.nq, gridDim.x), cq = blockIdx.x % QN;
+    const unsigned qn = tp.ntiles / QN + (cq < tp.ntiles % QN ? 1u : 0u);                // tiles in this queue
+    unsigned* const qctr = tp.tq + (unsigned)(g % 3ull) * tp.nq + cq;
+    if (gw < tp.nq && lane == 0u) tp.tq[(unsigned)((g + 2ull) % 3ull) * tp.nq + gw] = 0u;  // the counters of the step after the next
+    auto draw = [&]() -> unsigned { return lane == 0u ? atomicAdd(qctr, 1u) : 0u; };     // lane 0 holds the ticket
+    auto ticket_tile = [&](unsigned t) -> unsigned { return t < qn ? (flip ? cq + QN * (qn - 1u - t) : cq + QN * t) : tp.ntiles; };
+    unsigned tk0 = __shfl_sync(FULL, draw(), 0), tk1 = draw(), phase = 0, txi = 0, tyi = 0;
+    uint2 hw = fetch_hdr(ticket_tile(tk0));
+    if (PROBE && gave_up) tk0 = qn;
+    while (tk0 < qn) {
+        const unsigned tile = ticket_tile(tk0);
+        tyi = tile / tp.tiles_x; txi = tile - tyi * tp.tiles_x;
         issue(tile, txi, tyi, hw);
-        hw = fetch_hdr(seq + nw < tp.ntiles ? (flip ? tile - nw : tile + nw) : tp.ntiles);      // in flight while this tile is worked on
+        tk0 = __shfl_sync(FULL, tk1, 0);                        // the ticket drawn one tile ago
+        tk1 = draw();
+        hw = fetch_hdr(ticket_tile(tk0));                       // in flight while this tile is worked on
         // the previous tile's leavers: their arrival counters were bumped before its border values went out; the stores go
         // out now, while this tile's copies are in flight
         if (pend) { store_arrival(pend_rec, pend_dt, pend_pos); pend = false; }
@@ -365,7 +384,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
         const float4* s_q = reinterpret_cast<const float4*>(st);
         const unsigned sq = sbase, smv = sq + L::ST_MV, shalo = sq + L::ST_HALO;
 
-        if (!__all_sync(FULL, mbar_wait(bar, phase, tp.wait_polls))) {
+        if (!__all_sync(FULL, mbar_wait(bar, phase, 0u))) {
             // Never seen with the time bound.  Flag it, let the copies land (they target this warp's shared memory), stop.
             if (lane == 0u) atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT);
             mbar_wait(bar, phase, 0u);
@@ -643,8 +662,6 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
         }
         fence_async_smem();                                      // this lane's reads of the stage come before the copies that will refill it
         __syncwarp();                                            // every lane is done with the tile
-        if (!flip) { txi += dtx; tyi += dty; if (txi >= tp.tiles_x) { txi -= tp.tiles_x; ++tyi; } }
-        else { txi -= dtx; tyi -= dty; if (txi >= tp.tiles_x) { txi += tp.tiles_x; --tyi; } }           // txi wrapped below zero
     }
 
     if (pend) store_arrival(pend_rec, pend_dt, pend_pos);
@@ -809,12 +826,13 @@ unsigned tile_cls_stride(unsigned tshift) { return tshift == 4u ? WarpSmem<4>::C
 template <unsigned TSH, unsigned MINB>
 static cudaError_t configure_one(int bytes, int* per_sm) {
     cudaError_t e = cudaSuccess;
-    const void* fns[2] = {(const void*)k_tile_step<false, TSH, MINB>, (const void*)k_tile_step<true, TSH, MINB>};
+    const void* fns[3] = {(const void*)k_tile_step<false, TSH, MINB, false>, (const void*)k_tile_step<true, TSH, MINB, false>,
+                          (const void*)k_tile_step<false, TSH, MINB, true>};
     for (const void* f : fns) {
         if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
     }
-    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH, MINB>, (int)(WPB * 32u), (size_t)bytes);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, k_tile_step<false, TSH, MINB, false>, (int)(WPB * 32u), (size_t)bytes);
     if (e == cudaSuccess && *per_sm > 0) {
         // no more shared memory than the resident blocks need (1 KB per block is the system's): the rest stays first-level cache
         int pct = (int)(((size_t)*per_sm * ((size_t)bytes + 1024u + 256u) * 100u + 228u * 1024u - 1u) / (228u * 1024u));
@@ -858,8 +876,9 @@ static void launch_step_one(const Params& p, bool trace, unsigned grid, size_t s
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    if (trace) cudaLaunchKernelEx(&cfg, k_tile_step<true, TSH, MINB>, p);
-    else       cudaLaunchKernelEx(&cfg, k_tile_step<false, TSH, MINB>, p);
+    if (trace)                cudaLaunchKernelEx(&cfg, k_tile_step<true, TSH, MINB, false>, p);
+    else if (p.tp.wait_polls) cudaLaunchKernelEx(&cfg, k_tile_step<false, TSH, MINB, true>, p);     // tests only: the waits run out
+    else                      cudaLaunchKernelEx(&cfg, k_tile_step<false, TSH, MINB, false>, p);
 }
 void launch_tile_step(const Params& p, bool trace, cudaStream_t st) {
     const size_t smem = tile_step_smem(p);

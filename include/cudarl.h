@@ -149,10 +149,10 @@ int cudarl_train_steps(cudarl_ctx* ctx, int64_t n);
 int cudarl_train_steps_eps(cudarl_ctx* ctx, int64_t n, const float* eps_host);
 /* Wait for everything enqueued on the context's stream; reports a failure recorded by a kernel. */
 int cudarl_synchronize(cudarl_ctx* ctx);
-/* Test hook, no counterpart in the reference: bound the train step's wait for a tile copy by `polls` tries
- * of the barrier instead of by time (0 = back to the time bound of two seconds).  With a bound of a few polls
- * the wait runs out before the copy lands: the warp records CUDARL_DEVERR_COPY_TIMEOUT, lets its copies
- * land, and leaves -- the path a copy that never arrives would take, exercised without any fault. */
+/* Test hook, no counterpart in the reference: with polls > 0 every warp of the train step first waits for its
+ * tile barrier for `polls` tries BEFORE any copy has been issued -- a wait nothing can complete, so it runs
+ * out: the warp records CUDARL_DEVERR_COPY_TIMEOUT and leaves, which is what it does when a copy never
+ * arrives within the normal bound (two seconds of wall time), exercised without any fault.  0 = normal operation. */
 int cudarl_debug_set_copy_wait_polls(cudarl_ctx* ctx, int32_t polls);
 
 /* When on, cudarl_train_steps records the action, reward and done flag of the LAST step of each
