@@ -39,7 +39,7 @@ PKG_DIR = os.path.join(ROOT, "cudarl-arena_b200")
 ALGO_BYTES_TRAIN = 60      # 12 state in + 12 state out + 16 Q[s] row + 16 Q[s'] row + 4 Q[s,a] write
 ALGO_BYTES_EVAL = 40       # greedy rollout step: 24 state + 16 Q[s] row
 FALLBACK_HBM_GBS = 6650.0
-TRAFFIC_C5 = 451.3e6      # dram__bytes_read.sum + dram__bytes_write.sum of one k_tile_step launch on C5 (one ncu capture of one launch)
+TRAFFIC_C5 = 455.5e6      # dram__bytes_read.sum + dram__bytes_write.sum of one k_tile_step launch on C5 (one ncu capture of one launch)
 
 
 def load_pkg():
