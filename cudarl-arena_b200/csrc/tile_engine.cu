@@ -25,6 +25,9 @@
 //     the next one starts on a seeded cell anywhere) is appended to its new tile's arrival buffer with one atomic;
 //     a full arrival buffer spills to a global list that every warp filters.  Regions are re-sized from the actual
 //     populations every few steps.
+//   * tiles are handed out from one queue per SM (one atomic per tile, drawn two tiles ahead), odd steps walk the queues
+//     backwards (a step starts on what the step before touched last, still in L2), and consecutive steps are chained by
+//     programmatic dependent launch (the next step's blocks are resident and initialised when this step's last tile is done).
 //
 // What bounds the kernel (B200, 4096 x 4096 cells, 4,194,304 environments): a tile is ~1,100 dependent instructions at ~10
 // cycles each for its warp; the 451 MB a step moves are hidden behind the other resident warps (28 per SM: 72 registers,
