@@ -276,6 +276,13 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     if (lane == 0) mbar_init(&s_bar[warp], 1u);
     for (unsigned q = lane; q < T2 * L::CELL_BYTES / 4u; q += 32u) reinterpret_cast<unsigned*>(s_n)[q] = 0u;
     __syncthreads();
+    // The first two tickets of this warp's tile queue (see the tile loop): this step's counters were cleared two steps ago and
+    // nobody else touches them, so the tickets can be on their way before the previous kernel is known to be complete.
+    const unsigned QN = min(tp.nq, gridDim.x), cq = blockIdx.x % QN;
+    const unsigned qn = tp.ntiles / QN + (cq < tp.ntiles % QN ? 1u : 0u);                // tiles in this queue
+    unsigned* const qctr = tp.tq + (unsigned)(g % 3ull) * tp.nq + cq;
+    auto draw = [&]() -> unsigned { return lane == 0u ? atomicAdd(qctr, 1u) : 0u; };     // lane 0 holds the ticket
+    unsigned tk0 = draw(), tk1 = draw();
     // The step is launched with programmatic stream serialisation: its blocks may become resident, and run everything above, while
     // the previous kernel's last blocks are still at work.  From here on that kernel is complete and its writes are visible.
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -288,6 +295,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
         if (gave_up && (threadIdx.x & 31u) == 0u) atomicOr(&p.ctl->error, ERR_COPY_TIMEOUT);
     }
     if (gw == 0u && lane == 0u) { tp.tctl[(unsigned)((g + 2ull) % 3ull)] = 0u; tp.tctl[3u + (par ^ 1u)] = 0u; }   // nobody touches these in this step
+    if (gw < tp.nq && lane == 0u) tp.tq[(unsigned)((g + 2ull) % 3ull) * tp.nq + gw] = 0u;                           // the queue counters of the step after the next
 
     StepCtx c;
     c.eps = p.eps_tab[p.eps_from_ctl ? p.ctl->eps_idx : p.eps_idx];
@@ -361,13 +369,9 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     // q + 2 nq, ... and is served by the blocks q, q + nq, ... of this launch (nq = the number of SMs, or of blocks when there are
     // fewer: every queue has a block, and blocks launched nq apart normally share an SM).  A warp draws its tickets with one atomic
     // per tile, two tiles ahead of the work, so that neither the ticket nor the tile's header is waited for.
-    const unsigned QN = min(tp.nq, gridDim.x), cq = blockIdx.x % QN;
-    const unsigned qn = tp.ntiles / QN + (cq < tp.ntiles % QN ? 1u : 0u);                // tiles in this queue
-    unsigned* const qctr = tp.tq + (unsigned)(g % 3ull) * tp.nq + cq;
-    if (gw < tp.nq && lane == 0u) tp.tq[(unsigned)((g + 2ull) % 3ull) * tp.nq + gw] = 0u;  // the counters of the step after the next
-    auto draw = [&]() -> unsigned { return lane == 0u ? atomicAdd(qctr, 1u) : 0u; };     // lane 0 holds the ticket
     auto ticket_tile = [&](unsigned t) -> unsigned { return t < qn ? (flip ? cq + QN * (qn - 1u - t) : cq + QN * t) : tp.ntiles; };
-    unsigned tk0 = __shfl_sync(FULL, draw(), 0), tk1 = draw(), phase = 0, txi = 0, tyi = 0;
+    unsigned phase = 0, txi = 0, tyi = 0;
+    tk0 = __shfl_sync(FULL, tk0, 0);
     uint2 hw = fetch_hdr(ticket_tile(tk0));
     if (PROBE && gave_up) tk0 = qn;
     while (tk0 < qn) {
