@@ -353,6 +353,7 @@ int alloc_tiles(cudarl_ctx* c) {
     tp.tshift = tsh; tp.T = 1u << tsh;
     tp.tiles_x = (unsigned)((p.W + (int)tp.T - 1) >> tsh); tp.tiles_y = (unsigned)((p.H + (int)tp.T - 1) >> tsh);
     tp.ntiles = tp.tiles_x * tp.tiles_y;
+    tp.tiles_x_rcp = tp.tiles_x > 1u ? (unsigned)((1ull << 32) / tp.tiles_x) : 0xFFFFFFFFu;
     const size_t nt = tp.ntiles;
     for (int k = 0; k < 2; ++k) {
         CK(cudaMalloc(&c->drec[k], (N + N / 4 + 34 * nt + 64) * sizeof(uint2)));

@@ -51,6 +51,7 @@ constexpr unsigned ARR_CAP = 32u;  // arrival slots per tile and step; what does
 struct TileP {
     unsigned tshift, T;        // tile edge = 1 << tshift cells
     unsigned tiles_x, tiles_y, ntiles;
+    unsigned tiles_x_rcp;      // floor(2^32 / tiles_x): umulhi(n, tiles_x_rcp) is n / tiles_x or one less, for every n < 2^32
     unsigned grid;             // blocks of the persistent step kernel (SMs x resident blocks per SM)
     unsigned wait_polls;       // 0: copy waits are bounded by time (seconds); > 0 (tests only): a wait of this many polls before the copies are issued, which must run out
     uint2* rec[2];             // 8-byte records {id, t << 8 | row in tile << 4 | column in tile} of the environments that stayed; [step & 1] is current

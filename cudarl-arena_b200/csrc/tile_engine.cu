@@ -376,7 +376,9 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     if (PROBE && gave_up) tk0 = qn;
     while (tk0 < qn) {
         const unsigned tile = ticket_tile(tk0);
-        tyi = tile / tp.tiles_x; txi = tile - tyi * tp.tiles_x;
+        // tile = tyi * tiles_x + txi: the quotient from a multiplication by the precomputed reciprocal, off by at most one
+        tyi = __umulhi(tile, tp.tiles_x_rcp); txi = tile - tyi * tp.tiles_x;
+        if (txi >= tp.tiles_x) { txi -= tp.tiles_x; ++tyi; }
         issue(tile, txi, tyi, hw);
         tk0 = __shfl_sync(FULL, tk1, 0);                        // the ticket drawn one tile ago
         tk1 = draw();
