@@ -403,6 +403,7 @@ def main():
                                    "one-byte-per-cell policy map once (k_eval_policy) and then reads one byte per environment-step, so "
                                    "against the 40 B per env-step of a rollout that reads Q[s] every step frac can exceed 1"}}
 
+    peer_mem = env.comm_peer_memory() if world > 1 else False
     if rank != 0:
         return
     cpu = None
@@ -431,6 +432,7 @@ def main():
         "eval": ev,
         "cpu_baseline": cpu,
         "cpu_baseline_reference_python": reference_python_sample(),
+        "averaging": (("peer memory: ordered sum over IPC-mapped peer tables, then NCCL all-gather" if peer_mem else "NCCL send/receive, ordered sum, all-gather") if world > 1 else None),
         "multi_gpu_parity": None if parity is None else "ok",
         "replica_digests_equal": digests_equal,
         "run_stats": {"steps": stats.steps, "goals": stats.goals, "timeouts": stats.timeouts,

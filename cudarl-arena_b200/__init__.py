@@ -44,7 +44,7 @@ class Config(C.Structure):
         ("eps_steps", C.c_int64),
         ("q_init_kind", C.c_int32), ("q_init_scale", C.c_float),
         ("legacy_clamp", C.c_int32), ("sync_every", C.c_int32),
-        ("rebucket_every", C.c_int32), ("tile_edge", C.c_int32), ("reserved", C.c_int32 * 2),
+        ("rebucket_every", C.c_int32), ("tile_edge", C.c_int32), ("avg_over_nccl", C.c_int32), ("reserved", C.c_int32 * 1),
     ]
 
     def copy(self):
@@ -100,6 +100,7 @@ ABI = {
     "cudarl_comm_unique_id": (C.c_int, [_P]),
     "cudarl_comm_init": (C.c_int, [_P, _P, C.c_int32, C.c_int32]),
     "cudarl_average_replicas": (C.c_int, [_P]),
+    "cudarl_comm_peer_memory": (C.c_int, [_P]),
     "cudarl_timer_start": (C.c_int, [_P]),
     "cudarl_timer_stop_ms": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "cudarl_kernel_timing": (C.c_int, [_P, C.c_int]),
@@ -341,6 +342,9 @@ class VecGridWorld:
 
     def average_replicas(self):
         self._ck(self.lib.cudarl_average_replicas(self.h))
+
+    def comm_peer_memory(self):
+        return bool(self.lib.cudarl_comm_peer_memory(self.h))
 
     def timer_start(self):
         self._ck(self.lib.cudarl_timer_start(self.h))

@@ -117,6 +117,11 @@ struct cudarl_ctx {
     bool trace = false;
     // communicator
     ncclComm_t comm = nullptr; int rank = 0, nranks = 1;
+    // replica averaging over peer memory: every rank's table mapped into this process (CUDA IPC), pointers in rank order
+    bool peer_ok = false;
+    std::vector<void*> peer_tables;         // [nranks]; this rank's own entry is its table
+    void* dpeer_ptrs = nullptr;             // the same pointers on the device
+    void* dbarrier_word = nullptr;          // one int for the all-reduce that serves as a barrier
     // timing
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     // kernel timing: one event pair around every uninterrupted run of step-kernel launches
@@ -421,6 +426,49 @@ int rebucket_tiles(cudarl_ctx* c) {
     return 0;
 }
 
+// Map every rank's table into this process: the CUDA IPC handles travel by an NCCL all-gather, each peer's handle is opened
+// (one process per GPU: a handle cannot be opened by the process that made it), and the ranks agree by an all-reduce whether
+// ALL of them succeeded -- only then is the peer-memory averaging used; otherwise every rank keeps the NCCL send / receive path.
+int map_peer_tables(cudarl_ctx* c) {
+    const int R = c->nranks, self = c->rank;
+    c->peer_ok = false;
+    std::vector<cudaIpcMemHandle_t> hs((size_t)R);
+    int ok = cudaIpcGetMemHandle(&hs[(size_t)self], c->dQ) == cudaSuccess ? 1 : 0;
+    cudaGetLastError();
+    void* dh = nullptr; int* dflag = nullptr;
+    CK(cudaMalloc(&dh, (size_t)R * sizeof(cudaIpcMemHandle_t)));
+    CK(cudaMalloc(&c->dbarrier_word, sizeof(int)));
+    dflag = (int*)c->dbarrier_word;
+    CK(cudaMemcpyAsync((char*)dh + (size_t)self * sizeof(cudaIpcMemHandle_t), &hs[(size_t)self], sizeof(cudaIpcMemHandle_t), cudaMemcpyHostToDevice, c->st));
+    NK(g_nccl.AllGather((char*)dh + (size_t)self * sizeof(cudaIpcMemHandle_t), dh, sizeof(cudaIpcMemHandle_t), ncclChar, c->comm, c->st));
+    CK(cudaMemcpyAsync(hs.data(), dh, (size_t)R * sizeof(cudaIpcMemHandle_t), cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    CK(cudaFree(dh));
+    c->peer_tables.assign((size_t)R, nullptr);
+    c->peer_tables[(size_t)self] = c->dQ;
+    for (int r = 0; r < R && ok; ++r) {
+        if (r == self) continue;
+        if (cudaIpcOpenMemHandle(&c->peer_tables[(size_t)r], hs[(size_t)r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { ok = 0; c->peer_tables[(size_t)r] = nullptr; }
+    }
+    cudaGetLastError();
+    // all or none
+    CK(cudaMemcpyAsync(dflag, &ok, sizeof(int), cudaMemcpyHostToDevice, c->st));
+    NK(g_nccl.AllReduce(dflag, dflag, 1, ncclInt, ncclMin, c->comm, c->st));
+    int all_ok = 0;
+    CK(cudaMemcpyAsync(&all_ok, dflag, sizeof(int), cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    CK(cudaMemsetAsync(dflag, 0, sizeof(int), c->st));          // from here on the word only carries the barrier all-reduce
+    if (all_ok) {
+        CK(cudaMalloc(&c->dpeer_ptrs, (size_t)R * sizeof(void*)));
+        CK(cudaMemcpyAsync(c->dpeer_ptrs, c->peer_tables.data(), (size_t)R * sizeof(void*), cudaMemcpyHostToDevice, c->st));
+        CK(cudaStreamSynchronize(c->st));
+        c->peer_ok = true;
+    } else {
+        for (int r = 0; r < R; ++r) if (r != self && c->peer_tables[(size_t)r]) { cudaIpcCloseMemHandle(c->peer_tables[(size_t)r]); c->peer_tables[(size_t)r] = nullptr; }
+    }
+    return 0;
+}
+
 // Q <- (Q_0 + Q_1 + ... + Q_{R-1}) * (1/R), summed in rank order on every GPU, shaped like an all-reduce: the table
 // is cut into R equal slices, rank j owns slice j.  (1) every rank sends its rows of slice j to rank j (grouped NCCL
 // send / receive over NVLink / NVSwitch); (2) rank j sums the R versions of its slice in rank order 0..R-1 in our own
@@ -433,6 +481,18 @@ int average_now(cudarl_ctx* c) {
     const size_t S = c->p.S, R = (size_t)c->nranks, self = (size_t)c->rank;
     const size_t slice = (S + R - 1) / R;                      // cells; R * slice <= S + 64 = the padded table
     if (R > 64) return fail(c, -1, "replica averaging supports at most 64 ranks");
+    if (c->peer_ok) {
+        // Fused exchange + ordered sum over NVLink: when every rank has finished its steps (the one-word all-reduce is the barrier),
+        // rank j reads slice j of every replica straight out of its peers' memory (plain loads, no staging copy), sums in rank
+        // order, scales, and writes its own table; the in-place all-gather then hands the averaged slices round.  Nobody's
+        // slice j is written before rank j has read it: only rank j's all-gather contribution lands there.
+        NK(g_nccl.AllReduce(c->dbarrier_word, c->dbarrier_word, 1, ncclInt, ncclSum, c->comm, c->st));
+        launch_q_average_peers((float4* const*)c->dpeer_ptrs, (unsigned)R, (unsigned)self, self * slice, slice, 1.0f / (float)R, c->st);
+        NK(g_nccl.AllGather(c->p.Q + self * slice, c->p.Q, slice * 4, ncclFloat, c->comm, c->st));
+        if (c->tile_mode) { c->p.step = (unsigned long long)c->h_step; launch_tile_border(c->p, c->st); }
+        CK(cudaGetLastError());
+        return 0;
+    }
     if (!c->dgather) CK(cudaMalloc(&c->dgather, (R - 1) * slice * sizeof(float4)));
     float4* table = c->p.Q; float4* others = (float4*)c->dgather;
     NK(g_nccl.GroupStart());
@@ -478,12 +538,13 @@ int run_steps(cudarl_ctx* c, int64_t n) {
 
 void free_all(cudarl_ctx* c) {
     if (c->st) cudaStreamSynchronize(c->st);
+    for (size_t r = 0; r < c->peer_tables.size(); ++r) if ((int)r != c->rank && c->peer_tables[r]) cudaIpcCloseMemHandle(c->peer_tables[r]);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     void* bufs[] = {c->dci, c->dstate[0], c->dstate[1], c->dimport, c->dactive, c->dreward, c->ddone, c->dent, c->dctl, c->deps,
                     c->dtra, c->dtrr, c->dtrd, c->dsckey, c->dscval, c->dgather, c->dact,
                     c->dub[0], c->dub[1], c->dub[2], c->dub[3], c->dub[4], c->dub[5], c->dub[6],
                     c->dQ, c->drec[0], c->drec[1], c->darr[0], c->darr[1], c->dovf[0], c->dovf[1], c->dbmax[0], c->dbmax[1],
-                    c->dtmeta, c->dtscratch, c->dtcls, c->dtraps, c->dpolicy, c->dtq};
+                    c->dtmeta, c->dtscratch, c->dtcls, c->dtraps, c->dpolicy, c->dtq, c->dpeer_ptrs, c->dbarrier_word};
     for (void* b : bufs) if (b) cudaFree(b);
     if (c->h_eps) cudaFreeHost(c->h_eps);
     for (auto e : c->kev) cudaEventDestroy(e);
@@ -903,8 +964,10 @@ int cudarl_comm_init(cudarl_ctx* c, const void* id128, int32_t rank, int32_t nra
     ncclUniqueId id; std::memcpy(&id, id128, sizeof(id));
     NK(g_nccl.CommInitRank(&c->comm, nranks, id, rank));
     c->rank = rank; c->nranks = nranks;
+    if (nranks > 1 && !c->cfg.avg_over_nccl) { int rp = map_peer_tables(c); if (rp) return rp; }
     return 0;
 }
+int cudarl_comm_peer_memory(const cudarl_ctx* c) { return (c && c->peer_ok) ? 1 : 0; }
 int cudarl_average_replicas(cudarl_ctx* c) {
     if (!c) return -1;
     CK(cudaSetDevice(c->cfg.device));

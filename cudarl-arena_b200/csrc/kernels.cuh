@@ -133,6 +133,7 @@ unsigned tile_cls_stride(unsigned tshift);                         // bytes of o
 void launch_tile_border(const Params& p, cudaStream_t st);         // border array of parity p.step & 1 from the table (after any change of the table outside train steps)
 // Replica averaging, the slice this rank owns: table[cell0 + i] = (sum over ranks 0..R-1 in that order) / R, where rank `self`'s
 // rows are the table's own and the other ranks' rows lie in `others` (R - 1 slices of n rows, ascending rank).
+void launch_q_average_peers(float4* const* tables, unsigned R, unsigned self, size_t cell0, size_t n, float scale, cudaStream_t st);
 void launch_q_average_slice(float4* table, const float4* others, unsigned R, unsigned self, size_t cell0, size_t n, float scale, cudaStream_t st);
 void launch_cell_set(const Params& p, unsigned cell, unsigned cls, int clear_goals, cudaStream_t st);
 

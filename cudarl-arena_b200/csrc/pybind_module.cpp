@@ -30,7 +30,7 @@ public:
             F(obstacle_kind, int) F(obstacle_p, float) F(goal_mode, int) F(num_goals, int) F(start_mode, int) F(start_x, int) F(start_y, int)
             F(max_steps, int) F(lr, float) F(gamma, float) F(eps_kind, int) F(eps0, double) F(eps_decay, double) F(eps_end, double)
             F(eps_steps, long long) F(q_init_kind, int) F(q_init_scale, float) F(legacy_clamp, int) F(sync_every, int)
-            F(rebucket_every, int) F(tile_edge, int)
+            F(rebucket_every, int) F(tile_edge, int) F(avg_over_nccl, int)
 #undef F
             if (k == "goals") {
                 auto lst = py::cast<std::vector<std::pair<int, int>>>(v);

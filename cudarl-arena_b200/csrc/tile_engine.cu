@@ -824,6 +824,20 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const 
     }
 }
 
+// The same over peer memory: tables[r] is rank r's whole table (this rank's own, or a peer's mapped through CUDA IPC and read
+// over NVLink with plain loads); this rank sums the slice it owns in rank order and writes it into its own table.
+__global__ void __launch_bounds__(BLOCK) k_q_average_peers(float4* const* __restrict__ tables, unsigned R, unsigned self, size_t cell0, size_t n, float scale) {
+    for (size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (size_t)gridDim.x * BLOCK) {
+        float4 acc = tables[0][cell0 + i];
+        for (unsigned r = 1; r < R; ++r) {
+            const float4 v = tables[r][cell0 + i];
+            acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+        }
+        acc.x = __fmul_rn(acc.x, scale); acc.y = __fmul_rn(acc.y, scale); acc.z = __fmul_rn(acc.z, scale); acc.w = __fmul_rn(acc.w, scale);
+        tables[self][cell0 + i] = acc;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 static inline unsigned nblk(unsigned n) { return (n + BLOCK - 1) / BLOCK; }
 static inline unsigned capped_blocks(size_t n) { const size_t b = (n + BLOCK - 1) / BLOCK; return (unsigned)(b < 1 ? 1 : (b > 2368 ? 2368 : b)); }
@@ -895,6 +909,9 @@ void launch_tile_step(const Params& p, bool trace, cudaStream_t st) {
     if (p.tp.tshift == 3u) launch_step_one<3, MINB8>(p, trace, grid, smem, st);
     else                   launch_step_one<4, MINB16>(p, trace, grid, smem, st);
     if (p.eps_from_ctl) k_tile_eps_episode<<<1, 1, 0, st>>>(p);
+}
+void launch_q_average_peers(float4* const* tables, unsigned R, unsigned self, size_t cell0, size_t n, float scale, cudaStream_t st) {
+    if (n) k_q_average_peers<<<capped_blocks(n), BLOCK, 0, st>>>(tables, R, self, cell0, n, scale);
 }
 void launch_q_average_slice(float4* table, const float4* others, unsigned R, unsigned self, size_t cell0, size_t n, float scale, cudaStream_t st) {
     if (n) k_q_average_slice<<<capped_blocks(n), BLOCK, 0, st>>>(table, others, R, self, cell0, n, scale);

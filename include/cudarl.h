@@ -86,7 +86,9 @@ typedef struct cudarl_config {
                                training starts); results never depend on it */
     int32_t  tile_edge;     /* tile edge of the train step in cells: 0 = chosen from the population density, or 8 / 16;
                                results never depend on it */
-    int32_t  reserved[2];
+    int32_t  avg_over_nccl; /* 1: the replica averaging always moves its slices by NCCL send / receive, never over IPC-mapped
+                               peer memory (same results; must be the same on every rank) */
+    int32_t  reserved[1];
 } cudarl_config;
 
 typedef struct cudarl_stats {
@@ -232,6 +234,11 @@ int cudarl_get_config(const cudarl_ctx* ctx, cudarl_config* out);
 int cudarl_comm_unique_id(void* id128);
 int cudarl_comm_init(cudarl_ctx* ctx, const void* id128, int32_t rank, int32_t nranks);
 int cudarl_average_replicas(cudarl_ctx* ctx);
+/* 1 when the averaging reads the peers' tables straight out of their memory (every rank a process of its own on one NVLink
+ * domain: the tables are mapped through CUDA IPC at cudarl_comm_init, the ordered sum of a rank's slice is one kernel over
+ * peer loads, NCCL only hands the averaged slices round); 0 when the slices travel by NCCL send / receive instead (chosen by
+ * all ranks together when any mapping fails); the results are the same bits either way. */
+int cudarl_comm_peer_memory(const cudarl_ctx* ctx);
 
 /* Timing helpers for benchmarks: record events on the context's stream. */
 int cudarl_timer_start(cudarl_ctx* ctx);

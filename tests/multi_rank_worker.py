@@ -41,6 +41,7 @@ def main():
     ap.add_argument("--envs", type=int, default=1024)
     ap.add_argument("--width", type=int, default=0)
     ap.add_argument("--height", type=int, default=0)
+    ap.add_argument("--avg", default="auto", help="gpu mode: 'nccl' forces the send / receive averaging, 'peer' demands the peer-memory one")
     a = ap.parse_args()
     SIZE[:] = [a.width, a.height]
     pkg = load_package()
@@ -50,10 +51,15 @@ def main():
     if a.mode == "gpu":
         cfg = shard_config(pkg, rank, a.envs, a.k)
         cfg.device = int(os.environ.get("LOCAL_RANK", rank))
+        cfg.avg_over_nccl = 1 if a.avg == "nccl" else 0
         env = pkg.VecGridWorld(cfg)
         ids = [pkg.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         env.comm_init(ids[0], rank, world)
+        if a.avg == "nccl":
+            assert not env.comm_peer_memory()
+        elif a.avg == "peer":
+            assert env.comm_peer_memory(), "the peers' tables could not be mapped"
         env.train_steps(a.steps)
         env.synchronize()
         mine_q, mine_state = env.get_q(), env.get_state()

@@ -46,6 +46,10 @@ def test_gpu_ranks_nccl():
     if n < 2:
         pytest.skip("needs at least two GPUs")
     run_ranks(2, "gpu", ["--steps", "24", "--k", "4", "--envs", "4096"])
+    # both forms of the averaging: slices by NCCL send / receive, and read straight out of the peers' IPC-mapped tables
+    run_ranks(2, "gpu", ["--steps", "12", "--k", "4", "--envs", "4096", "--avg", "nccl"])
+    run_ranks(2, "gpu", ["--steps", "12", "--k", "4", "--envs", "4096", "--avg", "peer"])
+    run_ranks(2, "gpu", ["--steps", "12", "--k", "4", "--envs", "8192", "--width", "1001", "--height", "999", "--avg", "nccl"])
     # 999,999 cells: the table does not split into equal slices, the last slice of the averaging runs into the table's padding
     run_ranks(2, "gpu", ["--steps", "12", "--k", "4", "--envs", "8192", "--width", "1001", "--height", "999"])
     if n >= 4:
