@@ -432,7 +432,7 @@ def main():
         "eval": ev,
         "cpu_baseline": cpu,
         "cpu_baseline_reference_python": reference_python_sample(),
-        "averaging": (("peer memory: ordered sum over IPC-mapped peer tables, then NCCL all-gather" if peer_mem else "NCCL send/receive, ordered sum, all-gather") if world > 1 else None),
+        "averaging": (("peer memory: one kernel per rank reads its slice of every IPC-mapped replica, sums in rank order, stores into every table" if peer_mem else "NCCL send/receive, ordered sum, all-gather") if world > 1 else None),
         "multi_gpu_parity": None if parity is None else "ok",
         "replica_digests_equal": digests_equal,
         "run_stats": {"steps": stats.steps, "goals": stats.goals, "timeouts": stats.timeouts,

@@ -482,13 +482,14 @@ int average_now(cudarl_ctx* c) {
     const size_t slice = (S + R - 1) / R;                      // cells; R * slice <= S + 64 = the padded table
     if (R > 64) return fail(c, -1, "replica averaging supports at most 64 ranks");
     if (c->peer_ok) {
-        // Fused exchange + ordered sum over NVLink: when every rank has finished its steps (the one-word all-reduce is the barrier),
-        // rank j reads slice j of every replica straight out of its peers' memory (plain loads, no staging copy), sums in rank
-        // order, scales, and writes its own table; the in-place all-gather then hands the averaged slices round.  Nobody's
-        // slice j is written before rank j has read it: only rank j's all-gather contribution lands there.
+        // Exchange, ordered sum and hand-round fused in one kernel over NVLink: when every rank has finished its steps (the
+        // one-word all-reduce is the barrier), rank j reads slice j of every replica straight out of its peers' memory (plain
+        // loads, no staging copy), sums in rank order, scales, and writes the result into slice j of EVERY rank's table (plain
+        // stores).  Slice j of any table is read and written by rank j alone, so the kernels of different ranks never meet; the
+        // second barrier tells a rank that all the others have delivered their slices into its table.
         NK(g_nccl.AllReduce(c->dbarrier_word, c->dbarrier_word, 1, ncclInt, ncclSum, c->comm, c->st));
         launch_q_average_peers((float4* const*)c->dpeer_ptrs, (unsigned)R, (unsigned)self, self * slice, slice, 1.0f / (float)R, c->st);
-        NK(g_nccl.AllGather(c->p.Q + self * slice, c->p.Q, slice * 4, ncclFloat, c->comm, c->st));
+        NK(g_nccl.AllReduce(c->dbarrier_word, c->dbarrier_word, 1, ncclInt, ncclSum, c->comm, c->st));
         if (c->tile_mode) { c->p.step = (unsigned long long)c->h_step; launch_tile_border(c->p, c->st); }
         CK(cudaGetLastError());
         return 0;

@@ -824,8 +824,10 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const 
     }
 }
 
-// The same over peer memory: tables[r] is rank r's whole table (this rank's own, or a peer's mapped through CUDA IPC and read
-// over NVLink with plain loads); this rank sums the slice it owns in rank order and writes it into its own table.
+// The same over peer memory: tables[r] is rank r's whole table (this rank's own, or a peer's mapped through CUDA IPC and
+// accessed over NVLink with plain loads and stores); this rank sums the slice it owns in rank order and writes the result into
+// EVERY rank's table -- reduce and hand-round in one kernel, both directions of the links in use at once.  Nobody else touches
+// slice `self` of any table between the two barriers that bracket the kernel (see average_now).
 __global__ void __launch_bounds__(BLOCK) k_q_average_peers(float4* const* __restrict__ tables, unsigned R, unsigned self, size_t cell0, size_t n, float scale) {
     for (size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (size_t)gridDim.x * BLOCK) {
         float4 acc = tables[0][cell0 + i];
@@ -834,8 +836,9 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_peers(float4* const* __rest
             acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
         }
         acc.x = __fmul_rn(acc.x, scale); acc.y = __fmul_rn(acc.y, scale); acc.z = __fmul_rn(acc.z, scale); acc.w = __fmul_rn(acc.w, scale);
-        tables[self][cell0 + i] = acc;
+        for (unsigned r = 0; r < R; ++r) tables[(self + r) % R][cell0 + i] = acc;       // own table first, then round the ring of peers
     }
+    __threadfence_system();
 }
 
 // ------------------------------------------------------------------------------------------------

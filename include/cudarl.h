@@ -234,10 +234,11 @@ int cudarl_get_config(const cudarl_ctx* ctx, cudarl_config* out);
 int cudarl_comm_unique_id(void* id128);
 int cudarl_comm_init(cudarl_ctx* ctx, const void* id128, int32_t rank, int32_t nranks);
 int cudarl_average_replicas(cudarl_ctx* ctx);
-/* 1 when the averaging reads the peers' tables straight out of their memory (every rank a process of its own on one NVLink
- * domain: the tables are mapped through CUDA IPC at cudarl_comm_init, the ordered sum of a rank's slice is one kernel over
- * peer loads, NCCL only hands the averaged slices round); 0 when the slices travel by NCCL send / receive instead (chosen by
- * all ranks together when any mapping fails); the results are the same bits either way. */
+/* 1 when the averaging works straight on the peers' memory (every rank a process of its own on one NVLink domain: the
+ * tables are mapped through CUDA IPC at cudarl_comm_init; one kernel per rank reads its slice of every replica with peer
+ * loads, sums in rank order and stores the result into every rank's table; NCCL only carries two one-word barriers);
+ * 0 when the slices travel by NCCL send / receive and all-gather instead (chosen by all ranks together when any mapping
+ * fails, or with avg_over_nccl); the results are the same bits either way. */
 int cudarl_comm_peer_memory(const cudarl_ctx* ctx);
 
 /* Timing helpers for benchmarks: record events on the context's stream. */
