@@ -828,15 +828,36 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const 
 // accessed over NVLink with plain loads and stores); this rank sums the slice it owns in rank order and writes the result into
 // EVERY rank's table -- reduce and hand-round in one kernel, both directions of the links in use at once.  Nobody else touches
 // slice `self` of any table between the two barriers that bracket the kernel (see average_now).
+template <unsigned RR>        // RR = number of ranks when it is small (all loads of a cell in flight together), 0 = any number
 __global__ void __launch_bounds__(BLOCK) k_q_average_peers(float4* const* __restrict__ tables, unsigned R, unsigned self, size_t cell0, size_t n, float scale) {
+    float4* tb[RR ? RR : 1u];
+    if (RR) {
+#pragma unroll
+        for (unsigned r = 0; r < RR; ++r) tb[r] = tables[r];
+    }
     for (size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (size_t)gridDim.x * BLOCK) {
-        float4 acc = tables[0][cell0 + i];
-        for (unsigned r = 1; r < R; ++r) {
-            const float4 v = tables[r][cell0 + i];
-            acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+        float4 acc;
+        if (RR) {
+            float4 v[RR ? RR : 1u];
+#pragma unroll
+            for (unsigned r = 0; r < RR; ++r) v[r] = tb[r][cell0 + i];
+            acc = v[0];
+#pragma unroll
+            for (unsigned r = 1; r < RR; ++r) { acc.x = __fadd_rn(acc.x, v[r].x); acc.y = __fadd_rn(acc.y, v[r].y); acc.z = __fadd_rn(acc.z, v[r].z); acc.w = __fadd_rn(acc.w, v[r].w); }
+        } else {
+            acc = tables[0][cell0 + i];
+            for (unsigned r = 1; r < R; ++r) {
+                const float4 v = tables[r][cell0 + i];
+                acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+            }
         }
         acc.x = __fmul_rn(acc.x, scale); acc.y = __fmul_rn(acc.y, scale); acc.z = __fmul_rn(acc.z, scale); acc.w = __fmul_rn(acc.w, scale);
-        for (unsigned r = 0; r < R; ++r) tables[(self + r) % R][cell0 + i] = acc;       // own table first, then round the ring of peers
+        if (RR) {
+#pragma unroll
+            for (unsigned r = 0; r < RR; ++r) tb[r][cell0 + i] = acc;
+        } else {
+            for (unsigned r = 0; r < R; ++r) tables[(self + r) % R][cell0 + i] = acc;       // own table first, then round the ring of peers
+        }
     }
     __threadfence_system();
 }
@@ -914,7 +935,15 @@ void launch_tile_step(const Params& p, bool trace, cudaStream_t st) {
     if (p.eps_from_ctl) k_tile_eps_episode<<<1, 1, 0, st>>>(p);
 }
 void launch_q_average_peers(float4* const* tables, unsigned R, unsigned self, size_t cell0, size_t n, float scale, cudaStream_t st) {
-    if (n) k_q_average_peers<<<capped_blocks(n), BLOCK, 0, st>>>(tables, R, self, cell0, n, scale);
+    if (!n) return;
+    const unsigned blocks = capped_blocks(n);
+    switch (R) {
+        case 2: k_q_average_peers<2><<<blocks, BLOCK, 0, st>>>(tables, R, self, cell0, n, scale); break;
+        case 3: k_q_average_peers<3><<<blocks, BLOCK, 0, st>>>(tables, R, self, cell0, n, scale); break;
+        case 4: k_q_average_peers<4><<<blocks, BLOCK, 0, st>>>(tables, R, self, cell0, n, scale); break;
+        case 8: k_q_average_peers<8><<<blocks, BLOCK, 0, st>>>(tables, R, self, cell0, n, scale); break;
+        default: k_q_average_peers<0><<<blocks, BLOCK, 0, st>>>(tables, R, self, cell0, n, scale); break;
+    }
 }
 void launch_q_average_slice(float4* table, const float4* others, unsigned R, unsigned self, size_t cell0, size_t n, float scale, cudaStream_t st) {
     if (n) k_q_average_slice<<<capped_blocks(n), BLOCK, 0, st>>>(table, others, R, self, cell0, n, scale);
