@@ -404,6 +404,7 @@ def main():
                                    "against the 40 B per env-step of a rollout that reads Q[s] every step frac can exceed 1"}}
 
     peer_mem = env.comm_peer_memory() if world > 1 else False
+    rebucket = int(cfg.rebucket_every) if int(cfg.rebucket_every) > 0 else 256      # the library's default period
     if rank != 0:
         return
     cpu = None
@@ -419,8 +420,8 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": bench_config(args.config, cfg, window, world),
         "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": int(window * 4), "d2h_bytes_per_step": 128},
-        # k_tile_step once per fused step, 5 kernels that re-size the record regions every 128th step, the averaging kernels
-        "gpu_launches": int(args.steps * (window + (window // 128) * 5 + averaging_kernels)),
+        # k_tile_step once per fused step, 5 kernels that re-size the record regions every `rebucket`-th step, the averaging kernels
+        "gpu_launches": int(args.steps * (window + (window // rebucket) * 5 + averaging_kernels)),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of ONE k_tile_step launch on this workload, from an ncu capture

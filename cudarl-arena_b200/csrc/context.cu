@@ -98,7 +98,7 @@ struct cudarl_ctx {
     void *dtmeta = nullptr, *dtscratch = nullptr, *dtcls = nullptr;   // per-tile regions / counters; 32-bit counters of crowded tiles
     bool tile_mode = false;               // true: the records live in tile regions (train steps), false: in environment order
     bool cls_dirty = true;                // the per-tile class bytes must be rebuilt from the cell words
-    int64_t bucket_every = 128, since_bucket = 0;
+    int64_t bucket_every = 256, since_bucket = 0;
     void *dent = nullptr, *dctl = nullptr, *deps = nullptr;
     void *dtra = nullptr, *dtrr = nullptr, *dtrd = nullptr, *dsckey = nullptr, *dscval = nullptr;
     void *dgather = nullptr;              // replica averaging: the other ranks' rows of this rank's slice
@@ -623,7 +623,7 @@ int cudarl_create(const cudarl_config* f, cudarl_ctx** out) {
             CK(cudaStreamSynchronize(c->st));
             return 0;
         };
-        c->bucket_every = f->rebucket_every > 0 ? f->rebucket_every : (f->rebucket_every < 0 ? 0 : 128);
+        c->bucket_every = f->rebucket_every > 0 ? f->rebucket_every : (f->rebucket_every < 0 ? 0 : 256);
         rc = body();
     } while (0);
     if (rc) { g_err = c->err; free_all(c); delete c; return rc; }

@@ -82,7 +82,7 @@ typedef struct cudarl_config {
     float    q_init_scale;
     int32_t  legacy_clamp;  /* 1: max_next = max(0, max_a' Q) as in src/kernels.cu:102-110 */
     int32_t  sync_every;    /* average the replicas every this many train steps; 0 = never */
-    int32_t  rebucket_every;/* re-size the per-tile record regions every this many train steps (0 = default 128, <0 = only when
+    int32_t  rebucket_every;/* re-size the per-tile record regions every this many train steps (0 = default 256, <0 = only when
                                training starts); results never depend on it */
     int32_t  tile_edge;     /* tile edge of the train step in cells: 0 = chosen from the population density, or 8 / 16;
                                results never depend on it */
