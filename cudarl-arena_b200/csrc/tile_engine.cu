@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
     unsigned* ovf_cnt_next = tp.tctl + (unsigned)((g + 1ull) % 3ull);
     const float* __restrict__ halo_in = tp.bmax[par];
     float* __restrict__ halo_out = tp.bmax[par ^ 1u];
-    const unsigned gw = blockIdx.x * WPB + warp, nw = gridDim.x * WPB;
+    const unsigned gw = blockIdx.x * WPB + warp;
 
     if (threadIdx.x < 6u) s_acc[threadIdx.x] = 0u;
     if (lane == 0) mbar_init(&s_bar[warp], 1u);
@@ -831,13 +831,13 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_slice(float4* table, const 
 template <unsigned RR>        // RR = number of ranks when it is small (all loads of a cell in flight together), 0 = any number
 __global__ void __launch_bounds__(BLOCK) k_q_average_peers(float4* const* __restrict__ tables, unsigned R, unsigned self, size_t cell0, size_t n, float scale) {
     float4* tb[RR ? RR : 1u];
-    if (RR) {
+    if constexpr (RR != 0u) {
 #pragma unroll
         for (unsigned r = 0; r < RR; ++r) tb[r] = tables[r];
     }
     for (size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (size_t)gridDim.x * BLOCK) {
         float4 acc;
-        if (RR) {
+        if constexpr (RR != 0u) {
             float4 v[RR ? RR : 1u];
 #pragma unroll
             for (unsigned r = 0; r < RR; ++r) v[r] = tb[r][cell0 + i];
@@ -852,7 +852,7 @@ __global__ void __launch_bounds__(BLOCK) k_q_average_peers(float4* const* __rest
             }
         }
         acc.x = __fmul_rn(acc.x, scale); acc.y = __fmul_rn(acc.y, scale); acc.z = __fmul_rn(acc.z, scale); acc.w = __fmul_rn(acc.w, scale);
-        if (RR) {
+        if constexpr (RR != 0u) {
 #pragma unroll
             for (unsigned r = 0; r < RR; ++r) tb[r][cell0 + i] = acc;
         } else {
