@@ -471,7 +471,8 @@ __global__ void __launch_bounds__(WPB * 32u, MINB) k_tile_step(const __grid_cons
                     else { const unsigned sh = 16u * ((unsigned)a & 1u), old = atoms_add(sn + (idx >> 1) * 4u, 1u << sh); first = ((old >> sh) & 0xFFFFu) == 0u; }
                     key = (first ? 0x40000000u : 0u) | idx;
                     const unsigned t1 = min((w1 >> 8) + 1u, T_SAT);
-                    nrec.y = (t1 << 8) | ((my & 15u) << 4) | (mx & 15u);             // meaningful when the record stays
+                    // meaningful when the record stays; on 16 x 16 tiles row << 4 | column is the cell's index inside the tile
+                    nrec.y = TSH == 4u ? (t1 << 8) | (((my << 4) | mx) & 0xFFu) : (t1 << 8) | ((my & 15u) << 4) | (mx & 15u);
                     if (done || t1 >= (unsigned)c.tmax) {  // the episode ends: the start cell of the next one is drawn when the record is sent (below)
                         nrec.y = 0xFFFFFFFFu; stays = false;
                         atomicAdd(&s_acc[done ? 0 : 1], 1u);
