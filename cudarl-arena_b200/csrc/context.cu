@@ -840,6 +840,7 @@ int cudarl_set_state(cudarl_ctx* c, const int32_t* x, const int32_t* y, const in
     const size_t N = c->p.N;
     if (x) for (size_t i = 0; i < N; ++i) if (x[i] < 0 || x[i] >= c->p.W) return fail(c, -3, "Invalid state");
     if (y) for (size_t i = 0; i < N; ++i) if (y[i] < 0 || y[i] >= c->p.H) return fail(c, -3, "Invalid state");
+    if (t) for (size_t i = 0; i < N; ++i) if (t[i] < 0 || t[i] > 0xFFFFFE) return fail(c, -3, "Invalid state (an episode's step count lies in 0 .. 16,777,214)");
     CK(cudaSetDevice(c->cfg.device));
     { int rl = leave_tiles(c); if (rl) return rl; }
     if (!c->dimport) CK(cudaMalloc(&c->dimport, (N ? N : 1) * 12));

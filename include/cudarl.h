@@ -193,7 +193,8 @@ int cudarl_update_batch_static(float* d_q, int32_t width, int32_t height, int64_
                                const uint8_t* d_dones, float lr, float gamma, int32_t legacy_clamp, void* stream);
 
 /* Environment::getAgentX/getAgentY (src/environment.h:27-28) for all environments, plus the
- * per-episode step counters.  Any pointer may be NULL. */
+ * per-episode step counters.  Any pointer may be NULL.  cudarl_set_state refuses positions outside the grid and
+ * step counters outside 0 .. 16,777,214 ("Invalid state"). */
 int cudarl_get_state(cudarl_ctx* ctx, int32_t* x, int32_t* y, int32_t* t);
 int cudarl_set_state(cudarl_ctx* ctx, const int32_t* x, const int32_t* y, const int32_t* t);
 /* Environment::getReward / isDone (src/environment.h:29-30) after cudarl_step_actions. */

@@ -448,6 +448,13 @@ def test_step_cap_beyond_the_record_format_is_refused(pkg):
     g = pkg.VecGridWorld(cfg)
     g.train_steps(3)
     assert g.get_stats().device_error == 0
+    x, y, t = g.get_state()
+    with pytest.raises(pkg.CudarlError):                # a step count the records cannot hold
+        g.set_state(x, y, np.full_like(t, 0xFFFFFF))
+    g.set_state(x, y, np.full_like(t, 0xFFFFFD))        # one step short of the cap: every environment times out in the next step
+    g.train_steps(1)
+    assert g.get_stats().timeouts >= 16 - g.get_stats().goals and g.get_stats().device_error == 0
+    assert int(g.get_state()[2].max()) <= 1
     g.close()
 
 
